@@ -1,0 +1,161 @@
+/*
+ * i8tk.h -- C ABI of the B200 (sm_100a) INT8 transformer-kernel library.
+ *
+ * Drop-in boundary for the hot path of Ashuuuri/int8-transformer-kernels:
+ * split-KV flash-decoding attention over an INT8 KV cache, the per-token INT8
+ * quantiser that feeds it, and the fused INT8 MLP.  Every entry point takes
+ * plain device pointers and sizes, an explicit CUDA stream, caller-owned
+ * workspace, and returns an int status (0 = success).  Nothing here allocates
+ * device memory, synchronises the device, or depends on PyTorch.
+ *
+ * The reference exposes the same operations as C++-linkage launchers declared
+ * in kernels/int8_ext.cu:27-70 (raw pointers + ints, void return, legacy
+ * default stream, library-owned static scratch).  Each declaration below cites
+ * the reference interface it replaces.
+ */
+#ifndef I8TK_H_
+#define I8TK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A cudaStream_t passed through an opaque pointer (NULL = legacy default stream). */
+typedef void* i8tk_stream_t;
+
+enum i8tk_status {
+    I8TK_OK = 0,
+    I8TK_ERR_INVALID_ARGUMENT = 1,  /* null pointer, non-positive size, bad flag      */
+    I8TK_ERR_UNSUPPORTED = 2,       /* head_dim not in {64,128}, non-tile MLP shape   */
+    I8TK_ERR_WORKSPACE = 3,         /* workspace null or smaller than *_workspace_bytes */
+    I8TK_ERR_ALIGNMENT = 4,         /* pointer not aligned as documented              */
+    I8TK_ERR_CUDA = 5,              /* a CUDA runtime/driver call or launch failed    */
+    I8TK_ERR_DEVICE_TIMEOUT = 6     /* a bounded device-side wait gave up             */
+};
+
+/* Human-readable name of a status code (static storage). */
+const char* i8tk_status_string(int status);
+/* Detail of the last failure on the calling thread (static thread-local storage). */
+const char* i8tk_last_error(void);
+/* Library version, major*10000 + minor*100 + patch. */
+int i8tk_version(void);
+
+/* ------------------------------------------------------------------------
+ * Per-token symmetric INT8 quantiser.
+ * Replaces the torch code tests/test_int8.py:47-63 (quantize_per_token) ==
+ * validation/validate_int8.py:63-66 (q_per_token); the reference has no native
+ * per-token quantiser (kernels/quant_utils.cu is per-tensor).
+ *   x       [rows, cols] fp32 (or fp16 for the _f16 form), row-major
+ *   q       [rows, cols] int8
+ *   scales  [rows]       fp32:  max(absmax,1e-8)/127, codes = clamp(rne(x/scale),-128,127)
+ * Results are bit-identical to the torch code.  cols >= 1.
+ * ---------------------------------------------------------------------- */
+int i8tk_quantize_per_token_f32(const float* x, int8_t* q, float* scales,
+                                int64_t rows, int cols, i8tk_stream_t stream);
+int i8tk_quantize_per_token_f16(const void* x_f16, int8_t* q, float* scales,
+                                int64_t rows, int cols, i8tk_stream_t stream);
+
+/* Per-tensor FP16 -> INT8 with a dynamically computed scale, and the inverse.
+ * Replaces quantize_fp16_to_int8 / dequantize_int8_to_fp16
+ * (kernels/int8_common.cuh:54-59, kernels/quant_utils.cu:57-77).
+ * d_scale (device float[1]) receives absmax/127; codes = clamp(rne(x/scale)).
+ * amax_scratch: device float[1] used for the reduction. */
+int i8tk_quantize_fp16_to_int8(const void* x_f16, int8_t* q, float* d_scale,
+                               int64_t n, i8tk_stream_t stream);
+int i8tk_dequantize_int8_to_fp16(const int8_t* q, void* out_f16, float scale,
+                                 int64_t n, i8tk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * INT8-KV decode attention (seq_q == 1), split-KV flash decoding.
+ * Replaces int8_decode_attention_forward (kernels/int8_ext.cu:34-38,
+ * kernels/int8_decode_attention.cu:443-547).
+ *   Q  [BH, D] int8          sQ [BH]    fp32
+ *   K  [BH, S, D] int8       sK [BH*S]  fp32      (contiguous, row-major)
+ *   V  [BH, S, D] int8       sV [BH*S]  fp32
+ *   out [BH, D] fp16
+ * score_j = (q.k_j) * sQ * sK_j / sqrt(D); out = softmax(score) . (sV_j * v_j).
+ * D in {64,128}.  Q, K, V must be 16-byte aligned, scales 4-byte aligned.
+ * workspace: >= i8tk_decode_workspace_bytes(BH,S,D) bytes, 256-byte aligned,
+ * private to this call until it completes on `stream`.
+ * ---------------------------------------------------------------------- */
+size_t i8tk_decode_workspace_bytes(int BH, int S, int head_dim);
+int i8tk_decode_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V,
+                                  void* out_f16,
+                                  const float* sQ, const float* sK, const float* sV,
+                                  int BH, int S, int head_dim,
+                                  void* workspace, size_t workspace_bytes,
+                                  i8tk_stream_t stream);
+
+/* Sequence-sharded form: the same scan over this caller's KV positions, but
+ * the result is left as ONE unnormalised online-softmax partial per (b,h):
+ *   part[bh] = { m (log2 units), l, 0, 0, acc[0..D) }   -- D+4 floats per row
+ * to be merged across shards with i8tk_decode_combine_partials.  Generalises
+ * the partial/combine hand-off of kernels/int8_decode_attention.cu:274-426
+ * from splits inside one GPU to KV chunks on several GPUs. */
+int i8tk_decode_attention_partial(const int8_t* Q, const int8_t* K, const int8_t* V,
+                                  float* part,
+                                  const float* sQ, const float* sK, const float* sV,
+                                  int BH, int S, int head_dim,
+                                  void* workspace, size_t workspace_bytes,
+                                  i8tk_stream_t stream);
+/* parts: [nparts, BH, D+4] fp32 as written above (gathered from all shards);
+ * out: [BH, D] fp16.  Partials with l <= 0 (empty shard) are skipped, as
+ * kernels/int8_decode_attention.cu:414 does. */
+int i8tk_decode_combine_partials(const float* parts, int nparts, int BH, int head_dim,
+                                 void* out_f16, i8tk_stream_t stream);
+
+/* Floats per (b,h) row of a partial: head_dim + 4. */
+int i8tk_decode_partial_stride(int head_dim);
+
+/* Describes how a call would be split (for tests and tuning): writes the
+ * number of KV splits per (b,h) and the positions per split. */
+int i8tk_decode_plan(int BH, int S, int head_dim, int* nsplit, int* chunk);
+
+/* ------------------------------------------------------------------------
+ * Fused INT8 MLP:  out = requant( (requant(GELU((x.W1)*sx*sW1 + b1))) . W2 * sh * sW2 )
+ * Replaces int8_mlp_forward, int8_mlp_forward_per_channel,
+ * int8_mlp_forward_per_channel_bias and int8_mlp_forward_prepacked
+ * (kernels/int8_ext.cu:40-68, kernels/int8_mlp.cu:1231-1314) with one entry
+ * point and flags.
+ *   x   [T, d_model] int8
+ *   W1  [d_model, d_ff] int8, W2 [d_ff, d_model] int8          (default), or
+ *   W1T [d_ff, d_model],      W2T [d_model, d_ff] when I8TK_MLP_PREPACKED
+ *   scale_x   fp32 [T]       (I8TK_MLP_X_PER_TOKEN)   else [1]
+ *   scale_W1  fp32 [d_ff]    (I8TK_MLP_W_PER_CHANNEL) else [1]
+ *   scale_W2  fp32 [d_model] (I8TK_MLP_W_PER_CHANNEL) else [1]
+ *   bias1     fp32 [d_ff] or NULL       (added before GELU)
+ *   out       [T, d_model] int8
+ *   out_row_scales  fp32 [T] or NULL.  Non-NULL: the output is requantised per
+ *                   token and its scales written here.  NULL: legacy dynamic
+ *                   per-tensor output scale, written to *out_tensor_scale.
+ *   out_tensor_scale device fp32[1] or NULL (required when out_row_scales is NULL)
+ * T, d_model, d_ff must be multiples of 128 (the reference's tile gate,
+ * kernels/int8_mlp.cu:1023-1026); other shapes return I8TK_ERR_UNSUPPORTED.
+ * All pointers 16-byte aligned.
+ * ---------------------------------------------------------------------- */
+enum i8tk_mlp_flags {
+    I8TK_MLP_X_PER_TOKEN = 1,
+    I8TK_MLP_W_PER_CHANNEL = 2,
+    I8TK_MLP_PREPACKED = 4
+};
+size_t i8tk_mlp_workspace_bytes(int T, int d_model, int d_ff, int flags);
+int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out,
+                     const float* scale_x, const float* scale_W1, const float* scale_W2,
+                     const float* bias1, float* out_row_scales, float* out_tensor_scale,
+                     int T, int d_model, int d_ff, int flags,
+                     void* workspace, size_t workspace_bytes, i8tk_stream_t stream);
+
+/* W1 [d_model,d_ff] -> W1T [d_ff,d_model]; W2 [d_ff,d_model] -> W2T [d_model,d_ff].
+ * Replaces transpose_int8_weights (kernels/int8_ext.cu:58-61,
+ * kernels/int8_mlp.cu:1288-1297). */
+int i8tk_transpose_int8_weights(const int8_t* W1, const int8_t* W2,
+                                int8_t* W1T, int8_t* W2T,
+                                int d_model, int d_ff, i8tk_stream_t stream);
+
+#ifdef __cplusplus
+}  /* extern "C" */
+#endif
+#endif  /* I8TK_H_ */

@@ -1,0 +1,170 @@
+// int8_ext -- PyTorch binding over the i8tk C ABI (include/i8tk.h).
+//
+// Mirrors the Python surface of the reference's torch extension
+// (kernels/int8_ext.cu:458-479): the same six names / seven overloads with
+// the same argument order, dtypes, shapes, scale layouts and return values,
+// the same argument checks (TORCH_CHECK -> RuntimeError) with the same
+// messages.  Differences, all additive:
+//   * launches go to torch's current CUDA stream on the tensors' device and
+//     scratch comes from torch's caching allocator (the reference uses the
+//     legacy default stream and process-global static buffers);
+//   * a non-zero status from the C ABI raises RuntimeError;
+//   * extra ops the reference only has as Python code or inside its launcher:
+//     quantize_per_token, int8_decode_attention_partial,
+//     int8_decode_combine_partials.
+// This file contains no kernels and no arithmetic.
+#include <torch/extension.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+
+#include <tuple>
+
+#include "../../include/i8tk.h"
+
+namespace {
+
+void check_status(int rc, const char* what) {
+    TORCH_CHECK(rc == I8TK_OK, what, " failed: ", i8tk_status_string(rc), " (", i8tk_last_error(), ")");
+}
+
+i8tk_stream_t current_stream() {
+    return static_cast<i8tk_stream_t>(c10::cuda::getCurrentCUDAStream().stream());
+}
+
+torch::Tensor make_workspace(size_t bytes, const torch::Device& dev) {
+    // torch's caching allocator returns 512-byte aligned blocks
+    return torch::empty({static_cast<int64_t>(bytes ? bytes : 256)},
+                        torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+}
+
+// ---- decode attention (kernels/int8_ext.cu:136-178) -------------------------
+struct DecodeArgs {
+    int BH, S, D;
+    torch::Tensor sQ, sK, sV;
+};
+
+DecodeArgs check_decode(const torch::Tensor& Q, const torch::Tensor& K, const torch::Tensor& V,
+                        const torch::Tensor& scale_Q, const torch::Tensor& scale_K,
+                        const torch::Tensor& scale_V) {
+    TORCH_CHECK(Q.device().is_cuda(), "Q must be a CUDA tensor");
+    TORCH_CHECK(Q.dtype() == torch::kInt8, "Q must be int8");
+    TORCH_CHECK(K.dtype() == torch::kInt8 && V.dtype() == torch::kInt8, "K, V must be int8");
+    TORCH_CHECK(Q.is_contiguous() && K.is_contiguous() && V.is_contiguous(),
+                "Q/K/V must be contiguous");
+    TORCH_CHECK(Q.dim() == 3, "expected Q (batch, heads, head_dim) — seq_q == 1");
+    TORCH_CHECK(K.dim() == 4, "expected K (batch, heads, seq_kv, head_dim)");
+    TORCH_CHECK(K.sizes() == V.sizes(), "K/V shape mismatch");
+    const int64_t batch = Q.size(0), heads = Q.size(1), head_dim = Q.size(2), seq_kv = K.size(2);
+    TORCH_CHECK(K.size(0) == batch && K.size(1) == heads && K.size(3) == head_dim,
+                "Q/K head/batch/dim mismatch");
+    TORCH_CHECK(head_dim == 64 || head_dim == 128, "decode kernel v1 supports head_dim 64 or 128");
+    TORCH_CHECK(K.device() == Q.device() && V.device() == Q.device(), "Q/K/V must be on one device");
+    TORCH_CHECK(scale_Q.dtype() == torch::kFloat32 && scale_K.dtype() == torch::kFloat32 &&
+                    scale_V.dtype() == torch::kFloat32, "scales must be float32");
+    TORCH_CHECK(scale_Q.device() == Q.device() && scale_K.device() == Q.device() &&
+                    scale_V.device() == Q.device(), "scales must be on the same CUDA device as Q");
+    TORCH_CHECK(batch * heads < (1ll << 31) && seq_kv < (1ll << 31), "shape too large");
+    DecodeArgs a;
+    a.BH = static_cast<int>(batch * heads);
+    a.S = static_cast<int>(seq_kv);
+    a.D = static_cast<int>(head_dim);
+    a.sQ = scale_Q.contiguous().view({a.BH});
+    a.sK = scale_K.contiguous().view({static_cast<int64_t>(a.BH) * a.S});
+    a.sV = scale_V.contiguous().view({static_cast<int64_t>(a.BH) * a.S});
+    return a;
+}
+
+torch::Tensor int8_decode_attention_forward_torch(torch::Tensor Q, torch::Tensor K, torch::Tensor V,
+                                                  torch::Tensor scale_Q, torch::Tensor scale_K,
+                                                  torch::Tensor scale_V) {
+    DecodeArgs a = check_decode(Q, K, V, scale_Q, scale_K, scale_V);
+    c10::cuda::CUDAGuard guard(Q.device());
+    auto out = torch::empty({Q.size(0), Q.size(1), Q.size(2)},
+                            torch::TensorOptions().dtype(torch::kFloat16).device(Q.device()));
+    const size_t wbytes = i8tk_decode_workspace_bytes(a.BH, a.S, a.D);
+    auto ws = make_workspace(wbytes, Q.device());
+    check_status(i8tk_decode_attention_forward(
+                     Q.data_ptr<int8_t>(), K.data_ptr<int8_t>(), V.data_ptr<int8_t>(), out.data_ptr(),
+                     a.sQ.data_ptr<float>(), a.sK.data_ptr<float>(), a.sV.data_ptr<float>(), a.BH, a.S,
+                     a.D, ws.data_ptr(), wbytes, current_stream()),
+                 "int8_decode_attention_forward");
+    return out;
+}
+
+// Unnormalised (m, l, acc) rows for a KV shard: fp32 [B, H, D+4].
+torch::Tensor int8_decode_attention_partial_torch(torch::Tensor Q, torch::Tensor K, torch::Tensor V,
+                                                  torch::Tensor scale_Q, torch::Tensor scale_K,
+                                                  torch::Tensor scale_V) {
+    DecodeArgs a = check_decode(Q, K, V, scale_Q, scale_K, scale_V);
+    c10::cuda::CUDAGuard guard(Q.device());
+    auto part = torch::empty({Q.size(0), Q.size(1), a.D + 4},
+                             torch::TensorOptions().dtype(torch::kFloat32).device(Q.device()));
+    const size_t wbytes = i8tk_decode_workspace_bytes(a.BH, a.S, a.D);
+    auto ws = make_workspace(wbytes, Q.device());
+    check_status(i8tk_decode_attention_partial(
+                     Q.data_ptr<int8_t>(), K.data_ptr<int8_t>(), V.data_ptr<int8_t>(),
+                     part.data_ptr<float>(), a.sQ.data_ptr<float>(), a.sK.data_ptr<float>(),
+                     a.sV.data_ptr<float>(), a.BH, a.S, a.D, ws.data_ptr(), wbytes, current_stream()),
+                 "int8_decode_attention_partial");
+    return part;
+}
+
+// parts fp32 [nparts, B, H, D+4] -> fp16 [B, H, D]
+torch::Tensor int8_decode_combine_partials_torch(torch::Tensor parts) {
+    TORCH_CHECK(parts.device().is_cuda(), "parts must be a CUDA tensor");
+    TORCH_CHECK(parts.dtype() == torch::kFloat32, "parts must be float32");
+    TORCH_CHECK(parts.is_contiguous(), "parts must be contiguous");
+    TORCH_CHECK(parts.dim() == 4, "expected parts (nparts, batch, heads, head_dim + 4)");
+    const int64_t D = parts.size(3) - 4;
+    TORCH_CHECK(D == 64 || D == 128, "decode kernel v1 supports head_dim 64 or 128");
+    c10::cuda::CUDAGuard guard(parts.device());
+    auto out = torch::empty({parts.size(1), parts.size(2), D},
+                            torch::TensorOptions().dtype(torch::kFloat16).device(parts.device()));
+    check_status(i8tk_decode_combine_partials(parts.data_ptr<float>(), static_cast<int>(parts.size(0)),
+                                              static_cast<int>(parts.size(1) * parts.size(2)),
+                                              static_cast<int>(D), out.data_ptr(), current_stream()),
+                 "int8_decode_combine_partials");
+    return out;
+}
+
+// ---- per-token quantiser (tests/test_int8.py:47-63) ---------------------------
+std::tuple<torch::Tensor, torch::Tensor> quantize_per_token_torch(torch::Tensor t) {
+    TORCH_CHECK(t.device().is_cuda(), "t must be a CUDA tensor");
+    TORCH_CHECK(t.dtype() == torch::kFloat32 || t.dtype() == torch::kFloat16,
+                "t must be float32 or float16");
+    TORCH_CHECK(t.dim() >= 1, "t must have at least one dimension");
+    auto x = t.contiguous();
+    const int64_t cols = x.size(-1);
+    TORCH_CHECK(cols >= 1 && cols < (1ll << 31), "last dimension out of range");
+    const int64_t rows = cols ? x.numel() / cols : 0;
+    c10::cuda::CUDAGuard guard(x.device());
+    auto q = torch::empty(x.sizes(), torch::TensorOptions().dtype(torch::kInt8).device(x.device()));
+    auto sizes = x.sizes().vec();
+    sizes.pop_back();
+    auto s = torch::empty(sizes, torch::TensorOptions().dtype(torch::kFloat32).device(x.device()));
+    int rc;
+    if (x.dtype() == torch::kFloat32)
+        rc = i8tk_quantize_per_token_f32(x.data_ptr<float>(), q.data_ptr<int8_t>(), s.data_ptr<float>(),
+                                         rows, static_cast<int>(cols), current_stream());
+    else
+        rc = i8tk_quantize_per_token_f16(x.data_ptr(), q.data_ptr<int8_t>(), s.data_ptr<float>(), rows,
+                                         static_cast<int>(cols), current_stream());
+    check_status(rc, "quantize_per_token");
+    return {q, s};
+}
+
+}  // namespace
+
+#include "int8_ext_mlp.inc"
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("int8_decode_attention_forward", &int8_decode_attention_forward_torch,
+          "INT8 flash-decoding attention (seq_q==1, INT8 KV cache) — returns FP16");
+    m.def("int8_decode_attention_partial", &int8_decode_attention_partial_torch,
+          "INT8 decode attention over a KV shard — returns unnormalised (m, l, 0, 0, acc[D]) rows");
+    m.def("int8_decode_combine_partials", &int8_decode_combine_partials_torch,
+          "Log-sum-exp merge of gathered decode partials — returns FP16");
+    m.def("quantize_per_token", &quantize_per_token_torch,
+          "Per-token symmetric INT8 quantisation — returns (int8, fp32 scales)");
+    register_mlp_ops(m);
+}

@@ -1,0 +1,258 @@
+// Per-token (row-wise) and per-tensor symmetric INT8 quantisers.
+//
+// Per token: bit-identical to the torch code the reference uses to feed its
+// kernels (tests/test_int8.py:47-63 == validation/validate_int8.py:63-66):
+//   absmax = max(|x|.amax(-1), 1e-8);  scale = absmax / 127   (fp32 IEEE division)
+//   q = clamp(round_half_even(x / scale), -128, 127)          (fp32 IEEE division)
+// Per tensor: kernels/quant_utils.cu:12-77 (absmax -> /127 -> rne(x/scale)).
+//
+// HBM-bound streaming kernels: 16-byte loads, several independent rows in
+// flight per lane group, absmax by warp shuffles, no shared memory.
+#include "common.cuh"
+
+namespace i8tk {
+namespace {
+
+template <typename T> struct Vec16;          // 16 bytes of input elements
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+};
+template <> struct Vec16<__half> {
+    static constexpr int N = 8;
+    __device__ static void load(const __half* p, float (&v)[8]) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+};
+
+__device__ __forceinline__ int quant1(float x, float scale) {
+    // true division + round-half-even + clamp, exactly as torch does on fp32
+    const float r = rintf(__fdiv_rn(x, scale));
+    return (int)fminf(fmaxf(r, -128.f), 127.f);
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
+           ((uint32_t)(d & 0xff) << 24);
+}
+
+// Rows of `cols` elements, cols a multiple of Vec16<T>::N.  A row is handled by a
+// group of G lanes (G a power of two <= 32); lane i of the group owns vectors
+// i, i+G, ... (at most NV of them).  Each group keeps R rows in flight.
+template <typename T, int G, int NV, int R>
+__global__ void __launch_bounds__(256)
+quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
+                         float* __restrict__ scales, long long rows, int cols) {
+    constexpr int N = Vec16<T>::N;
+    const int nvec = cols / N;
+    constexpr int GPW = 32 / G;                     // groups per warp
+    const int lane_in_group = threadIdx.x % G;
+    const int group_in_warp = (threadIdx.x & 31) / G;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+
+    // The trip count is the same for every lane of a warp (the shuffles below
+    // name all 32 lanes); rows past the end are predicated off.
+    for (long long w0 = warp * GPW * R; w0 < rows; w0 += nwarps * GPW * R) {
+        const long long r0 = w0 + (long long)group_in_warp * R;
+        float v[R][NV][N];
+        float amax[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            amax[r] = 0.f;
+            const long long row = r0 + r;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int vi = lane_in_group + j * G;
+                if (row < rows && vi < nvec) {
+                    Vec16<T>::load(x + row * cols + (long long)vi * N, v[r][j]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) v[r][j][e] = 0.f;
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+#pragma unroll
+                for (int e = 0; e < N; ++e) amax[r] = fmaxf(amax[r], fabsf(v[r][j][e]));
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1)
+                amax[r] = fmaxf(amax[r], __shfl_xor_sync(0xffffffffu, amax[r], o));
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const long long row = r0 + r;
+            if (row >= rows) continue;
+            const float scale = __fdiv_rn(fmaxf(amax[r], 1e-8f), 127.0f);
+            if (lane_in_group == 0) scales[row] = scale;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int vi = lane_in_group + j * G;
+                if (vi >= nvec) continue;
+                int8_t* dst = q + row * cols + (long long)vi * N;
+                if constexpr (N == 4) {
+                    *reinterpret_cast<uint32_t*>(dst) =
+                        pack4(quant1(v[r][j][0], scale), quant1(v[r][j][1], scale),
+                              quant1(v[r][j][2], scale), quant1(v[r][j][3], scale));
+                } else {
+                    uint2 pk;
+                    pk.x = pack4(quant1(v[r][j][0], scale), quant1(v[r][j][1], scale),
+                                 quant1(v[r][j][2], scale), quant1(v[r][j][3], scale));
+                    pk.y = pack4(quant1(v[r][j][4], scale), quant1(v[r][j][5], scale),
+                                 quant1(v[r][j][6], scale), quant1(v[r][j][7], scale));
+                    *reinterpret_cast<uint2*>(dst) = pk;
+                }
+            }
+        }
+    }
+}
+
+// Any width / any alignment: one warp per row, two passes over the row (the
+// second pass hits L1/L2).
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_rows_generic_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
+                             float* __restrict__ scales, long long rows, int cols) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long row = warp; row < rows; row += nwarps) {
+        const T* xr = x + row * cols;
+        float amax = 0.f;
+        for (int i = lane; i < cols; i += 32) amax = fmaxf(amax, fabsf((float)xr[i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+        if (lane == 0) scales[row] = scale;
+        int8_t* qr = q + row * cols;
+        for (int i = lane; i < cols; i += 32) qr[i] = (int8_t)quant1((float)xr[i], scale);
+    }
+}
+
+template <typename T, int G, int NV, int R>
+int launch_vec(const T* x, int8_t* q, float* scales, long long rows, int cols, cudaStream_t st) {
+    const long long groups = (rows + R - 1) / R;
+    const long long threads = groups * G;
+    long long blocks = (threads + 255) / 256;
+    const long long cap = 148ll * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    quantize_rows_vec_kernel<T, G, NV, R><<<(int)blocks, 256, 0, st>>>(x, q, scales, rows, cols);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
+
+template <typename T>
+int quantize_per_token(const T* x, int8_t* q, float* scales, long long rows, int cols,
+                       cudaStream_t st) {
+    I8TK_REQUIRE(x && q && scales, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(rows >= 0 && cols >= 1, I8TK_ERR_INVALID_ARGUMENT,
+                 "rows must be >= 0 and cols >= 1 (rows=%lld cols=%d)", rows, cols);
+    if (rows == 0) return I8TK_OK;
+    constexpr int N = Vec16<T>::N;
+    const bool vec_ok = (cols % N == 0) && aligned_to(x, 16) && aligned_to(q, N);
+    const int nvec = cols / N;
+    if (vec_ok && nvec <= 256) {
+        if (nvec <= 1) return launch_vec<T, 1, 1, 4>(x, q, scales, rows, cols, st);
+        if (nvec <= 2) return launch_vec<T, 2, 1, 4>(x, q, scales, rows, cols, st);
+        if (nvec <= 4) return launch_vec<T, 4, 1, 4>(x, q, scales, rows, cols, st);
+        if (nvec <= 8) return launch_vec<T, 8, 1, 4>(x, q, scales, rows, cols, st);
+        if (nvec <= 16) return launch_vec<T, 16, 1, 4>(x, q, scales, rows, cols, st);
+        if (nvec <= 32) return launch_vec<T, 32, 1, 4>(x, q, scales, rows, cols, st);
+        if (nvec <= 64) return launch_vec<T, 32, 2, 2>(x, q, scales, rows, cols, st);
+        if (nvec <= 128) return launch_vec<T, 32, 4, 1>(x, q, scales, rows, cols, st);
+        return launch_vec<T, 32, 8, 1>(x, q, scales, rows, cols, st);
+    }
+    long long blocks = (rows * 32 + 255) / 256;
+    if (blocks > 148ll * 16) blocks = 148ll * 16;
+    quantize_rows_generic_kernel<T><<<(int)blocks, 256, 0, st>>>(x, q, scales, rows, cols);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
+
+// ---- per-tensor (kernels/quant_utils.cu) ---------------------------------
+__global__ void amax_f16_kernel(const __half* __restrict__ x, long long n, float* amax) {
+    float v = 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        v = fmaxf(v, fabsf(__half2float(x[i])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(v));
+}
+
+__global__ void finalize_scale_kernel(float* s) { *s = *s / 127.f; }
+
+__global__ void quant_tensor_f16_kernel(const __half* __restrict__ x, int8_t* __restrict__ q,
+                                        long long n, const float* __restrict__ d_scale) {
+    const float scale = *d_scale;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float v = __fdiv_rn(__half2float(x[i]), scale);
+        q[i] = (int8_t)__float2int_rn(fmaxf(-128.f, fminf(127.f, v)));
+    }
+}
+
+__global__ void dequant_tensor_kernel(const int8_t* __restrict__ q, __half* __restrict__ out,
+                                      long long n, float scale) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = __float2half((float)q[i] * scale);
+}
+
+int grid_for(long long n) {
+    long long b = (n + 255) / 256;
+    if (b > 148ll * 16) b = 148ll * 16;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+}  // namespace
+}  // namespace i8tk
+
+using namespace i8tk;
+
+extern "C" int i8tk_quantize_per_token_f32(const float* x, int8_t* q, float* scales, int64_t rows,
+                                           int cols, i8tk_stream_t stream) {
+    return quantize_per_token<float>(x, q, scales, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int i8tk_quantize_per_token_f16(const void* x, int8_t* q, float* scales, int64_t rows,
+                                           int cols, i8tk_stream_t stream) {
+    return quantize_per_token<__half>(static_cast<const __half*>(x), q, scales, rows, cols,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int i8tk_quantize_fp16_to_int8(const void* x, int8_t* q, float* d_scale, int64_t n,
+                                          i8tk_stream_t stream) {
+    I8TK_REQUIRE(x && q && d_scale && n > 0, I8TK_ERR_INVALID_ARGUMENT, "bad arguments");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half* xh = static_cast<const __half*>(x);
+    I8TK_CUDA(cudaMemsetAsync(d_scale, 0, sizeof(float), st));
+    amax_f16_kernel<<<grid_for(n), 256, 0, st>>>(xh, n, d_scale);
+    finalize_scale_kernel<<<1, 1, 0, st>>>(d_scale);
+    quant_tensor_f16_kernel<<<grid_for(n), 256, 0, st>>>(xh, q, n, d_scale);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
+
+extern "C" int i8tk_dequantize_int8_to_fp16(const int8_t* q, void* out, float scale, int64_t n,
+                                            i8tk_stream_t stream) {
+    I8TK_REQUIRE(q && out && n > 0, I8TK_ERR_INVALID_ARGUMENT, "bad arguments");
+    dequant_tensor_kernel<<<grid_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        q, static_cast<__half*>(out), n, scale);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
