@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the INT8-KV decode-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  Metric: decode-attention KV-read GB/s, i.e. the int8 K
+and V bytes (2*B*H*S*D per step, the reference's own definition in
+bench/bench_attn_decode.py:82) divided by the step time.
+
+Workload at every N: per GPU, B=32 H=12 D=64 ctx=32768 (the serving-scale
+configuration, 1.6 GB of int8 KV per step -- far larger than the 126 MB L2, so
+no cache flush is needed between steps).  With N > 1 every rank owns its own
+(batch, head) shard of an N-times larger batch and there is no collective in
+the data path (weak scaling); the step time is the max over ranks.
+
+Synthetic data: q fp16 ~ N(0,1), K/V fp32 ~ N(0,1), quantised per token on the
+device with the library's own quantiser, seed 0.
+
+  value     : steps timed back to back with CUDA events, inputs resident in HBM
+  e2e       : the same call with every input copied from pinned host memory and
+              the fp16 result copied back inside the timed region
+  roofline  : the streaming kernel alone (events recorded around it inside the
+              library), against the measured HBM copy rate
+  cpu_baseline / --impl reference : the reference's CPU torch path
+              (dequantise + fp32 SDPA), restated in oracle/torch_cpu.py, on a
+              bounded sample of (b,h) rows of the same workload
+"""
+import argparse
+import ctypes
+import importlib
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B, H, D, S = 32, 12, 64, 32768
+WORKLOAD = f"int8kv_decode_attention B{B} H{H} D{D} ctx{S} per GPU, fp16 out"
+METRIC = "decode_attn_kv_read_GBps"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def kv_bytes(b, h, s, d):
+    return 2 * b * h * s * d
+
+
+def measured_hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) in a thread."""
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join(timeout=2)
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_reference_rate(seconds_budget=12.0, rows=24):
+    """Time the reference's CPU path on `rows` (b,h) rows of the workload.
+
+    Returns (GB/s of int8 K+V bytes, threads, description).
+    """
+    import torch
+    from oracle import torch_cpu
+    torch.manual_seed(0)
+    q = torch.randn(1, rows, D).half()
+    K = torch.randn(1, rows, S, D)
+    V = torch.randn(1, rows, S, D)
+    Qi, sQ = torch_cpu.quantize_per_token_cpu(q)
+    Ki, sK = torch_cpu.quantize_per_token_cpu(K)
+    Vi, sV = torch_cpu.quantize_per_token_cpu(V)
+    del K, V
+    torch_cpu.decode_attention_cpu(Qi, Ki, Vi, sQ, sK, sV)      # warm-up
+    times = []
+    t_end = time.perf_counter() + seconds_budget
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 200):
+        t0 = time.perf_counter()
+        torch_cpu.decode_attention_cpu(Qi, Ki, Vi, sQ, sK, sV)
+        times.append(time.perf_counter() - t0)
+    per_iter = sum(times) / len(times)
+    gbs = kv_bytes(1, rows, S, D) / per_iter / 1e9
+    desc = (f"{rows} of the {B * H} (b,h) rows at ctx {S}, D {D}: dequantise + fp32 SDPA "
+            f"(torch CPU), mean of {len(times)} iterations")
+    return gbs, per_iter, torch.get_num_threads(), desc
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    budget = min(20.0, max(2.0, 1.0 * args.steps))
+    gbs, per_iter, threads, desc = cpu_reference_rate(seconds_budget=budget)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_iter * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sampled": desc},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "host": {"cpu_count": os.cpu_count(), "torch_threads": threads, "torch": torch.__version__},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+# Small cases for profiler captures: larger than L2 (126 MB) so DRAM counters
+# mean something, a few hundred MB on the device, a handful of launches.
+PROFILE_CASES = {
+    "decode_d64": (8, 12, 64, 16384),      # 201 MB of int8 K+V
+    "decode_d128": (8, 8, 128, 8192),      # 134 MB
+}
+
+
+def run_profile_case(name):
+    import torch
+    pkg = importlib.import_module("int8-transformer-kernels_b200")
+    ext = pkg.int8_ext
+    b, h, d, s = PROFILE_CASES[name]
+    args = make_inputs(torch, ext, b, h, s, d)
+    for _ in range(5):
+        out = ext.int8_decode_attention_forward(*args)
+    torch.cuda.synchronize()
+    print(f"profile case {name}: B{b} H{h} D{d} ctx{s}, K+V bytes per launch {kv_bytes(b, h, s, d)}, "
+          f"plan {pkg.cabi.decode_plan(b * h, s, d)}, checksum {float(out.float().sum()):.4f}")
+
+
+def make_inputs(torch, ext, b, h, s, d, outliers=False, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(b, h, d, device="cuda", dtype=torch.float16, generator=g)
+    Qi, sQ = ext.quantize_per_token(q)
+    out = [Qi, None, None, sQ, None, None]
+    for idx in (1, 2):
+        x = torch.randn(b, h, s, d, device="cuda", generator=g)
+        if outliers:
+            ch = torch.randperm(d, device="cuda", generator=g)[: max(1, int(0.01 * d))]
+            x[..., ch] *= 20.0
+        xi, sx = ext.quantize_per_token(x)
+        del x
+        out[idx], out[idx + 3] = xi, sx
+    torch.cuda.synchronize()
+    return out
+
+
+def timed_steps(torch, fn, steps, warmup, barrier=None):
+    for _ in range(warmup):
+        fn()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3      # seconds
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the sweep over the other configurations")
+    ap.add_argument("--profile-case", default=None, choices=sorted(PROFILE_CASES),
+                    help="run a few launches of one small case and exit (for ncu captures)")
+    args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    distributed = world > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    pkg = importlib.import_module("int8-transformer-kernels_b200")
+    ext = pkg.int8_ext
+    cabi = pkg.cabi
+    lib = cabi.load()
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+
+    sampler = ClockSampler(local_rank)
+    Qi, Ki, Vi, sQ, sK, sV = make_inputs(torch, ext, B, H, S, D, seed=rank)
+    step_bytes = kv_bytes(B, H, S, D)
+
+    def step():
+        return ext.int8_decode_attention_forward(Qi, Ki, Vi, sQ, sK, sV)
+
+    # ---- value: K steps back to back, inputs resident ---------------------------------
+    sampler.start()
+    elapsed = timed_steps(torch, step, args.steps, args.warmup, barrier)
+    if distributed:
+        t = torch.tensor([elapsed], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed = float(t.item())
+    value = world * step_bytes * args.steps / elapsed / 1e9
+
+    # ---- roofline: the streaming kernel alone, events recorded around it -------------
+    nsplit, chunk = cabi.decode_plan(B * H, S, D)
+    BH = B * H
+    wbytes = lib.i8tk_decode_workspace_bytes(BH, S, D)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device="cuda")
+    out = torch.empty(B, H, D, dtype=torch.float16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    n_prof = max(args.steps, 20)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(n_prof)]
+    have_probe = hasattr(lib, "i8tk_decode_set_probe_events")
+    kernel_s = None
+    if have_probe:
+        lib.i8tk_decode_set_probe_events.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        lib.i8tk_decode_set_probe_events.restype = ctypes.c_int
+        for a, b_ in ev:
+            # events must exist before their handles are read
+            a.record(); b_.record()
+        torch.cuda.synchronize()
+        t_until = time.perf_counter() + 1.0
+        total, count = 0.0, 0
+        while count < n_prof or time.perf_counter() < t_until:
+            a, b_ = ev[count % n_prof]
+            lib.i8tk_decode_set_probe_events(a.cuda_event, b_.cuda_event)
+            cabi.check(lib.i8tk_decode_attention_forward(
+                Qi.data_ptr(), Ki.data_ptr(), Vi.data_ptr(), out.data_ptr(), sQ.data_ptr(),
+                sK.data_ptr(), sV.data_ptr(), BH, S, D, ws.data_ptr(), wbytes, stream))
+            lib.i8tk_decode_set_probe_events(None, None)
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b_) / 1e3
+            count += 1
+        kernel_s = total / count
+    clocks = sampler.stop()
+
+    # ---- e2e: host buffers, H2D + call + D2H inside the timed region -----------------
+    host = [t.cpu().pin_memory() for t in (Qi, Ki, Vi, sQ, sK, sV)]
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    out_host = torch.empty(B, H, D, dtype=torch.float16).pin_memory()
+    d2h = out_host.numel() * out_host.element_size()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        dev = [t.to("cuda", non_blocking=True) for t in host]
+        o = ext.int8_decode_attention_forward(*dev)
+        out_host.copy_(o, non_blocking=True)
+
+    e2e_elapsed = timed_steps(torch, e2e_step, e2e_steps, 3, barrier)
+    if distributed:
+        t = torch.tensor([e2e_elapsed], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_elapsed = float(t.item())
+    e2e_value = world * step_bytes * e2e_steps / e2e_elapsed / 1e9
+    del host
+
+    peak, peak_kind = measured_hbm_peak()
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 dot, fp32 softmax/accumulate",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_bh": world * B * H, "sharding": "(batch, head) per rank, no collective",
+                   "kv_splits": nsplit, "positions_per_split": chunk,
+                   "l2": "inputs (1.6 GB per step) larger than L2, no flush",
+                   "pct_of_8TBps": 100.0 * value / world / NOMINAL_HBM_GBS},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    if kernel_s is not None:
+        achieved = step_bytes / kernel_s / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": "decode_partial_kernel<64>", "achieved": achieved,
+                            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                            "frac_of_8TBps": achieved / NOMINAL_HBM_GBS,
+                            "algorithmic_bytes_per_launch": step_bytes,
+                            "us_per_launch": kernel_s * 1e6, "traffic": None}
+    prof = os.path.join(ROOT, "profiles", "decode_partial_d64_traffic.json")
+    if "roofline" in line and os.path.exists(prof):
+        try:
+            with open(prof) as f:
+                line["roofline"]["traffic"] = json.load(f).get("traffic_bytes_per_launch_at_bench_size")
+        except Exception:
+            pass
+
+    if rank == 0 and world == 1:
+        gbs, per_iter, threads, desc = cpu_reference_rate(seconds_budget=10.0)
+        line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
+
+    if not args.no_extras:
+        line["sweep"] = sweep(torch, ext, cabi, world, rank, barrier, dist if distributed else None)
+
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+def sweep(torch, ext, cabi, world, rank, barrier, dist):
+    """Other configurations, device-timed, reported beside the headline."""
+    res = []
+    cases = [("cfg0 B1 H12 D64 ctx1024", 1, 12, 64, 1024, False, 200),
+             ("cfg1 B32 H12 D64 ctx4096", 32, 12, 64, 4096, False, 100),
+             ("cfg1 B32 H12 D64 ctx8192", 32, 12, 64, 8192, False, 100),
+             ("cfg1 B32 H12 D64 ctx16384", 32, 12, 64, 16384, False, 50)]
+    if world == 1:
+        cases.append(("cfg2 B64 H32 D128 ctx8192 (1 GPU)", 64, 32, 128, 8192, True, 20))
+    else:
+        # config 2 strong-scaled: the 2048 (b,h) rows split evenly over the ranks
+        cases.append((f"cfg2 B64 H32 D128 ctx8192 sharded over {world} GPUs", 64 // world, 32, 128, 8192, True, 20))
+    for name, b, h, d, s, outl, steps in cases:
+        args = make_inputs(torch, ext, b, h, s, d, outliers=outl, seed=rank)
+        el = timed_steps(torch, lambda: ext.int8_decode_attention_forward(*args), steps, 5, barrier)
+        if dist is not None:
+            t = torch.tensor([el], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            el = float(t.item())
+        mult = world
+        gbs = mult * kv_bytes(b, h, s, d) * steps / el / 1e9
+        res.append({"workload": name, "us_per_step": el / steps * 1e6, "GBps": gbs,
+                    "pct_of_8TBps_per_gpu": 100.0 * gbs / world / NOMINAL_HBM_GBS,
+                    "l2_resident": kv_bytes(b, h, s, d) < 100e6})
+        del args
+        torch.cuda.empty_cache()
+    return res
+
+
+if __name__ == "__main__":
+    main()

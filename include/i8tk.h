@@ -61,8 +61,8 @@ int i8tk_quantize_per_token_f16(const void* x_f16, int8_t* q, float* scales,
 /* Per-tensor FP16 -> INT8 with a dynamically computed scale, and the inverse.
  * Replaces quantize_fp16_to_int8 / dequantize_int8_to_fp16
  * (kernels/int8_common.cuh:54-59, kernels/quant_utils.cu:57-77).
- * d_scale (device float[1]) receives absmax/127; codes = clamp(rne(x/scale)).
- * amax_scratch: device float[1] used for the reduction. */
+ * d_scale (device float[1]) receives absmax/127 (it is also the cell the
+ * absmax reduction runs in); codes = clamp(rne(x/scale), -128, 127). */
 int i8tk_quantize_fp16_to_int8(const void* x_f16, int8_t* q, float* d_scale,
                                int64_t n, i8tk_stream_t stream);
 int i8tk_dequantize_int8_to_fp16(const int8_t* q, void* out_f16, float scale,
@@ -109,6 +109,12 @@ int i8tk_decode_combine_partials(const float* parts, int nparts, int BH, int hea
 
 /* Floats per (b,h) row of a partial: head_dim + 4. */
 int i8tk_decode_partial_stride(int head_dim);
+
+/* Measurement hook (no counterpart in the reference): two cudaEvent_t handles
+ * that the decode calls made afterwards BY THIS THREAD record on their stream
+ * immediately before and after the streaming (pass 1) kernel, so a benchmark
+ * can time that kernel apart from the merge kernel.  Pass NULL, NULL to stop. */
+int i8tk_decode_set_probe_events(void* start_event, void* stop_event);
 
 /* Describes how a call would be split (for tests and tuning): writes the
  * number of KV splits per (b,h) and the positions per split. */

@@ -81,6 +81,23 @@ __device__ __forceinline__ void fma_i8x4(float* acc, uint32_t biased, float w) {
     acc[3] = fmaf(w, f3, acc[3]);
 }
 
+// Variant without the subtraction: byte j is moved into the low byte of an
+// otherwise zero word, which read as fp32 is the denormal u * 2^-149.  FFMA
+// takes denormal operands at full rate, the product with a weight pre-scaled
+// by 2^kDenormShift is exact, and the +128 bias of u is removed once per unit
+// from the running sum of weights.
+constexpr int kDenormShift = 100;
+__device__ __forceinline__ void fma_u8x4_denorm(float* acc, uint32_t biased, float w_scaled) {
+    const float f0 = __uint_as_float(biased & 0xffu);
+    const float f1 = __uint_as_float(prmt(biased, 0u, 0x4441u));
+    const float f2 = __uint_as_float(prmt(biased, 0u, 0x4442u));
+    const float f3 = __uint_as_float(biased >> 24);
+    acc[0] = fmaf(w_scaled, f0, acc[0]);
+    acc[1] = fmaf(w_scaled, f1, acc[1]);
+    acc[2] = fmaf(w_scaled, f2, acc[2]);
+    acc[3] = fmaf(w_scaled, f3, acc[3]);
+}
+
 // Reduce-scatter of LPR partial dots over the LPR lanes that share a row set:
 // on return lane c of the group holds the full dot of position index k == c.
 template <int LPR>
@@ -139,7 +156,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Pass 1: one warp scans KV positions [sp*chunk, min(S,(sp+1)*chunk)) of one
 // (b,h) and leaves an unnormalised online-softmax row.
 // ---------------------------------------------------------------------------
-template <int D>
+template <int D, int VMODE>
 __global__ void __launch_bounds__(kWarps * 32)
 decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K,
                       const int8_t* __restrict__ V, const float* __restrict__ sQ,
@@ -210,6 +227,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
     if (kTile + own < n) { sk1 = sKb[kTile + own]; sv1 = sVb[kTile + own]; }
 
     float m = -INFINITY, l = 0.f;
+    float wsum = 0.f;                               // VMODE 1: sum of weights of this lane's rows
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
@@ -244,6 +262,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         if (m_new > m) {                            // warp-uniform
             const float corr = ex2_approx(m - m_new);
             l *= corr;
+            wsum *= corr;
 #pragma unroll
             for (int i = 0; i < 16; ++i) acc[i] *= corr;
             m = m_new;
@@ -257,10 +276,19 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         for (int k = 0; k < LPR; ++k) {
             const float wk = __shfl_sync(0xffffffffu, w, (lane & ~(LPR - 1)) | k);
             const int4 vw = Vt[(g + RPP * k) * LPR + c];
-            fma_i8x4(acc + 0, (uint32_t)vw.x ^ 0x80808080u, wk);
-            fma_i8x4(acc + 4, (uint32_t)vw.y ^ 0x80808080u, wk);
-            fma_i8x4(acc + 8, (uint32_t)vw.z ^ 0x80808080u, wk);
-            fma_i8x4(acc + 12, (uint32_t)vw.w ^ 0x80808080u, wk);
+            if constexpr (VMODE == 0) {
+                fma_i8x4(acc + 0, (uint32_t)vw.x ^ 0x80808080u, wk);
+                fma_i8x4(acc + 4, (uint32_t)vw.y ^ 0x80808080u, wk);
+                fma_i8x4(acc + 8, (uint32_t)vw.z ^ 0x80808080u, wk);
+                fma_i8x4(acc + 12, (uint32_t)vw.w ^ 0x80808080u, wk);
+            } else {
+                wsum += wk;
+                const float ws = wk * __uint_as_float((127u + kDenormShift) << 23);
+                fma_u8x4_denorm(acc + 0, (uint32_t)vw.x ^ 0x80808080u, ws);
+                fma_u8x4_denorm(acc + 4, (uint32_t)vw.y ^ 0x80808080u, ws);
+                fma_u8x4_denorm(acc + 8, (uint32_t)vw.z ^ 0x80808080u, ws);
+                fma_u8x4_denorm(acc + 12, (uint32_t)vw.w ^ 0x80808080u, ws);
+            }
         }
 
         // every lane is done reading this stage: refill it
@@ -284,6 +312,15 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         for (int i = 0; i < 16; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
     }
     l = warp_sum(l);
+    if constexpr (VMODE == 1) {
+        // rows were spread over the row groups; lanes of one group saw the same weights
+#pragma unroll
+        for (int o = LPR; o < 32; o <<= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+        const float unscale = __uint_as_float((127u + 149u - kDenormShift) << 23);
+        const float bias = 128.0f * wsum;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = fmaf(acc[i], unscale, -bias);
+    }
 
     if (mode == kToFinalF16) {
         if (g == 0) {
@@ -381,6 +418,12 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nsplit,
 // ---------------------------------------------------------------------------
 struct Plan { int nsplit; int chunk; };
 
+// Optional timing probe: events recorded on the launch stream immediately
+// before and after the streaming (pass 1) kernel of the next calls made by
+// this thread.
+thread_local cudaEvent_t g_probe_start = nullptr;
+thread_local cudaEvent_t g_probe_stop = nullptr;
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;
@@ -399,10 +442,8 @@ int sm_count() {
 // fill/drain overhead; the grid runs in ceil(units/slots) rounds.  Chunks are
 // whole tiles so every bulk copy starts on a row boundary.
 Plan make_plan(int BH, int S, int D, int sms) {
-    static const int forced = [] {
-        const char* e = getenv("I8TK_DECODE_NSPLIT");
-        return e ? atoi(e) : 0;
-    }();
+    const char* e = getenv("I8TK_DECODE_NSPLIT");
+    const int forced = e ? atoi(e) : 0;
     const int ctas_per_sm = (D == 64) ? DecodeTraits<64>::CTAS_PER_SM : DecodeTraits<128>::CTAS_PER_SM;
     const long long slots = (long long)sms * ctas_per_sm * kWarps;
     const int tiles = (S + kTile - 1) / kTile;
@@ -429,16 +470,16 @@ size_t workspace_bytes(int BH, int S, int D) {
     return 256 + (size_t)BH * p.nsplit * (D + 4) * sizeof(float);
 }
 
-template <int D>
-int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, float* part,
+template <int D, int VMODE>
+int launch_decode_v(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, float* part,
                   const float* sQ, const float* sK, const float* sV, int BH, int S,
                   void* workspace, size_t wbytes, cudaStream_t stream) {
     using T = DecodeTraits<D>;
-    static bool attr_done[64] = {false};
+    static bool attr_done[64] = {false};   // per template instance
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(decode_partial_kernel<D>,
+        I8TK_CUDA(cudaFuncSetAttribute(decode_partial_kernel<D, VMODE>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
         attr_done[dev] = true;
     }
@@ -457,16 +498,32 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
     const int grid = (units + kWarps - 1) / kWarps;
 
     const bool direct = (p.nsplit == 1 && out != nullptr);
-    decode_partial_kernel<D><<<grid, kWarps * 32, T::SMEM_BYTES, stream>>>(
+    if (g_probe_start) I8TK_CUDA(cudaEventRecord(g_probe_start, stream));
+    decode_partial_kernel<D, VMODE><<<grid, kWarps * 32, T::SMEM_BYTES, stream>>>(
         Q, K, V, sQ, sK, sV, rows, out, S, p.nsplit, p.chunk, units, score_scale_log2,
         direct ? kToFinalF16 : kToScratchRows, status);
     I8TK_CUDA(cudaGetLastError());
+    if (g_probe_stop) I8TK_CUDA(cudaEventRecord(g_probe_stop, stream));
     if (!direct) {
         decode_combine_kernel<D><<<(BH + 3) / 4, 128, 0, stream>>>(
             rows, BH, p.nsplit, (long long)p.nsplit, 1ll, out, part);
         I8TK_CUDA(cudaGetLastError());
     }
     return I8TK_OK;
+}
+
+int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
+template <int D>
+int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, float* part,
+                  const float* sQ, const float* sK, const float* sV, int BH, int S,
+                  void* workspace, size_t wbytes, cudaStream_t stream) {
+    if (env_int("I8TK_DECODE_VMODE", 0) == 1)
+        return launch_decode_v<D, 1>(Q, K, V, out, part, sQ, sK, sV, BH, S, workspace, wbytes, stream);
+    return launch_decode_v<D, 0>(Q, K, V, out, part, sQ, sK, sV, BH, S, workspace, wbytes, stream);
 }
 
 int check_decode_args(const void* Q, const void* K, const void* V, const void* o,
@@ -494,6 +551,12 @@ extern "C" size_t i8tk_decode_workspace_bytes(int BH, int S, int head_dim) {
 }
 
 extern "C" int i8tk_decode_partial_stride(int head_dim) { return head_dim + 4; }
+
+extern "C" int i8tk_decode_set_probe_events(void* start_event, void* stop_event) {
+    g_probe_start = static_cast<cudaEvent_t>(start_event);
+    g_probe_stop = static_cast<cudaEvent_t>(stop_event);
+    return I8TK_OK;
+}
 
 extern "C" int i8tk_decode_plan(int BH, int S, int head_dim, int* nsplit, int* chunk) {
     I8TK_REQUIRE(BH > 0 && S > 0 && nsplit && chunk, I8TK_ERR_INVALID_ARGUMENT, "bad plan arguments");
