@@ -281,7 +281,7 @@ def main():
     value = world * step_bytes * args.steps / elapsed / 1e9
 
     # ---- roofline: the streaming kernel alone, events recorded around it -------------
-    nsplit, chunk = cabi.decode_plan(B * H, S, D)
+    plan_warps, plan_tiles = cabi.decode_plan(B * H, S, D)
     BH = B * H
     wbytes = lib.i8tk_decode_workspace_bytes(BH, S, D)
     ws = torch.empty(wbytes, dtype=torch.uint8, device="cuda")
@@ -341,7 +341,7 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 dot, fp32 softmax/accumulate",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "global_bh": world * B * H, "sharding": "(batch, head) per rank, no collective",
-                   "kv_splits": nsplit, "positions_per_split": chunk,
+                   "persistent_ctas": plan_warps, "kv_tiles_per_cta": plan_tiles,
                    "l2": "inputs (1.6 GB per step) larger than L2, no flush",
                    "pct_of_8TBps": 100.0 * value / world / NOMINAL_HBM_GBS},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

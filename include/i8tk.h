@@ -116,9 +116,9 @@ int i8tk_decode_partial_stride(int head_dim);
  * can time that kernel apart from the merge kernel.  Pass NULL, NULL to stop. */
 int i8tk_decode_set_probe_events(void* start_event, void* stop_event);
 
-/* Describes how a call would be split (for tests and tuning): writes the
- * number of KV splits per (b,h) and the positions per split. */
-int i8tk_decode_plan(int BH, int S, int head_dim, int* nsplit, int* chunk);
+/* Describes how a call would be divided (for tests and tuning): the number of
+ * persistent CTAs launched and the 128-position KV tiles each one scans. */
+int i8tk_decode_plan(int BH, int S, int head_dim, int* nctas, int* tiles_per_cta);
 
 /* ------------------------------------------------------------------------
  * Fused INT8 MLP:  out = requant( (requant(GELU((x.W1)*sx*sW1 + b1))) . W2 * sh * sW2 )

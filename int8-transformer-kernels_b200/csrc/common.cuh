@@ -69,21 +69,26 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One poll of the barrier phase.  `suspend_ns` lets the hardware park the
+// thread until the phase completes or that much time has passed, instead of
+// burning issue slots in a spin loop.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity,
+                                              uint32_t suspend_ns = 20000u) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(suspend_ns)
         : "memory");
     return ok != 0;
 }
 
-// Bounded wait: returns false (after `limit` polls) instead of spinning forever.
+// Bounded wait: returns false (after `limit` polls, each parked for at most
+// the suspend hint -- about a second in total) instead of waiting forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  uint32_t limit = (1u << 24)) {
+                                                  uint32_t limit = (1u << 16)) {
     for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;

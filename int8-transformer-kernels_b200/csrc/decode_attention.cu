@@ -7,12 +7,17 @@
 //   out     = sum_j softmax(score)_j * sV_j * v_j    (fp32 accumulate, fp16 out)
 // -- different machine mapping:
 //
-// * One warp owns one work unit (b*h, KV split) and a private ring of shared
-//   memory stages.  K and V tiles of 32 positions are streamed HBM -> shared
-//   memory by 1-D bulk async copies (the TMA engine) that complete on an
-//   mbarrier; several tiles per warp are always in flight, so the bytes in
-//   flight per SM (up to ~190 KB) cover HBM3e latency x bandwidth without
-//   needing many resident warps.  No block-level barrier exists anywhere.
+// * The KV cache is cut into tiles of 32 positions; the tiles of all (b,h)
+//   rows form one flat sequence that is divided EVENLY over a single wave of
+//   persistent warps (one resident warp slot each), so every SM streams the
+//   same number of bytes and no warp ever restarts its pipeline.  A warp's
+//   range may cross (b,h) boundaries; it leaves one unnormalised
+//   (m, l, acc[D]) row per (b,h) segment it touched.
+// * Each warp owns a private ring of shared-memory stages.  K, V and the two
+//   scale vectors of a tile are streamed HBM -> shared memory by 1-D bulk
+//   async copies (the TMA engine) that complete on an mbarrier; several tiles
+//   per warp are always in flight, so the bytes in flight per SM (~200 KB)
+//   cover HBM3e latency x bandwidth.  No block-level barrier exists anywhere.
 // * A tile row (64 or 128 int8) is split into 16-byte chunks; lane (g, c)
 //   reads chunk c of rows g, g+R, g+2R, ... with 128-bit shared loads that are
 //   bank-conflict free (a quarter-warp reads 128 contiguous bytes).
@@ -24,9 +29,9 @@
 //   byte-permute into the mantissa of 2^23 (full-rate ALU/FMA ops; no I2F).
 // * Softmax runs in log2 units (log2(e) folded into the score scale) with a
 //   running max per warp; the accumulator is rescaled only when the max moves.
-// * Each unit leaves one unnormalised (m, l, acc[D]) row; a small second
-//   kernel merges the rows of a (b,h) by log-sum-exp.  The same row format is
-//   the exchange format of the multi-GPU sequence-sharded path.
+// * A small second kernel merges the rows of a (b,h) by log-sum-exp.  The
+//   same row format is the exchange format of the multi-GPU sequence-sharded
+//   path.
 #include "common.cuh"
 
 #include <cmath>
@@ -35,26 +40,34 @@
 namespace i8tk {
 namespace {
 
-constexpr int kTile = 32;             // KV positions per stage
-constexpr int kWarps = 4;             // work units per CTA
+constexpr int kSub = 32;              // KV positions per warp pass (one per lane)
+constexpr int kConsumers = 4;         // consumer warps per CTA; one more warp feeds the ring
+constexpr int kTile = kSub * kConsumers;   // KV positions per stage: one sub-tile per consumer warp
+constexpr int kThreads = (kConsumers + 1) * 32;
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
 struct DecodeTraits {
     static constexpr int LPR = D / 16;                 // lanes per row (16 B each)
     static constexpr int RPP = 32 / LPR;               // rows per warp pass
-    static constexpr int STAGES = (D == 64) ? 4 : 3;   // ring depth per warp
-    static constexpr int TILE_BYTES = kTile * D;       // one of K or V
-    static constexpr int STAGE_BYTES = 2 * TILE_BYTES; // K tile then V tile
+    static constexpr int STAGES = (D == 64) ? 4 : 3;   // ring depth per CTA
+    static constexpr int TILE_BYTES = kTile * D;       // one of K or V: 8 KB / 16 KB contiguous
+    static constexpr int SCALE_BYTES = kTile * 4;      // one of sK or sV
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES + 2 * SCALE_BYTES;  // K | V | sK | sV
     static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int SMEM_BYTES = kWarps * RING_BYTES + kWarps * STAGES * 8;
+    static constexpr int SMEM_BYTES = RING_BYTES + 2 * STAGES * 8;
     static constexpr int CTAS_PER_SM = (D == 64) ? 3 : 2;
     static constexpr int ROW_FLOATS = D + 4;           // m, l, 0, 0, acc[D]
 };
 
-enum EpilogueMode : int {
-    kToScratchRows = 0,   // (m, l, acc) row per unit, merged by the combine kernel
-    kToFinalF16 = 1,      // nsplit == 1: normalise and write fp16 directly
+// How the flat tile sequence is divided.  CTA c scans flat tiles
+// [c*tpc, min(total, (c+1)*tpc)); flat tile f is tile f % tpb of (b,h) f / tpb.
+struct DecodePlan {
+    int tpb;             // tiles per (b,h) = ceil(S / kTile)
+    int tpc;             // tiles per CTA
+    int nctas;           // CTAs launched
+    int maxseg;          // (b,h) segments a CTA can touch
+    long long total;     // BH * tpb
 };
 
 __device__ __forceinline__ int dot16(const int4& q, const int4& k) {
@@ -65,37 +78,43 @@ __device__ __forceinline__ int dot16(const int4& q, const int4& k) {
     return d;
 }
 
-// acc[0..3] += w * int8x4(word).  The word has been XORed with 0x80808080 so
-// its bytes are u = v + 128 in [0, 255]; prmt drops byte j into the low
-// mantissa of 0x4B000000 (= 2^23), and subtracting 2^23 + 128 recovers v
-// exactly in fp32.
-__device__ __forceinline__ void fma_i8x4(float* acc, uint32_t biased, float w) {
-    constexpr float kMagic = 8388736.0f;  // 2^23 + 128
-    const float f0 = __uint_as_float(prmt(biased, 0x4B000000u, 0x7650u)) - kMagic;
-    const float f1 = __uint_as_float(prmt(biased, 0x4B000000u, 0x7651u)) - kMagic;
-    const float f2 = __uint_as_float(prmt(biased, 0x4B000000u, 0x7652u)) - kMagic;
-    const float f3 = __uint_as_float(prmt(biased, 0x4B000000u, 0x7653u)) - kMagic;
-    acc[0] = fmaf(w, f0, acc[0]);
-    acc[1] = fmaf(w, f1, acc[1]);
-    acc[2] = fmaf(w, f2, acc[2]);
-    acc[3] = fmaf(w, f3, acc[3]);
+// Packed fp32x2 arithmetic (one instruction for two lanes of a register pair).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    float2 t = make_float2(a, b);
+    return *reinterpret_cast<f32x2*>(&t);
+}
+__device__ __forceinline__ float2 unpack2(f32x2 v) { return *reinterpret_cast<float2*>(&v); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
 }
 
-// Variant without the subtraction: byte j is moved into the low byte of an
-// otherwise zero word, which read as fp32 is the denormal u * 2^-149.  FFMA
-// takes denormal operands at full rate, the product with a weight pre-scaled
-// by 2^kDenormShift is exact, and the +128 bias of u is removed once per unit
-// from the running sum of weights.
-constexpr int kDenormShift = 100;
-__device__ __forceinline__ void fma_u8x4_denorm(float* acc, uint32_t biased, float w_scaled) {
-    const float f0 = __uint_as_float(biased & 0xffu);
-    const float f1 = __uint_as_float(prmt(biased, 0u, 0x4441u));
-    const float f2 = __uint_as_float(prmt(biased, 0u, 0x4442u));
-    const float f3 = __uint_as_float(biased >> 24);
-    acc[0] = fmaf(w_scaled, f0, acc[0]);
-    acc[1] = fmaf(w_scaled, f1, acc[1]);
-    acc[2] = fmaf(w_scaled, f2, acc[2]);
-    acc[3] = fmaf(w_scaled, f3, acc[3]);
+// acc[0..1] (four floats) += w * int8x4(word).  The word is XORed with
+// 0x80808080 so its bytes are u = v + 128 in [0, 255]; prmt drops byte j into
+// the low mantissa of 0x4B000000 (= 2^23), and adding -(2^23 + 128) recovers v
+// exactly in fp32.  The add and the FMA are issued as packed fp32x2 pairs.
+__device__ __forceinline__ void fma_i8x4(f32x2* acc, uint32_t raw, f32x2 w2, f32x2 neg_magic2) {
+    const uint32_t b = raw ^ 0x80808080u;
+    f32x2 f01 = pack2(__uint_as_float(prmt(b, 0x4B000000u, 0x7650u)),
+                      __uint_as_float(prmt(b, 0x4B000000u, 0x7651u)));
+    f32x2 f23 = pack2(__uint_as_float(prmt(b, 0x4B000000u, 0x7652u)),
+                      __uint_as_float(prmt(b, 0x4B000000u, 0x7653u)));
+    f01 = add2(f01, neg_magic2);
+    f23 = add2(f23, neg_magic2);
+    acc[0] = fma2(w2, f01, acc[0]);
+    acc[1] = fma2(w2, f23, acc[1]);
 }
 
 // Reduce-scatter of LPR partial dots over the LPR lanes that share a row set:
@@ -141,9 +160,9 @@ __device__ __forceinline__ int reduce_scatter(int (&d)[LPR], int c) {
 }
 
 __device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -153,218 +172,244 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ---------------------------------------------------------------------------
-// Pass 1: one warp scans KV positions [sp*chunk, min(S,(sp+1)*chunk)) of one
-// (b,h) and leaves an unnormalised online-softmax row.
+// Pass 1: persistent CTAs over the flat tile sequence.  Warp kConsumers feeds
+// the ring (one lane issues the bulk copies); warps 0..kConsumers-1 each scan
+// one 32-position sub-tile of every stage and keep their own running
+// (m, l, acc).  full[s]: copies of stage s landed; empty[s]: all consumers are
+// done with stage s.
+// SCALES_BULK: the per-position scales ride the bulk copies (needs S % 4 == 0
+// and 16-byte aligned scale arrays); otherwise the owning lane loads them.
 // ---------------------------------------------------------------------------
-template <int D, int VMODE>
-__global__ void __launch_bounds__(kWarps * 32)
+template <int D, bool SCALES_BULK>
+__global__ void __launch_bounds__(kThreads)
 decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K,
                       const int8_t* __restrict__ V, const float* __restrict__ sQ,
                       const float* __restrict__ sK, const float* __restrict__ sV,
-                      float* __restrict__ rows,     // [units, D+4] (mode 0)
-                      __half* __restrict__ out,     // [BH, D]      (mode 1)
-                      int S, int nsplit, int chunk, int units, float score_scale_log2,
-                      int mode, uint32_t* __restrict__ status) {
+                      float* __restrict__ rows,     // [nctas * maxseg * kConsumers, D+4]
+                      int S, DecodePlan plan, float score_scale_log2,
+                      uint32_t* __restrict__ status) {
     using T = DecodeTraits<D>;
     constexpr int LPR = T::LPR, RPP = T::RPP, STAGES = T::STAGES;
 
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int unit = blockIdx.x * kWarps + warp;
-    if (unit >= units) return;
+    const long long f0 = (long long)blockIdx.x * plan.tpc;
+    if (f0 >= plan.total) return;
+    const int ntl = (int)min((long long)plan.tpc, plan.total - f0);   // tiles of this CTA
+    const int tpb = plan.tpb;
 
-    unsigned char* ring = smem + warp * T::RING_BYTES;
-    const uint32_t ring_s = smem_u32(ring);
-    const uint32_t bar0 = smem_u32(smem + kWarps * T::RING_BYTES) + warp * STAGES * 8;
+    const uint32_t ring_s = smem_u32(smem);
+    const uint32_t full0 = ring_s + T::RING_BYTES;
+    const uint32_t empty0 = full0 + STAGES * 8;
 
-    const int bh = unit / nsplit;
-    const int sp = unit - bh * nsplit;
-    const int j0 = sp * chunk;
-    const int n = min(S, j0 + chunk) - j0;          // positions of this unit
-    const int ntiles = n > 0 ? (n + kTile - 1) / kTile : 0;
-
-    const int c = lane % LPR;                       // 16-byte chunk of a row
-    const int g = lane / LPR;                       // row within a pass
-    const int own = g + RPP * c;                    // position in the tile whose softmax this lane runs
-
-    const size_t row0 = (size_t)bh * S + j0;
-    const int8_t* Kb = K + row0 * D;
-    const int8_t* Vb = V + row0 * D;
-    const float* sKb = sK + row0;
-    const float* sVb = sV + row0;
-
-    if (lane == 0) {
+    if (threadIdx.x == 0) {
 #pragma unroll
-        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, kConsumers);
+        }
         fence_mbar_init();
     }
-    __syncwarp();
+    __syncthreads();
 
-    auto issue = [&](int t) {
-        // lane 0 only: start the K and V copies of tile t into stage t % STAGES
-        const int st = t % STAGES;
-        const int nrow = min(kTile, n - t * kTile);
-        const uint32_t bytes = (uint32_t)nrow * D;
-        const uint32_t bar = bar0 + 8 * st;
-        const uint32_t dst = ring_s + st * T::STAGE_BYTES;
-        mbar_expect_tx(bar, 2 * bytes);
-        bulk_g2s(dst, Kb + (size_t)t * T::TILE_BYTES, bytes, bar);
-        bulk_g2s(dst + T::TILE_BYTES, Vb + (size_t)t * T::TILE_BYTES, bytes, bar);
-    };
+    const int bh0 = (int)(f0 / tpb);
+    const int tb0 = (int)(f0 - (long long)bh0 * tpb);
 
-    if (lane == 0) {
-        const int pre = min(STAGES, ntiles);
-        for (int t = 0; t < pre; ++t) issue(t);
-    }
-
-    const int4 q4 = *reinterpret_cast<const int4*>(Q + (size_t)bh * D + c * 16);
-    const float qs = sQ[bh] * score_scale_log2;
-
-    // per-position scales of the owned position, fetched two tiles ahead
-    float sk0 = 0.f, sv0 = 0.f, sk1 = 0.f, sv1 = 0.f;
-    if (own < n) { sk0 = sKb[own]; sv0 = sVb[own]; }
-    if (kTile + own < n) { sk1 = sKb[kTile + own]; sv1 = sVb[kTile + own]; }
-
-    float m = -INFINITY, l = 0.f;
-    float wsum = 0.f;                               // VMODE 1: sum of weights of this lane's rows
-    float acc[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-
-    bool ok = true;
-    for (int t = 0; t < ntiles; ++t) {
-        float sk2 = 0.f, sv2 = 0.f;
-        {
-            const int p2 = (t + 2) * kTile + own;
-            if (p2 < n) { sk2 = sKb[p2]; sv2 = sVb[p2]; }
-        }
-        const int st = t % STAGES;
-        const bool got = mbar_wait_bounded(bar0 + 8 * st, (t / STAGES) & 1);
-        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-
-        const int4* Kt = reinterpret_cast<const int4*>(ring + st * T::STAGE_BYTES);
-        const int4* Vt = reinterpret_cast<const int4*>(ring + st * T::STAGE_BYTES + T::TILE_BYTES);
-
-        // ---- QK^T partial dots, then one full dot per lane ----------------
-        int d[LPR];
-#pragma unroll
-        for (int k = 0; k < LPR; ++k) {
-            const int4 kw = Kt[(g + RPP * k) * LPR + c];
-            d[k] = dot16(q4, kw);
-        }
-        const int tot = reduce_scatter<LPR>(d, c);
-
-        // ---- online softmax, log2 units, one position per lane -------------
-        const bool valid = (t * kTile + own) < n;
-        const float s = valid ? (float)tot * (qs * sk0) : -INFINITY;
-        const float m_new = fmaxf(m, warp_max(s));
-        if (m_new > m) {                            // warp-uniform
-            const float corr = ex2_approx(m - m_new);
-            l *= corr;
-            wsum *= corr;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] *= corr;
-            m = m_new;
-        }
-        const float p = ex2_approx(s - m);
-        l += p;
-        const float w = p * sv0;
-
-        // ---- PV: acc[16 dims of chunk c] += w_row * v_row -------------------
-#pragma unroll
-        for (int k = 0; k < LPR; ++k) {
-            const float wk = __shfl_sync(0xffffffffu, w, (lane & ~(LPR - 1)) | k);
-            const int4 vw = Vt[(g + RPP * k) * LPR + c];
-            if constexpr (VMODE == 0) {
-                fma_i8x4(acc + 0, (uint32_t)vw.x ^ 0x80808080u, wk);
-                fma_i8x4(acc + 4, (uint32_t)vw.y ^ 0x80808080u, wk);
-                fma_i8x4(acc + 8, (uint32_t)vw.z ^ 0x80808080u, wk);
-                fma_i8x4(acc + 12, (uint32_t)vw.w ^ 0x80808080u, wk);
-            } else {
-                wsum += wk;
-                const float ws = wk * __uint_as_float((127u + kDenormShift) << 23);
-                fma_u8x4_denorm(acc + 0, (uint32_t)vw.x ^ 0x80808080u, ws);
-                fma_u8x4_denorm(acc + 4, (uint32_t)vw.y ^ 0x80808080u, ws);
-                fma_u8x4_denorm(acc + 8, (uint32_t)vw.z ^ 0x80808080u, ws);
-                fma_u8x4_denorm(acc + 12, (uint32_t)vw.w ^ 0x80808080u, ws);
+    if (warp == kConsumers) {
+        // ---- producer: one lane walks the tile list and keeps the ring full ----
+        if (lane != 0) return;
+        int p_bh = bh0, p_tb = tb0;
+        for (int i = 0; i < ntl; ++i) {
+            const int st = i % STAGES;
+            if (i >= STAGES) {
+                if (!mbar_wait_bounded(empty0 + 8 * st, ((i / STAGES) - 1) & 1)) {
+                    atomicExch(status, kDeviceTimeoutMagic);
+                    return;
+                }
             }
+            const int pos0 = p_tb * kTile;
+            const int nrow = min(kTile, S - pos0);
+            const size_t row = (size_t)p_bh * S + pos0;
+            const uint32_t kv_bytes = (uint32_t)nrow * D;
+            const uint32_t bar = full0 + 8 * st;
+            const uint32_t dst = ring_s + st * T::STAGE_BYTES;
+            if constexpr (SCALES_BULK) {
+                const uint32_t sc_bytes = (uint32_t)nrow * 4;       // multiple of 16: S % 4 == 0
+                mbar_expect_tx(bar, 2 * kv_bytes + 2 * sc_bytes);
+                bulk_g2s(dst + 2 * T::TILE_BYTES, sK + row, sc_bytes, bar);
+                bulk_g2s(dst + 2 * T::TILE_BYTES + T::SCALE_BYTES, sV + row, sc_bytes, bar);
+            } else {
+                mbar_expect_tx(bar, 2 * kv_bytes);
+            }
+            bulk_g2s(dst, K + row * D, kv_bytes, bar);
+            bulk_g2s(dst + T::TILE_BYTES, V + row * D, kv_bytes, bar);
+            if (++p_tb == tpb) { p_tb = 0; ++p_bh; }
         }
-
-        // every lane is done reading this stage: refill it
-        __syncwarp();
-        if (lane == 0 && t + STAGES < ntiles) {
-            fence_proxy_async();
-            issue(t + STAGES);
-        }
-        sk0 = sk1; sv0 = sv1; sk1 = sk2; sv1 = sv2;
-    }
-
-    if (!ok) {
-        if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
         return;
     }
 
-    // ---- fold the row groups; lanes g == 0 hold the chunk's 16 sums --------
-#pragma unroll
-    for (int o = LPR; o < 32; o <<= 1) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
-    }
-    l = warp_sum(l);
-    if constexpr (VMODE == 1) {
-        // rows were spread over the row groups; lanes of one group saw the same weights
-#pragma unroll
-        for (int o = LPR; o < 32; o <<= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
-        const float unscale = __uint_as_float((127u + 149u - kDenormShift) << 23);
-        const float bias = 128.0f * wsum;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] = fmaf(acc[i], unscale, -bias);
-    }
+    // ---- consumers ------------------------------------------------------------
+    const int c = lane % LPR;                       // 16-byte chunk of a row
+    const int g = lane / LPR;                       // row within a pass
+    const int own = warp * kSub + g + RPP * c;      // position in the tile whose softmax this lane runs
+    const f32x2 neg_magic2 = pack2(-8388736.0f, -8388736.0f);   // -(2^23 + 128)
 
-    if (mode == kToFinalF16) {
-        if (g == 0) {
-            const float inv = 1.0f / l;
-            __half2 h[8];
+    int c_bh = bh0, c_tb = tb0;
+    int i = 0;                                      // tiles of this CTA consumed so far
+    for (int seg = 0; i < ntl; ++seg) {
+        // ---- one (b,h) segment: tiles [c_tb, c_tb + seg_tiles) of row c_bh ----
+        const int seg_tiles = min(ntl - i, tpb - c_tb);
+        const int4 q4 = *reinterpret_cast<const int4*>(Q + (size_t)c_bh * D + c * 16);
+        const float qs = sQ[c_bh] * score_scale_log2;
+        const float* sKb = sK + (size_t)c_bh * S;
+        const float* sVb = sV + (size_t)c_bh * S;
+        float m = -INFINITY, l = 0.f;
+        f32x2 acc[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                h[i] = __floats2half2_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv);
-            int4* dst = reinterpret_cast<int4*>(out + (size_t)bh * D + c * 16);
-            dst[0] = *reinterpret_cast<int4*>(&h[0]);
-            dst[1] = *reinterpret_cast<int4*>(&h[4]);
+        for (int k = 0; k < 8; ++k) acc[k] = 0ull;
+
+        float sk_next = 0.f, sv_next = 0.f;         // scales when they do not ride the bulk copies
+        if constexpr (!SCALES_BULK) {
+            const int pos = c_tb * kTile + own;
+            if (pos < S) { sk_next = sKb[pos]; sv_next = sVb[pos]; }
         }
-    } else {
-        float* row = rows + (size_t)unit * T::ROW_FLOATS;
-        if (lane == 0) *reinterpret_cast<float4*>(row) = make_float4(m, l, 0.f, 0.f);
+
+        for (int t = 0; t < seg_tiles; ++t, ++i) {
+            const int pos0 = (c_tb + t) * kTile;
+            const bool valid = (pos0 + own) < S;
+
+            float sk0 = 0.f, sv0 = 0.f;
+            if constexpr (!SCALES_BULK) {
+                sk0 = sk_next;
+                sv0 = sv_next;
+                const int pos = pos0 + kTile + own;     // next tile of this segment, if any
+                sk_next = 0.f;
+                sv_next = 0.f;
+                if (t + 1 < seg_tiles && pos < S) { sk_next = sKb[pos]; sv_next = sVb[pos]; }
+            }
+
+            const int st = i % STAGES;
+            const bool got = mbar_wait_bounded(full0 + 8 * st, (i / STAGES) & 1);
+            if (!__all_sync(0xffffffffu, got)) {
+                if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
+                return;
+            }
+
+            if (pos0 + warp * kSub < S) {           // this warp's sub-tile has rows (warp-uniform)
+                const unsigned char* stage = smem + st * T::STAGE_BYTES;
+                const int4* Kt = reinterpret_cast<const int4*>(stage + warp * kSub * D);
+                const int4* Vt = reinterpret_cast<const int4*>(stage + T::TILE_BYTES + warp * kSub * D);
+                if constexpr (SCALES_BULK) {
+                    const float* sc = reinterpret_cast<const float*>(stage + 2 * T::TILE_BYTES);
+                    sk0 = valid ? sc[own] : 0.f;
+                    sv0 = valid ? sc[kTile + own] : 0.f;
+                }
+
+                // ---- QK^T partial dots, then one full dot per lane ------------
+                int d[LPR];
+#pragma unroll
+                for (int k = 0; k < LPR; ++k) {
+                    const int4 kw = Kt[(g + RPP * k) * LPR + c];
+                    d[k] = dot16(q4, kw);
+                }
+                const int tot = reduce_scatter<LPR>(d, c);
+
+                // ---- online softmax, log2 units, one position per lane ---------
+                const float s = valid ? (float)tot * (qs * sk0) : -INFINITY;
+                const float m_new = fmaxf(m, warp_max(s));
+                if (m_new > m) {                    // warp-uniform, rare after the first tiles
+                    const float corr = ex2_approx(m - m_new);
+                    const f32x2 corr2 = pack2(corr, corr);
+                    l *= corr;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[k] = mul2(acc[k], corr2);
+                    m = m_new;
+                }
+                const float p = ex2_approx(s - m);
+                l += p;
+                const float wgt = p * sv0;
+
+                // ---- PV: acc[16 dims of chunk c] += w_row * v_row ---------------
+#pragma unroll
+                for (int k = 0; k < LPR; ++k) {
+                    const float wk = __shfl_sync(0xffffffffu, wgt, (lane & ~(LPR - 1)) | k);
+                    const f32x2 w2 = pack2(wk, wk);
+                    const int4 vw = Vt[(g + RPP * k) * LPR + c];
+                    fma_i8x4(acc + 0, (uint32_t)vw.x, w2, neg_magic2);
+                    fma_i8x4(acc + 2, (uint32_t)vw.y, w2, neg_magic2);
+                    fma_i8x4(acc + 4, (uint32_t)vw.z, w2, neg_magic2);
+                    fma_i8x4(acc + 6, (uint32_t)vw.w, w2, neg_magic2);
+                }
+            }
+
+            // every lane of this warp is done reading the stage
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * st);
+        }
+
+        // ---- end of the segment: fold the row groups and emit the row ----------
+        float a[16];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float2 v = unpack2(acc[k]);
+            a[2 * k] = v.x;
+            a[2 * k + 1] = v.y;
+        }
+#pragma unroll
+        for (int o = LPR; o < 32; o <<= 1) {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
+        }
+        const float lsum = warp_sum(l);
+        float* row = rows + (((size_t)blockIdx.x * plan.maxseg + seg) * kConsumers + warp) * T::ROW_FLOATS;
+        if (lane == 0) *reinterpret_cast<float4*>(row) = make_float4(m, lsum, 0.f, 0.f);
         if (g == 0) {
             float4* dst = reinterpret_cast<float4*>(row + 4 + c * 16);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+            for (int k = 0; k < 4; ++k)
+                dst[k] = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
         }
+        c_tb += seg_tiles;
+        if (c_tb == tpb) { c_tb = 0; ++c_bh; }
     }
 }
 
 // ---------------------------------------------------------------------------
-// Pass 2: log-sum-exp merge of the rows of one (b,h).  One warp per (b,h);
-// row (bh, s) lives at rows + (bh*stride_bh + s*stride_s) * (D+4).
+// Pass 2: log-sum-exp merge of the rows of one (b,h).  One warp per (b,h).
+// FLAT: rows were written by the consumer warps of pass 1 (indexed through
+// the plan).  Otherwise: row (s, bh) of a gathered [nparts, BH, D+4] array.
 // Writes either the normalised fp16 output or one merged row.
 // ---------------------------------------------------------------------------
-template <int D>
+template <int D, bool FLAT>
 __global__ void __launch_bounds__(128)
-decode_combine_kernel(const float* __restrict__ rows, int BH, int nsplit,
-                      long long stride_bh, long long stride_s,
+decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, DecodePlan plan,
                       __half* __restrict__ out, float* __restrict__ row_out) {
     constexpr int ROW = D + 4;
     constexpr int DPL = D / 32;
     const int bh = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (bh >= BH) return;
     const int lane = threadIdx.x & 31;
-    const float* base = rows + (size_t)bh * stride_bh * ROW;
+
+    int c_first = 0, n = nparts;
+    if constexpr (FLAT) {
+        const long long fb = (long long)bh * plan.tpb;
+        c_first = (int)(fb / plan.tpc);
+        n = ((int)((fb + plan.tpb - 1) / plan.tpc) - c_first + 1) * kConsumers;
+    }
+    auto row_ptr = [&](int i) -> const float* {
+        if constexpr (FLAT) {
+            const int cta = c_first + i / kConsumers;
+            const int seg = bh - (int)(((long long)cta * plan.tpc) / plan.tpb);
+            return rows + (((size_t)cta * plan.maxseg + seg) * kConsumers + i % kConsumers) * ROW;
+        } else {
+            return rows + ((size_t)i * BH + bh) * ROW;
+        }
+    };
 
     float gm = -INFINITY;
-    for (int s = lane; s < nsplit; s += 32) {
-        const float2 ml = *reinterpret_cast<const float2*>(base + (size_t)s * stride_s * ROW);
+    for (int i = lane; i < n; i += 32) {
+        const float2 ml = *reinterpret_cast<const float2*>(row_ptr(i));
         if (ml.y > 0.f) gm = fmaxf(gm, ml.x);
     }
     gm = warp_max(gm);
@@ -372,21 +417,21 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nsplit,
     float L = 0.f;
     float a[DPL];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) a[i] = 0.f;
+    for (int k = 0; k < DPL; ++k) a[k] = 0.f;
 #pragma unroll 4
-    for (int s = 0; s < nsplit; ++s) {
-        const float* r = base + (size_t)s * stride_s * ROW;
+    for (int i = 0; i < n; ++i) {
+        const float* r = row_ptr(i);
         const float2 ml = *reinterpret_cast<const float2*>(r);
-        if (ml.y <= 0.f) continue;                 // empty split
-        const float w = ex2_approx(ml.x - gm);
-        L = fmaf(ml.y, w, L);
+        if (ml.y <= 0.f) continue;                 // empty part
+        const float wgt = ex2_approx(ml.x - gm);
+        L = fmaf(ml.y, wgt, L);
         if constexpr (DPL == 4) {
             const float4 v = *reinterpret_cast<const float4*>(r + 4 + lane * 4);
-            a[0] = fmaf(v.x, w, a[0]); a[1] = fmaf(v.y, w, a[1]);
-            a[2] = fmaf(v.z, w, a[2]); a[3] = fmaf(v.w, w, a[3]);
+            a[0] = fmaf(v.x, wgt, a[0]); a[1] = fmaf(v.y, wgt, a[1]);
+            a[2] = fmaf(v.z, wgt, a[2]); a[3] = fmaf(v.w, wgt, a[3]);
         } else {
             const float2 v = *reinterpret_cast<const float2*>(r + 4 + lane * 2);
-            a[0] = fmaf(v.x, w, a[0]); a[1] = fmaf(v.y, w, a[1]);
+            a[0] = fmaf(v.x, wgt, a[0]); a[1] = fmaf(v.y, wgt, a[1]);
         }
     }
 
@@ -416,8 +461,6 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nsplit,
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-struct Plan { int nsplit; int chunk; };
-
 // Optional timing probe: events recorded on the launch stream immediately
 // before and after the streaming (pass 1) kernel of the next calls made by
 // this thread.
@@ -437,93 +480,93 @@ int sm_count() {
     return cached[dev];
 }
 
-// Pick the number of KV splits.  Units run one per warp, `slots` warps are
-// resident on the device at once; a unit costs its tile count plus a fixed
-// fill/drain overhead; the grid runs in ceil(units/slots) rounds.  Chunks are
-// whole tiles so every bulk copy starts on a row boundary.
-Plan make_plan(int BH, int S, int D, int sms) {
-    const char* e = getenv("I8TK_DECODE_NSPLIT");
-    const int forced = e ? atoi(e) : 0;
+int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
+// CTAs are persistent over contiguous runs of the flat tile sequence.  The
+// count is between one and four resident waves: about 64 tiles per CTA keeps
+// the cost of filling a ring negligible while leaving the hardware scheduler
+// room to even out SM-to-SM speed differences; tiny problems get at least
+// kMinTiles tiles per CTA.  I8TK_DECODE_CTAS overrides the count (tuning only).
+DecodePlan make_plan(int BH, int S, int D, int sms) {
+    constexpr int kMinTiles = 2;
+    constexpr int kTargetTiles = 64;
     const int ctas_per_sm = (D == 64) ? DecodeTraits<64>::CTAS_PER_SM : DecodeTraits<128>::CTAS_PER_SM;
-    const long long slots = (long long)sms * ctas_per_sm * kWarps;
-    const int tiles = (S + kTile - 1) / kTile;
-    const int max_split = forced > 0 ? forced : (tiles / 4 > 1 ? tiles / 4 : 1);
-    const double overhead = 6.0;                     // tile-times per unit (pipeline fill + epilogue)
-    Plan best{1, tiles * kTile};
-    double best_cost = 1e300;
-    for (int ns = (forced > 0 ? forced : 1); ns <= max_split && ns <= 512; ++ns) {
-        const int ctiles = (tiles + ns - 1) / ns;
-        const int eff = (tiles + ctiles - 1) / ctiles;  // splits that are non-empty
-        const long long units = (long long)BH * eff;
-        const long long rounds = (units + slots - 1) / slots;
-        const double cost = (double)rounds * (ctiles + overhead) + 0.02 * eff;
-        if (cost < best_cost - 1e-9) {
-            best_cost = cost;
-            best = Plan{eff, ctiles * kTile};
-        }
-    }
-    return best;
+    DecodePlan p;
+    p.tpb = (S + kTile - 1) / kTile;
+    p.total = (long long)BH * p.tpb;
+    const long long slots = (long long)sms * ctas_per_sm;
+    long long want = p.total / kTargetTiles;
+    if (want < slots) want = slots;
+    if (want > 4 * slots) want = 4 * slots;
+    const long long cap = (p.total + kMinTiles - 1) / kMinTiles;
+    if (want > cap) want = cap;
+    const int forced = env_int("I8TK_DECODE_CTAS", 0);
+    if (forced > 0) want = forced;
+    if (want > p.total) want = p.total;
+    if (want < 1) want = 1;
+    p.tpc = (int)((p.total + want - 1) / want);
+    p.nctas = (int)((p.total + p.tpc - 1) / p.tpc);
+    p.maxseg = (p.tpc + p.tpb - 1) / p.tpb + 1;
+    return p;
+}
+
+size_t rows_bytes(const DecodePlan& p, int D) {
+    return (size_t)p.nctas * p.maxseg * kConsumers * (D + 4) * sizeof(float);
 }
 
 size_t workspace_bytes(int BH, int S, int D) {
-    const Plan p = make_plan(BH, S, D, sm_count());
-    return 256 + (size_t)BH * p.nsplit * (D + 4) * sizeof(float);
+    return 256 + rows_bytes(make_plan(BH, S, D, sm_count()), D);
 }
 
-template <int D, int VMODE>
-int launch_decode_v(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, float* part,
-                  const float* sQ, const float* sK, const float* sV, int BH, int S,
-                  void* workspace, size_t wbytes, cudaStream_t stream) {
+template <int D, bool SCALES_BULK>
+int launch_partial(const int8_t* Q, const int8_t* K, const int8_t* V, const float* sQ,
+                   const float* sK, const float* sV, float* rows, int S, const DecodePlan& p,
+                   uint32_t* status, cudaStream_t stream) {
     using T = DecodeTraits<D>;
     static bool attr_done[64] = {false};   // per template instance
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(decode_partial_kernel<D, VMODE>,
+        I8TK_CUDA(cudaFuncSetAttribute(decode_partial_kernel<D, SCALES_BULK>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
         attr_done[dev] = true;
     }
-    const Plan p = make_plan(BH, S, D, sm_count());
-    const long long units_ll = (long long)BH * p.nsplit;
-    I8TK_REQUIRE(units_ll < (1ll << 31) - 8, I8TK_ERR_UNSUPPORTED, "too many work units");
-    const int units = (int)units_ll;
-    const size_t need = 256 + (size_t)units * T::ROW_FLOATS * sizeof(float);
-    I8TK_REQUIRE(workspace != nullptr && wbytes >= need, I8TK_ERR_WORKSPACE,
-                 "decode workspace too small: need %zu bytes, got %zu", need, wbytes);
-    I8TK_REQUIRE(aligned_to(workspace, 256), I8TK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
-
-    uint32_t* status = reinterpret_cast<uint32_t*>(workspace);
-    float* rows = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 256);
     const float score_scale_log2 = kLog2e / sqrtf((float)D);
-    const int grid = (units + kWarps - 1) / kWarps;
-
-    const bool direct = (p.nsplit == 1 && out != nullptr);
     if (g_probe_start) I8TK_CUDA(cudaEventRecord(g_probe_start, stream));
-    decode_partial_kernel<D, VMODE><<<grid, kWarps * 32, T::SMEM_BYTES, stream>>>(
-        Q, K, V, sQ, sK, sV, rows, out, S, p.nsplit, p.chunk, units, score_scale_log2,
-        direct ? kToFinalF16 : kToScratchRows, status);
+    decode_partial_kernel<D, SCALES_BULK><<<p.nctas, kThreads, T::SMEM_BYTES, stream>>>(
+        Q, K, V, sQ, sK, sV, rows, S, p, score_scale_log2, status);
     I8TK_CUDA(cudaGetLastError());
     if (g_probe_stop) I8TK_CUDA(cudaEventRecord(g_probe_stop, stream));
-    if (!direct) {
-        decode_combine_kernel<D><<<(BH + 3) / 4, 128, 0, stream>>>(
-            rows, BH, p.nsplit, (long long)p.nsplit, 1ll, out, part);
-        I8TK_CUDA(cudaGetLastError());
-    }
     return I8TK_OK;
-}
-
-int env_int(const char* name, int dflt) {
-    const char* e = getenv(name);
-    return e ? atoi(e) : dflt;
 }
 
 template <int D>
 int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, float* part,
                   const float* sQ, const float* sK, const float* sV, int BH, int S,
                   void* workspace, size_t wbytes, cudaStream_t stream) {
-    if (env_int("I8TK_DECODE_VMODE", 0) == 1)
-        return launch_decode_v<D, 1>(Q, K, V, out, part, sQ, sK, sV, BH, S, workspace, wbytes, stream);
-    return launch_decode_v<D, 0>(Q, K, V, out, part, sQ, sK, sV, BH, S, workspace, wbytes, stream);
+    using T = DecodeTraits<D>;
+    const DecodePlan p = make_plan(BH, S, D, sm_count());
+    const size_t need = 256 + rows_bytes(p, D);
+    I8TK_REQUIRE(workspace != nullptr && wbytes >= need, I8TK_ERR_WORKSPACE,
+                 "decode workspace too small: need %zu bytes, got %zu", need, wbytes);
+    I8TK_REQUIRE(aligned_to(workspace, 256), I8TK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+
+    uint32_t* status = reinterpret_cast<uint32_t*>(workspace);
+    float* rows = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 256);
+    const bool bulk_scales = (S % 4 == 0) && aligned_to(sK, 16) && aligned_to(sV, 16) &&
+                             env_int("I8TK_DECODE_SCALES_LDG", 0) == 0;
+    int rc;
+    if (bulk_scales)
+        rc = launch_partial<D, true>(Q, K, V, sQ, sK, sV, rows, S, p, status, stream);
+    else
+        rc = launch_partial<D, false>(Q, K, V, sQ, sK, sV, rows, S, p, status, stream);
+    if (rc != I8TK_OK) return rc;
+    decode_combine_kernel<D, true><<<(BH + 3) / 4, 128, 0, stream>>>(rows, BH, 0, p, out, part);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
 }
 
 int check_decode_args(const void* Q, const void* K, const void* V, const void* o,
@@ -558,12 +601,12 @@ extern "C" int i8tk_decode_set_probe_events(void* start_event, void* stop_event)
     return I8TK_OK;
 }
 
-extern "C" int i8tk_decode_plan(int BH, int S, int head_dim, int* nsplit, int* chunk) {
-    I8TK_REQUIRE(BH > 0 && S > 0 && nsplit && chunk, I8TK_ERR_INVALID_ARGUMENT, "bad plan arguments");
+extern "C" int i8tk_decode_plan(int BH, int S, int head_dim, int* nctas, int* tiles_per_cta) {
+    I8TK_REQUIRE(BH > 0 && S > 0 && nctas && tiles_per_cta, I8TK_ERR_INVALID_ARGUMENT, "bad plan arguments");
     I8TK_REQUIRE(head_dim == 64 || head_dim == 128, I8TK_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
-    const Plan p = make_plan(BH, S, head_dim, sm_count());
-    *nsplit = p.nsplit;
-    *chunk = p.chunk;
+    const DecodePlan p = make_plan(BH, S, head_dim, sm_count());
+    *nctas = p.nctas;
+    *tiles_per_cta = p.tpc;
     return I8TK_OK;
 }
 
@@ -606,12 +649,13 @@ extern "C" int i8tk_decode_combine_partials(const float* parts, int nparts, int 
                  "parts and out must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = (BH + 3) / 4;
+    const DecodePlan none{};
     if (head_dim == 64)
-        decode_combine_kernel<64><<<grid, 128, 0, st>>>(parts, BH, nparts, 1ll, (long long)BH,
-                                                        static_cast<__half*>(out_f16), nullptr);
+        decode_combine_kernel<64, false><<<grid, 128, 0, st>>>(parts, BH, nparts, none,
+                                                               static_cast<__half*>(out_f16), nullptr);
     else
-        decode_combine_kernel<128><<<grid, 128, 0, st>>>(parts, BH, nparts, 1ll, (long long)BH,
-                                                         static_cast<__half*>(out_f16), nullptr);
+        decode_combine_kernel<128, false><<<grid, 128, 0, st>>>(parts, BH, nparts, none,
+                                                                static_cast<__half*>(out_f16), nullptr);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }

@@ -142,6 +142,7 @@ std::tuple<torch::Tensor, torch::Tensor> quantize_per_token_torch(torch::Tensor 
     auto sizes = x.sizes().vec();
     sizes.pop_back();
     auto s = torch::empty(sizes, torch::TensorOptions().dtype(torch::kFloat32).device(x.device()));
+    if (rows == 0) return {q, s};
     int rc;
     if (x.dtype() == torch::kFloat32)
         rc = i8tk_quantize_per_token_f32(x.data_ptr<float>(), q.data_ptr<int8_t>(), s.data_ptr<float>(),

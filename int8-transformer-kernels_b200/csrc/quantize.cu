@@ -157,10 +157,10 @@ int launch_vec(const T* x, int8_t* q, float* scales, long long rows, int cols, c
 template <typename T>
 int quantize_per_token(const T* x, int8_t* q, float* scales, long long rows, int cols,
                        cudaStream_t st) {
-    I8TK_REQUIRE(x && q && scales, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
     I8TK_REQUIRE(rows >= 0 && cols >= 1, I8TK_ERR_INVALID_ARGUMENT,
                  "rows must be >= 0 and cols >= 1 (rows=%lld cols=%d)", rows, cols);
-    if (rows == 0) return I8TK_OK;
+    if (rows == 0) return I8TK_OK;                 // empty input: nothing to read or write
+    I8TK_REQUIRE(x && q && scales, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
     constexpr int N = Vec16<T>::N;
     const bool vec_ok = (cols % N == 0) && aligned_to(x, 16) && aligned_to(q, N);
     const int nvec = cols / N;

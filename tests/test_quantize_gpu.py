@@ -83,10 +83,16 @@ def test_large_rows_property():
     x = torch.randn(32 * 12 * 4096, 64, device="cuda")
     q, s = ext().quantize_per_token(x)
     err = (x - q.float() * s[:, None]).abs()
-    assert bool((err <= s[:, None] * 0.5000001).all())
+    assert bool((err <= s[:, None] * 0.5001).all())      # half a step, plus fp32 rounding of x/s
     assert int(q.abs().amax(dim=1).min()) == 127
-    ref_s = x.abs().amax(dim=1).clamp(min=1e-8) / 127.0
-    assert torch.equal(s, ref_s)
+    # scales bit-exact against the CPU torch arithmetic on a slice (CUDA torch turns
+    # `t / 127.0` into a multiply by the rounded reciprocal, which is 1 ulp off in
+    # some rows, so the device-side torch result is not the yardstick)
+    xs = x[:200000].cpu()
+    ref_s = xs.abs().amax(dim=1).clamp(min=1e-8) / 127.0
+    assert torch.equal(s[:200000].cpu(), ref_s)
+    ref_q = (xs / ref_s[:, None]).round().clamp(-128, 127).to(torch.int8)
+    assert torch.equal(q[:200000].cpu(), ref_q)
 
 
 def test_per_tensor_roundtrip():
