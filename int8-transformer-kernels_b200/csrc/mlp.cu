@@ -1,18 +1,403 @@
-// Fused INT8 MLP (placeholder while the tcgen05 GEMM is brought up).
+// Fused INT8 MLP for B200:  x.W1 -> dequant(+bias) -> GELU -> per-token requant
+// -> .W2 -> dequant -> requant.
+//
+// Replaces int8_mlp_forward_impl and its public wrappers of the reference
+// (kernels/int8_mlp.cu:999-1314): same stage arithmetic --
+//   GEMM epilogue  v = (float)acc * sa[row] * sb[col] (+ bias[col]); GELU(tanh
+//                  form); fp16 store; row absmax taken on the fp32 value
+//                  (kernels/int8_mlp.cu:437-449)
+//   requantiser    amax = max(absmax,1e-8); q = rne(clamp(fp16(v) * (127/amax)));
+//                  scale = amax/127            (kernels/int8_mlp.cu:768-825)
+// -- with the two GEMMs on the 5th-generation tensor cores:
+//
+// * tcgen05.mma kind::i8 (int8 x int8 -> int32), 128 x BN x 32 per instruction,
+//   issued by one elected thread; accumulators live in tensor memory (TMEM),
+//   two buffers of BN columns so the epilogue of one tile overlaps the MMAs
+//   of the next.
+// * Operands are K-major in shared memory in the 128-byte-swizzled layout,
+//   brought in by TMA (cp.async.bulk.tensor.2d) through a ring of stages that
+//   completes on mbarriers; a stage is handed back to the TMA warp by
+//   tcgen05.commit when the MMAs that read it have retired.
+// * Warp roles in a persistent CTA (one per SM): warp 0 = TMA producer, warp 1 =
+//   TMEM allocator + MMA issuer, warps 2..5 = epilogue (one TMEM lane quarter
+//   each: tcgen05.ld 32 lanes x 32 columns at a time -> registers -> dequant /
+//   bias / GELU / absmax -> fp16).
+// * Every wait on an mbarrier is bounded; on a timeout the kernel records a
+//   status word, all roles fall through to the common exit and TMEM is freed.
+//
+// Weights are consumed as [N][K] (K contiguous).  Callers that hold the
+// reference's [K][N] layout get them transposed into the workspace first.
 #include "common.cuh"
+
+#include <cuda.h>
 
 namespace i8tk {
 namespace {
+
+constexpr int BM = 128;          // rows per tile (= TMEM lanes)
+constexpr int BK = 128;          // K bytes per stage: one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+constexpr int kEpiWarp0 = 2;     // first epilogue warp
+constexpr int kEpiThreads = 128;
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int B_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;                 // two accumulator buffers
+    static constexpr int AUX_BYTES = 2 * 2 * BN * 4;         // [buf][scale|bias][BN] fp32
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES + BAR_BYTES;
+};
+
+struct EpiParams {
+    const float* scale_a;     // [M] or [1]
+    const float* scale_b;     // [N] or [1]
+    const float* bias;        // [N] or nullptr
+    __half* C;                // [M, N] fp16
+    float* row_absmax;        // [M] or nullptr (atomic max, must start at 0)
+    float* out_absmax;        // [1] or nullptr (atomic max, must start at 0)
+    int a_per_row;
+    int b_per_col;
+};
+
+// ---- tcgen05 / TMA wrappers -------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_dst), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// mbarrier arrives once all tcgen05 operations issued so far by this thread retire
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], int8 x int8 -> int32
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
+// 128 bytes, 8-row groups 1024 bytes apart (stride-byte-offset), descriptor
+// version 1 (sm_100), swizzle mode 2 (128 B).  Addresses in 16-byte units.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+
+// Instruction descriptor: D = s32 (2 @ bit 4), A = B = signed int8 (1 @ bits 7, 10),
+// both K-major, N/8 @ bit 17, M/16 @ bit 24.
+__host__ __device__ constexpr uint32_t idesc_i8(int M, int N) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// GELU, tanh form: 0.5 x (1 + tanh(y)) == x / (1 + e^{-2y}), y = kC (x + kA x^3)
+// (kernels/int8_common.cuh:9-13), evaluated with ex2 and an approximate divide.
+__device__ __forceinline__ float gelu_tanh(float x) {
+    constexpr float kC = 0.7978845608028654f, kA = 0.044715f, kLog2e = 1.4426950408889634f;
+    const float u = x * x;
+    const float y2 = x * fmaf(u, -2.0f * kC * kA * kLog2e, -2.0f * kC * kLog2e);   // -2 y log2(e)
+    const float t = ex2_approx(y2);
+    return __fdividef(x, 1.0f + t);
+}
+
+__device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
+    atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));   // non-negative floats order as ints
+}
+
+// ---------------------------------------------------------------------------
+// C[M,N] fp16 = epilogue( A[M,K] int8 . B[N,K]^T int8 ), persistent over tiles.
+// M % 128 == 0, N % BN == 0, K % 128 == 0.
+// ---------------------------------------------------------------------------
+template <int BN, bool GELU>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               EpiParams ep, int M, int N, int K, uint32_t* __restrict__ status) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment: the swizzle pattern is a function of the address bits
+    const uint32_t raw_s = smem_u32(smem_raw);
+    const uint32_t base_s = (raw_s + 1023u) & ~1023u;
+    unsigned char* base = smem_raw + (base_s - raw_s);
+    float* aux = reinterpret_cast<float*>(base + STAGES * Cfg::STAGE_BYTES);
+    const uint32_t bars = base_s + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES;
+    const uint32_t full0 = bars;                       // [STAGES]  TMA landed
+    const uint32_t empty0 = bars + STAGES * 8;         // [STAGES]  MMAs done with the stage
+    const uint32_t tfull0 = bars + 2 * STAGES * 8;     // [2]       accumulator complete
+    const uint32_t tempty0 = tfull0 + 16;              // [2]       accumulator drained
+    const uint32_t tmem_slot = tempty0 + 16;
+    volatile uint32_t* tmem_slot_p =
+        reinterpret_cast<volatile uint32_t*>(base + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES +
+                                             (2 * STAGES + 4) * 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_n = N / BN;
+    const int num_tiles = (M / BM) * tiles_n;
+    const int kblocks = K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull0 + 8 * b, 1);
+            mbar_init(tempty0 + 8 * b, 4);             // one arrival per epilogue warp
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_p;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (elect_one()) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / tiles_n) * BM;
+                const int n0 = (tile % tiles_n) * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int st = it % STAGES;
+                    if (!mbar_wait_bounded(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) {
+                        atomicExch(status, kDeviceTimeoutMagic);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sa = base_s + st * Cfg::STAGE_BYTES;
+                    mbar_expect_tx(full0 + 8 * st, Cfg::STAGE_BYTES);
+                    tma_load_2d(sa, &tmA, kb * BK, m0, full0 + 8 * st);
+                    tma_load_2d(sa + Cfg::A_BYTES, &tmB, kb * BK, n0, full0 + 8 * st);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_i8(BM, BN);
+            int it = 0, lt = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+                const int buf = lt & 1;
+                if (!mbar_wait_bounded(tempty0 + 8 * buf, ((lt >> 1) & 1) ^ 1)) {
+                    atomicExch(status, kDeviceTimeoutMagic);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int st = it % STAGES;
+                    if (!mbar_wait_bounded(full0 + 8 * st, (it / STAGES) & 1)) {
+                        atomicExch(status, kDeviceTimeoutMagic);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = base_s + st * Cfg::STAGE_BYTES;
+                    const uint64_t da = smem_desc_sw128(sa);
+                    const uint64_t db = smem_desc_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)     // 32 bytes of K per instruction: +2 in 16-byte units
+                        mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    tc_commit(empty0 + 8 * st);           // stage reusable when these MMAs retire
+                }
+                if (ok) tc_commit(tfull0 + 8 * buf);      // accumulator complete
+            }
+        }
+    } else {
+        // ================= epilogue =================
+        const int q = warp & 3;                           // TMEM lane quarter this warp may read
+        const int et = threadIdx.x - kEpiWarp0 * 32;      // 0..127
+        int lt = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+            const int buf = lt & 1;
+            const int m0 = (tile / tiles_n) * BM;
+            const int n0 = (tile % tiles_n) * BN;
+            const int row = m0 + q * 32 + lane;
+
+            // column scales and bias of this tile -> shared memory
+            float* sb = aux + buf * 2 * BN;
+            float* bb = sb + BN;
+            for (int j = et; j < BN; j += kEpiThreads) {
+                sb[j] = ep.b_per_col ? ep.scale_b[n0 + j] : ep.scale_b[0];
+                bb[j] = ep.bias ? ep.bias[n0 + j] : 0.f;
+            }
+            const float sa = ep.a_per_row ? ep.scale_a[row] : ep.scale_a[0];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+
+            const bool got = mbar_wait_bounded(tfull0 + 8 * buf, (lt >> 1) & 1);
+            if (!__all_sync(0xffffffffu, got)) {
+                if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
+                break;
+            }
+            tc_fence_after();
+
+            float rmax = 0.f;
+            __half* crow = ep.C + (size_t)row * N + n0;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + cc * 32, r);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const float2 s2 = *reinterpret_cast<const float2*>(sb + cc * 32 + j);
+                    const float2 b2 = *reinterpret_cast<const float2*>(bb + cc * 32 + j);
+                    float v0 = (float)(int)r[j] * sa * s2.x + b2.x;
+                    float v1 = (float)(int)r[j + 1] * sa * s2.y + b2.y;
+                    if (GELU) {
+                        v0 = gelu_tanh(v0);
+                        v1 = gelu_tanh(v1);
+                    }
+                    rmax = fmaxf(rmax, fmaxf(fabsf(v0), fabsf(v1)));
+                    const __half2 h = __floats2half2_rn(v0, v1);
+                    packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(crow + cc * 32);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            }
+            // accumulator buffer drained: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+
+            if (ep.row_absmax) atomic_max_pos(ep.row_absmax + row, rmax);
+            if (ep.out_absmax) {
+                float wmax;
+                asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(wmax) : "f"(rmax));
+                if (lane == 0) atomic_max_pos(ep.out_absmax, wmax);
+            }
+        }
+    }
+
+    // common exit: every role ends here, then the allocating warp frees TMEM
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Row requantiser: fp16 [M,N] + row absmax -> int8 [M,N] + row scales
+// (kernels/int8_mlp.cu:768-795).  PER_TENSOR: one absmax for the whole tensor,
+// the scale goes to *tensor_scale (kernels/int8_mlp.cu:799-825).
+// ---------------------------------------------------------------------------
+template <bool PER_TENSOR>
+__global__ void __launch_bounds__(256)
+requant_rows_kernel(const __half* __restrict__ H, const float* __restrict__ absmax,
+                    int8_t* __restrict__ out, float* __restrict__ scales, long long M, int N) {
+    const long long total_vec = M * N / 16;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total_vec;
+         v += (long long)gridDim.x * blockDim.x) {
+        const long long e0 = v * 16;
+        const long long row = e0 / N;
+        const float amax = fmaxf(PER_TENSOR ? absmax[0] : absmax[row], 1e-8f);
+        const float inv = 127.f / amax;
+        if (PER_TENSOR) {
+            if (v == 0) scales[0] = amax / 127.f;
+        } else if (e0 % N == 0) {
+            scales[row] = amax / 127.f;
+        }
+        const uint4 h0 = *reinterpret_cast<const uint4*>(H + e0);
+        const uint4 h1 = *reinterpret_cast<const uint4*>(H + e0 + 8);
+        const __half2* hp0 = reinterpret_cast<const __half2*>(&h0);
+        const __half2* hp1 = reinterpret_cast<const __half2*>(&h1);
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 a = __half22float2(i < 2 ? hp0[2 * i] : hp1[2 * i - 4]);
+            const float2 b = __half22float2(i < 2 ? hp0[2 * i + 1] : hp1[2 * i - 3]);
+            const int q0 = __float2int_rn(fmaxf(-128.f, fminf(127.f, a.x * inv)));
+            const int q1 = __float2int_rn(fmaxf(-128.f, fminf(127.f, a.y * inv)));
+            const int q2 = __float2int_rn(fmaxf(-128.f, fminf(127.f, b.x * inv)));
+            const int q3 = __float2int_rn(fmaxf(-128.f, fminf(127.f, b.y * inv)));
+            w[i] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+                   ((uint32_t)(q3 & 0xff) << 24);
+        }
+        *reinterpret_cast<uint4*>(out + e0) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
 
 // int8 [R][C] -> [C][R]; 64x64 tiles, 4-byte global accesses on both sides.
 __global__ void __launch_bounds__(256)
 transpose_i8_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int R, int C) {
     __shared__ int8_t tile[64][68];
     const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+    const bool fast_in = (C % 4) == 0, fast_out = (R % 4) == 0;
     for (int i = threadIdx.x; i < 64 * 16; i += 256) {
         const int r = i / 16, c4 = (i % 16) * 4;
         if (r0 + r < R) {
-            if (c0 + c4 + 3 < C && (C % 4) == 0) {
+            if (fast_in && c0 + c4 + 3 < C) {
                 const uint32_t w = *reinterpret_cast<const uint32_t*>(in + (size_t)(r0 + r) * C + c0 + c4);
                 tile[r][c4] = (int8_t)(w & 0xff); tile[r][c4 + 1] = (int8_t)((w >> 8) & 0xff);
                 tile[r][c4 + 2] = (int8_t)((w >> 16) & 0xff); tile[r][c4 + 3] = (int8_t)(w >> 24);
@@ -26,7 +411,7 @@ transpose_i8_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int
     for (int i = threadIdx.x; i < 64 * 16; i += 256) {
         const int c = i / 16, r4 = (i % 16) * 4;      // output row c0+c, cols r0+r4..
         if (c0 + c < C) {
-            if (r0 + r4 + 3 < R && (R % 4) == 0) {
+            if (fast_out && r0 + r4 + 3 < R) {
                 const uint32_t w = (uint32_t)(uint8_t)tile[r4][c] | ((uint32_t)(uint8_t)tile[r4 + 1][c] << 8) |
                                    ((uint32_t)(uint8_t)tile[r4 + 2][c] << 16) | ((uint32_t)(uint8_t)tile[r4 + 3][c] << 24);
                 *reinterpret_cast<uint32_t*>(out + (size_t)(c0 + c) * R + r0 + r4) = w;
@@ -38,8 +423,6 @@ transpose_i8_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int
     }
 }
 
-}  // namespace
-
 int transpose_i8(const int8_t* in, int8_t* out, int R, int C, cudaStream_t st) {
     dim3 grid((C + 63) / 64, (R + 63) / 64);
     transpose_i8_kernel<<<grid, 256, 0, st>>>(in, out, R, C);
@@ -47,6 +430,143 @@ int transpose_i8(const int8_t* in, int8_t* out, int R, int C, cudaStream_t st) {
     return I8TK_OK;
 }
 
+// ---- host: tensor maps ------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// int8 matrix [rows][cols] row-major, box of box_rows x 128 bytes, 128-byte swizzle
+int make_map(CUtensorMap* map, const int8_t* ptr, int rows, int cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    I8TK_REQUIRE(fn != nullptr, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(ptr), dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    I8TK_REQUIRE(r == CUDA_SUCCESS, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return I8TK_OK;
+}
+
+int sm_count_mlp() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    return n;
+}
+
+template <int BN, bool GELU>
+int launch_gemm(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, int N, int K,
+                uint32_t* status, cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    I8TK_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES));
+        attr_done[dev] = true;
+    }
+    CUtensorMap tmA, tmB;
+    int rc = make_map(&tmA, A, M, K, BM);
+    if (rc != I8TK_OK) return rc;
+    rc = make_map(&tmB, BT, N, K, BN);
+    if (rc != I8TK_OK) return rc;
+    const int tiles = (M / BM) * (N / BN);
+    const int sms = sm_count_mlp();
+    const int grid = tiles < sms ? tiles : sms;
+    gemm_i8_kernel<BN, GELU><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, status);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
+
+template <bool GELU>
+int launch_gemm_bn(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, int N, int K,
+                   uint32_t* status, cudaStream_t st) {
+    // 256-wide tiles when they divide N and still give every SM a tile; else 128-wide
+    const int sms = sm_count_mlp();
+    const bool wide = (N % 256 == 0) && ((long long)(M / BM) * (N / 256) >= sms);
+    if (wide) return launch_gemm<256, GELU>(A, BT, ep, M, N, K, status, st);
+    return launch_gemm<128, GELU>(A, BT, ep, M, N, K, status, st);
+}
+
+int requant_grid(long long vecs) {
+    long long b = (vecs + 255) / 256;
+    if (b > 148ll * 8) b = 148ll * 8;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+// workspace carve-up
+struct MlpWorkspace {
+    uint32_t* status;
+    float* hid_absmax;    // [T]
+    float* out_absmax;    // [T]   (per-token output)  -- zeroed together with the two below
+    float* tensor_absmax; // [1]
+    float* hid_scale;     // [T]
+    __half* hid_f16;      // [T, d_ff]
+    int8_t* hid_i8;       // [T, d_ff]
+    __half* out_f16;      // [T, d_model]
+    int8_t* w1t;          // [d_ff, d_model]  (only when the weights are not prepacked)
+    int8_t* w2t;          // [d_model, d_ff]
+    size_t bytes;
+    size_t zero_bytes;    // hid_absmax .. tensor_absmax
+};
+
+MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
+    MlpWorkspace w{};
+    size_t off = 0;
+    auto take = [&](size_t n) { size_t o = off; off = round_up(off + n, 256); return o; };
+    unsigned char* b = static_cast<unsigned char*>(base);
+    const size_t o_status = take(256);
+    const size_t o_habs = take((size_t)T * 4);
+    const size_t o_oabs = take((size_t)T * 4);
+    const size_t o_tabs = take(256);
+    const size_t zero_end = off;
+    const size_t o_hsc = take((size_t)T * 4);
+    const size_t o_h16 = take((size_t)T * d_ff * 2);
+    const size_t o_hi8 = take((size_t)T * d_ff);
+    const size_t o_o16 = take((size_t)T * d_model * 2);
+    size_t o_w1 = 0, o_w2 = 0;
+    if (!(flags & I8TK_MLP_PREPACKED)) {
+        o_w1 = take((size_t)d_model * d_ff);
+        o_w2 = take((size_t)d_model * d_ff);
+    }
+    w.bytes = off;
+    w.zero_bytes = zero_end - o_habs;
+    if (b) {
+        w.status = reinterpret_cast<uint32_t*>(b + o_status);
+        w.hid_absmax = reinterpret_cast<float*>(b + o_habs);
+        w.out_absmax = reinterpret_cast<float*>(b + o_oabs);
+        w.tensor_absmax = reinterpret_cast<float*>(b + o_tabs);
+        w.hid_scale = reinterpret_cast<float*>(b + o_hsc);
+        w.hid_f16 = reinterpret_cast<__half*>(b + o_h16);
+        w.hid_i8 = reinterpret_cast<int8_t*>(b + o_hi8);
+        w.out_f16 = reinterpret_cast<__half*>(b + o_o16);
+        if (!(flags & I8TK_MLP_PREPACKED)) {
+            w.w1t = reinterpret_cast<int8_t*>(b + o_w1);
+            w.w2t = reinterpret_cast<int8_t*>(b + o_w2);
+        }
+    }
+    return w;
+}
+
+}  // namespace
 }  // namespace i8tk
 
 using namespace i8tk;
@@ -64,13 +584,67 @@ extern "C" int i8tk_transpose_int8_weights(const int8_t* W1, const int8_t* W2, i
 }
 
 extern "C" size_t i8tk_mlp_workspace_bytes(int T, int d_model, int d_ff, int flags) {
-    (void)T; (void)d_model; (void)d_ff; (void)flags;
-    return 0;
+    if (T <= 0 || d_model <= 0 || d_ff <= 0) return 0;
+    return carve(nullptr, T, d_model, d_ff, flags).bytes;
 }
 
-extern "C" int i8tk_mlp_forward(const int8_t*, const int8_t*, const int8_t*, int8_t*, const float*,
-                                const float*, const float*, const float*, float*, float*, int, int,
-                                int, int, void*, size_t, i8tk_stream_t) {
-    set_error("i8tk_mlp_forward is not built in this snapshot");
-    return I8TK_ERR_UNSUPPORTED;
+extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out,
+                                const float* scale_x, const float* scale_W1, const float* scale_W2,
+                                const float* bias1, float* out_row_scales, float* out_tensor_scale,
+                                int T, int d_model, int d_ff, int flags, void* workspace,
+                                size_t workspace_bytes, i8tk_stream_t stream) {
+    I8TK_REQUIRE(x && W1 && W2 && out && scale_x && scale_W1 && scale_W2, I8TK_ERR_INVALID_ARGUMENT,
+                 "null pointer argument");
+    I8TK_REQUIRE(out_row_scales || out_tensor_scale, I8TK_ERR_INVALID_ARGUMENT,
+                 "one of out_row_scales / out_tensor_scale must be given");
+    I8TK_REQUIRE(T > 0 && d_model > 0 && d_ff > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
+    I8TK_REQUIRE((flags & ~7) == 0, I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
+    I8TK_REQUIRE(T % 128 == 0 && d_model % 128 == 0 && d_ff % 128 == 0, I8TK_ERR_UNSUPPORTED,
+                 "T, d_model and d_ff must be multiples of 128 (got %d, %d, %d)", T, d_model, d_ff);
+    I8TK_REQUIRE(aligned_to(x, 16) && aligned_to(W1, 16) && aligned_to(W2, 16) && aligned_to(out, 16),
+                 I8TK_ERR_ALIGNMENT, "x, W1, W2 and out must be 16-byte aligned");
+    const MlpWorkspace w = carve(workspace, T, d_model, d_ff, flags);
+    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= w.bytes, I8TK_ERR_WORKSPACE,
+                 "mlp workspace too small: need %zu bytes, got %zu", w.bytes, workspace_bytes);
+    I8TK_REQUIRE(aligned_to(workspace, 256), I8TK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    const int8_t* W1T = W1;
+    const int8_t* W2T = W2;
+    int rc;
+    if (!(flags & I8TK_MLP_PREPACKED)) {
+        rc = transpose_i8(W1, w.w1t, d_model, d_ff, st);
+        if (rc != I8TK_OK) return rc;
+        rc = transpose_i8(W2, w.w2t, d_ff, d_model, st);
+        if (rc != I8TK_OK) return rc;
+        W1T = w.w1t;
+        W2T = w.w2t;
+    }
+    I8TK_CUDA(cudaMemsetAsync(w.hid_absmax, 0, w.zero_bytes, st));
+
+    const int per_token = (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0;
+    const int per_channel = (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0;
+
+    // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), fp16 + row absmax
+    EpiParams e1{scale_x, scale_W1, bias1, w.hid_f16, w.hid_absmax, nullptr, per_token, per_channel};
+    rc = launch_gemm_bn<true>(x, W1T, e1, T, d_ff, d_model, w.status, st);
+    if (rc != I8TK_OK) return rc;
+    // per-token requant of the hidden
+    requant_rows_kernel<false><<<requant_grid((long long)T * d_ff / 16), 256, 0, st>>>(
+        w.hid_f16, w.hid_absmax, w.hid_i8, w.hid_scale, T, d_ff);
+    I8TK_CUDA(cudaGetLastError());
+    // GEMM2: out = (hidden_i8 . W2) * sh * sW2, fp16 + absmax
+    EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16,
+                 out_row_scales ? w.out_absmax : nullptr,
+                 out_row_scales ? nullptr : w.tensor_absmax, 1, per_channel};
+    rc = launch_gemm_bn<false>(w.hid_i8, W2T, e2, T, d_model, d_ff, w.status, st);
+    if (rc != I8TK_OK) return rc;
+    if (out_row_scales)
+        requant_rows_kernel<false><<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
+            w.out_f16, w.out_absmax, out, out_row_scales, T, d_model);
+    else
+        requant_rows_kernel<true><<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
+            w.out_f16, w.tensor_absmax, out, out_tensor_scale, T, d_model);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
 }
