@@ -94,6 +94,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return false;
 }
 
+// Latency-critical variant: polls without a suspend hint (the hinted form backs
+// off with nanosleep, which adds wake-up latency to every wait).  Still bounded.
+__device__ __forceinline__ bool mbar_wait_spin_bounded(uint32_t bar, uint32_t parity,
+                                                       uint32_t limit = (1u << 24)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // 1-D bulk async copy global -> shared, completion counted on an mbarrier.
 // Both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,

@@ -19,9 +19,10 @@
 //   completes on mbarriers; a stage is handed back to the TMA warp by
 //   tcgen05.commit when the MMAs that read it have retired.
 // * Warp roles in a persistent CTA (one per SM): warp 0 = TMA producer, warp 1 =
-//   TMEM allocator + MMA issuer, warps 2..5 = epilogue (one TMEM lane quarter
-//   each: tcgen05.ld 32 lanes x 32 columns at a time -> registers -> dequant /
-//   bias / GELU / absmax -> fp16).
+//   TMEM allocator + MMA issuer, warps 2..9 = epilogue (two warps per TMEM lane
+//   quarter, each taking half of the tile's columns: tcgen05.ld 32 lanes x 32
+//   columns at a time, the next load in flight while the current block goes
+//   registers -> dequant / bias / GELU / absmax -> fp16).
 // * Every wait on an mbarrier is bounded; on a timeout the kernel records a
 //   status word, all roles fall through to the common exit and TMEM is freed.
 //
@@ -36,20 +37,22 @@ namespace {
 
 constexpr int BM = 128;          // rows per tile (= TMEM lanes)
 constexpr int BK = 128;          // K bytes per stage: one 128-byte swizzle row
-constexpr int kGemmThreads = 192;
 constexpr int kEpiWarp0 = 2;     // first epilogue warp
-constexpr int kEpiThreads = 128;
+constexpr int kEpiWarps = 8;     // two per TMEM lane quarter, each takes half of the columns
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kGemmThreads = (kEpiWarp0 + kEpiWarps) * 32;
 
 template <int BN>
 struct GemmCfg {
-    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : 6);
     static constexpr int A_BYTES = BM * BK;
     static constexpr int B_BYTES = BN * BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN;                 // two accumulator buffers
+    static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;   // two accumulator buffers, power of two
     static constexpr int AUX_BYTES = 2 * 2 * BN * 4;         // [buf][scale|bias][BN] fp32
+    static constexpr int CSTAGE_BYTES = kEpiWarps * 32 * 64; // per epilogue warp: 32 rows x 32 fp16
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES + BAR_BYTES;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES + BAR_BYTES + CSTAGE_BYTES;
 };
 
 struct EpiParams {
@@ -136,8 +139,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+// Waits for this thread's outstanding tcgen05.ld.  The registers of the block
+// about to be used are listed as in/out operands so the compiler cannot move
+// a read of them above the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+          "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+          "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]),
+          "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]),
+          "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :
+        : "memory");
 }
 
 __device__ __forceinline__ bool elect_one() {
@@ -150,14 +164,19 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
-// GELU, tanh form: 0.5 x (1 + tanh(y)) == x / (1 + e^{-2y}), y = kC (x + kA x^3)
-// (kernels/int8_common.cuh:9-13), evaluated with ex2 and an approximate divide.
+// GELU, tanh form: 0.5 x (1 + tanh(y)), y = kC (x + kA x^3)
+// (kernels/int8_common.cuh:9-13).  One MUFU op per element: the epilogue is
+// bound by the special-function unit, not by the tensor cores.  tanh.approx
+// has a relative error of about 2^-11, the same size as the fp16 rounding the
+// value goes through next.
 __device__ __forceinline__ float gelu_tanh(float x) {
-    constexpr float kC = 0.7978845608028654f, kA = 0.044715f, kLog2e = 1.4426950408889634f;
+    constexpr float kC = 0.7978845608028654f, kA = 0.044715f;
     const float u = x * x;
-    const float y2 = x * fmaf(u, -2.0f * kC * kA * kLog2e, -2.0f * kC * kLog2e);   // -2 y log2(e)
-    const float t = ex2_approx(y2);
-    return __fdividef(x, 1.0f + t);
+    const float y = x * fmaf(u, kC * kA, kC);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(y));
+    const float hx = 0.5f * x;
+    return fmaf(hx, t, hx);
 }
 
 __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
@@ -190,6 +209,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     volatile uint32_t* tmem_slot_p =
         reinterpret_cast<volatile uint32_t*>(base + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES +
                                              (2 * STAGES + 4) * 8);
+    unsigned char* cstage_base = base + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES + Cfg::BAR_BYTES;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -204,7 +224,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull0 + 8 * b, 1);
-            mbar_init(tempty0 + 8 * b, 4);             // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * b, kEpiWarps);     // one arrival per epilogue warp
         }
         fence_mbar_init();
     }
@@ -224,7 +244,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int n0 = (tile % tiles_n) * BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % STAGES;
-                    if (!mbar_wait_bounded(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) {
+                    if (!mbar_wait_spin_bounded(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) {
                         atomicExch(status, kDeviceTimeoutMagic);
                         ok = false;
                         break;
@@ -244,7 +264,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
                 const int buf = lt & 1;
-                if (!mbar_wait_bounded(tempty0 + 8 * buf, ((lt >> 1) & 1) ^ 1)) {
+                if (!mbar_wait_spin_bounded(tempty0 + 8 * buf, ((lt >> 1) & 1) ^ 1)) {
                     atomicExch(status, kDeviceTimeoutMagic);
                     break;
                 }
@@ -252,7 +272,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t tmem_d = tmem_base + buf * BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % STAGES;
-                    if (!mbar_wait_bounded(full0 + 8 * st, (it / STAGES) & 1)) {
+                    if (!mbar_wait_spin_bounded(full0 + 8 * st, (it / STAGES) & 1)) {
                         atomicExch(status, kDeviceTimeoutMagic);
                         ok = false;
                         break;
@@ -271,8 +291,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else {
         // ================= epilogue =================
+        const int ew = warp - kEpiWarp0;                  // 0..7
         const int q = warp & 3;                           // TMEM lane quarter this warp may read
-        const int et = threadIdx.x - kEpiWarp0 * 32;      // 0..127
+        const int half = ew >> 2;                         // which half of the tile's columns
+        constexpr int HC = BN / 2;                        // columns per warp
+        constexpr int NCH = HC / 32;                      // 32-column blocks per warp
+        const int et = threadIdx.x - kEpiWarp0 * 32;      // 0..255
         int lt = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
             const int buf = lt & 1;
@@ -288,9 +312,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 bb[j] = ep.bias ? ep.bias[n0 + j] : 0.f;
             }
             const float sa = ep.a_per_row ? ep.scale_a[row] : ep.scale_a[0];
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
 
-            const bool got = mbar_wait_bounded(tfull0 + 8 * buf, (lt >> 1) & 1);
+            const bool got = mbar_wait_spin_bounded(tfull0 + 8 * buf, (lt >> 1) & 1);
             if (!__all_sync(0xffffffffu, got)) {
                 if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
                 break;
@@ -298,19 +322,24 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_fence_after();
 
             float rmax = 0.f;
-            __half* crow = ep.C + (size_t)row * N + n0;
-#pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + cc * 32, r);
-                tmem_ld_wait();
+            const int c0 = half * HC;
+            __half* cblk = ep.C + (size_t)(m0 + q * 32) * N + n0 + c0;   // first row of this warp's block
+            unsigned char* cst = cstage_base + ew * (32 * 64);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c0;
+            uint32_t r[2][32];
+            tmem_ld32(taddr, r[0]);
+#pragma unroll
+            for (int cc = 0; cc < NCH; ++cc) {
+                tmem_ld_wait(r[cc & 1]);                                   // block cc is in r[cc & 1]
+                if (cc + 1 < NCH) tmem_ld32(taddr + (cc + 1) * 32, r[(cc + 1) & 1]);
+                const uint32_t* rr = r[cc & 1];
                 uint32_t packed[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
-                    const float2 s2 = *reinterpret_cast<const float2*>(sb + cc * 32 + j);
-                    const float2 b2 = *reinterpret_cast<const float2*>(bb + cc * 32 + j);
-                    float v0 = (float)(int)r[j] * sa * s2.x + b2.x;
-                    float v1 = (float)(int)r[j + 1] * sa * s2.y + b2.y;
+                    const float2 s2 = *reinterpret_cast<const float2*>(sb + c0 + cc * 32 + j);
+                    const float2 b2 = *reinterpret_cast<const float2*>(bb + c0 + cc * 32 + j);
+                    float v0 = (float)(int)rr[j] * sa * s2.x + b2.x;
+                    float v1 = (float)(int)rr[j + 1] * sa * s2.y + b2.y;
                     if (GELU) {
                         v0 = gelu_tanh(v0);
                         v1 = gelu_tanh(v1);
@@ -319,10 +348,23 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const __half2 h = __floats2half2_rn(v0, v1);
                     packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
                 }
-                uint4* dst = reinterpret_cast<uint4*>(crow + cc * 32);
+                // 32 rows x 64 bytes through this warp's staging block so that the
+                // global stores cover whole 64-byte row segments (4 lanes per row).
+                // 16-byte slot j of row r lives at slot j ^ ((r >> 1) & 3): both the
+                // row-wise writes and the 8-rows-at-a-time reads are conflict free.
+                __syncwarp();
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    *reinterpret_cast<uint4*>(cst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                __syncwarp();
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int rr2 = it * 8 + (lane >> 2);
+                    const int j = lane & 3;
+                    const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 64 + ((j ^ ((rr2 >> 1) & 3)) << 4));
+                    *reinterpret_cast<uint4*>(cblk + (size_t)rr2 * N + cc * 32 + j * 8) = v;
+                }
             }
             // accumulator buffer drained: hand it back to the MMA warp
             tc_fence_before();
@@ -498,10 +540,21 @@ int launch_gemm(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, i
 template <bool GELU>
 int launch_gemm_bn(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, int N, int K,
                    uint32_t* status, cudaStream_t st) {
-    // 256-wide tiles when they divide N and still give every SM a tile; else 128-wide
+    // Tile width: among the widths that divide N, the one with the least
+    // (rounds of CTAs over the SMs) x (tile width); ties go to the wider tile.
     const int sms = sm_count_mlp();
-    const bool wide = (N % 256 == 0) && ((long long)(M / BM) * (N / 256) >= sms);
-    if (wide) return launch_gemm<256, GELU>(A, BT, ep, M, N, K, status, st);
+    const int widths[3] = {256, 192, 128};
+    int best = 128;
+    long long best_cost = -1;
+    for (int i = 0; i < 3; ++i) {
+        const int bn = widths[i];
+        if (N % bn) continue;
+        const long long tiles = (long long)(M / BM) * (N / bn);
+        const long long cost = ((tiles + sms - 1) / sms) * bn;
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    if (best == 256) return launch_gemm<256, GELU>(A, BT, ep, M, N, K, status, st);
+    if (best == 192) return launch_gemm<192, GELU>(A, BT, ep, M, N, K, status, st);
     return launch_gemm<128, GELU>(A, BT, ep, M, N, K, status, st);
 }
 
