@@ -379,6 +379,13 @@ def main():
 
 def sweep(torch, ext, cabi, world, rank, barrier, dist):
     """Other configurations, device-timed, reported beside the headline."""
+    def reduce_max(el):
+        if dist is None:
+            return el
+        t = torch.tensor([el], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     res = []
     cases = [("cfg0 B1 H12 D64 ctx1024", 1, 12, 64, 1024, False, 200),
              ("cfg1 B32 H12 D64 ctx4096", 32, 12, 64, 4096, False, 100),
@@ -388,22 +395,89 @@ def sweep(torch, ext, cabi, world, rank, barrier, dist):
         cases.append(("cfg2 B64 H32 D128 ctx8192 (1 GPU)", 64, 32, 128, 8192, True, 20))
     else:
         # config 2 strong-scaled: the 2048 (b,h) rows split evenly over the ranks
-        cases.append((f"cfg2 B64 H32 D128 ctx8192 sharded over {world} GPUs", 64 // world, 32, 128, 8192, True, 20))
+        cases.append((f"cfg2 B64 H32 D128 ctx8192 sharded by (b,h) over {world} GPUs", 64 // world, 32, 128,
+                      8192, True, 20))
     for name, b, h, d, s, outl, steps in cases:
         args = make_inputs(torch, ext, b, h, s, d, outliers=outl, seed=rank)
-        el = timed_steps(torch, lambda: ext.int8_decode_attention_forward(*args), steps, 5, barrier)
-        if dist is not None:
-            t = torch.tensor([el], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            el = float(t.item())
-        mult = world
-        gbs = mult * kv_bytes(b, h, s, d) * steps / el / 1e9
+        el = reduce_max(timed_steps(torch, lambda: ext.int8_decode_attention_forward(*args), steps, 5, barrier))
+        strong = name.startswith("cfg2") and world > 1
+        gbs = world * kv_bytes(b, h, s, d) * steps / el / 1e9
         res.append({"workload": name, "us_per_step": el / steps * 1e6, "GBps": gbs,
                     "pct_of_8TBps_per_gpu": 100.0 * gbs / world / NOMINAL_HBM_GBS,
+                    "scaling": "strong" if strong else "weak",
                     "l2_resident": kv_bytes(b, h, s, d) < 100e6})
         del args
         torch.cuda.empty_cache()
+
+    if world > 1:
+        # config 3: B4 H32 D128 ctx 524288, KV sequence cut into `world` chunks, one per GPU;
+        # per-(b,h) (m, l, acc) rows all-gathered over NCCL and merged on every rank
+        pkg = importlib.import_module("int8-transformer-kernels_b200")
+        sh = pkg.sharding
+        b, h, d, s = 4, 32, 128, 524288
+        a, e_ = sh.seq_shard_range(s, world, rank)
+        Qi, Ki, Vi, sQ, sK, sV = make_inputs(torch, ext, b, h, e_ - a, d, outliers=True, seed=100 + rank)
+        g = torch.Generator(device="cuda").manual_seed(7)       # q is replicated: same seed on every rank
+        Qi, sQ = ext.quantize_per_token(torch.randn(b, h, d, device="cuda", dtype=torch.float16, generator=g))
+        steps = 20
+        fn = lambda: sh.decode_attention_seq_sharded(Qi, Ki, Vi, sQ, sK, sV)
+        el = reduce_max(timed_steps(torch, fn, steps, 5, barrier))
+        gbs = kv_bytes(b, h, s, d) * steps / el / 1e9
+        res.append({"workload": f"cfg3 B4 H32 D128 ctx524288 KV-sequence sharded over {world} GPUs "
+                                f"(NCCL all-gather of {b * h * (d + 4) * 4} B per rank + merge)",
+                    "us_per_step": el / steps * 1e6, "GBps": gbs,
+                    "pct_of_8TBps_per_gpu": 100.0 * gbs / world / NOMINAL_HBM_GBS, "scaling": "strong"})
+        del Ki, Vi, sK, sV
+        torch.cuda.empty_cache()
+    elif rank == 0:
+        res.extend(mlp_sweep(torch, ext, cabi))
     return res
+
+
+def mlp_sweep(torch, ext, cabi):
+    """Fused INT8 MLP (per-token x, per-channel W, bias, GELU, per-token requant), INT8 TOPS =
+    4*M*d_model*d_ff / time (bench/sweep.py:97-99 of the reference).  Weights are handed over
+    pre-transposed once (the prepacked form); the op-level call that transposes on every
+    call is timed beside it."""
+    lib = cabi.load()
+    out = []
+    for (dm, dff) in ((768, 3072), (1024, 4096)):
+        for M in (512, 4096, 16384):
+            g = torch.Generator(device="cuda").manual_seed(0)
+            x = torch.randn(1, M, dm, device="cuda", dtype=torch.float16, generator=g)
+            xi, sx = ext.quantize_per_token(x)
+            W1 = torch.randn(dm, dff, device="cuda", generator=g) * 0.02
+            W2 = torch.randn(dff, dm, device="cuda", generator=g) * 0.02
+            s1 = W1.abs().amax(dim=0).clamp(min=1e-8) / 127.0
+            s2 = W2.abs().amax(dim=0).clamp(min=1e-8) / 127.0
+            w1i = (W1 / s1).round().clamp(-128, 127).to(torch.int8).contiguous()
+            w2i = (W2 / s2).round().clamp(-128, 127).to(torch.int8).contiguous()
+            b1 = torch.randn(dff, device="cuda", generator=g) * 0.01
+            sxf = sx.reshape(-1).contiguous()
+            W1T, W2T = ext.transpose_int8_weights(w1i, w2i)
+            flags = cabi.MLP_X_PER_TOKEN | cabi.MLP_W_PER_CHANNEL | cabi.MLP_PREPACKED
+            wb = lib.i8tk_mlp_workspace_bytes(M, dm, dff, flags)
+            ws = torch.empty(wb, dtype=torch.uint8, device="cuda")
+            o = torch.empty_like(xi)
+            osc = torch.empty(M, device="cuda")
+            st = torch.cuda.current_stream().cuda_stream
+
+            def prepacked():
+                cabi.check(lib.i8tk_mlp_forward(xi.data_ptr(), W1T.data_ptr(), W2T.data_ptr(), o.data_ptr(),
+                                                sxf.data_ptr(), s1.data_ptr(), s2.data_ptr(), b1.data_ptr(),
+                                                osc.data_ptr(), None, M, dm, dff, flags, ws.data_ptr(), wb, st))
+
+            steps = 50
+            el = timed_steps(torch, prepacked, steps, 5)
+            el2 = timed_steps(torch, lambda: ext.int8_mlp_forward_per_channel_bias(xi, w1i, w2i, sxf, s1, s2, b1),
+                              steps, 5)
+            ops = 4.0 * M * dm * dff
+            out.append({"workload": f"cfg4 fused INT8 MLP M={M} {dm}->{dff}->{dm}",
+                        "us_per_step": el / steps * 1e6, "int8_TOPS": ops * steps / el / 1e12,
+                        "pct_of_4.5_POPS_nominal": 100.0 * ops * steps / el / 4.5e15,
+                        "us_per_step_with_per_call_weight_transpose": el2 / steps * 1e6,
+                        "l2_resident": True})
+    return out
 
 
 if __name__ == "__main__":
