@@ -253,6 +253,7 @@ def main():
     torch.cuda.set_device(local_rank)
     distributed = world > 1
     if distributed:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")      # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     pkg = importlib.import_module("int8-transformer-kernels_b200")
