@@ -89,6 +89,34 @@ int i8tk_decode_attention_forward(const int8_t* Q, const int8_t* K, const int8_t
                                   void* workspace, size_t workspace_bytes,
                                   i8tk_stream_t stream);
 
+/* The same operation for callers that must not allocate device memory and have
+ * no spare buffer to lend: plugin "enqueue" hooks of serving runtimes, code
+ * running after the application has handed the whole device to its own memory
+ * pool, or hot loops where an allocation would stall the device.  It has no
+ * counterpart in the reference (whose launcher grows a cudaMalloc'ed static
+ * buffer on demand, kernels/int8_decode_attention.cu:430-440).
+ *
+ * The scratch is a fixed 8 MiB block that is part of the library image
+ * (i8tk_decode_static_scratch_bytes()); every GPU that loads the library
+ * carries it until the process exits.  The call itself allocates nothing and
+ * frees nothing.  Shapes whose scratch need (i8tk_decode_workspace_bytes)
+ * exceeds the block are refused with I8TK_ERR_WORKSPACE -- on a 148-SM part the
+ * serving shapes need well under 4 MiB; only very many (b,h) rows with a very
+ * short context go over.
+ *
+ * The first call on each device looks up the device address of the block
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * All calls on a device share the one block and it keeps whatever the last
+ * call left there; the kernels overwrite every row they later read, so nothing
+ * has to be cleared.  Two calls that may run on the GPU at the same time
+ * (different streams) would race on it: serialise them, or use the
+ * workspace form above for one of them. */
+size_t i8tk_decode_static_scratch_bytes(void);
+int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_t* K, const int8_t* V,
+                                         void* out_f16,
+                                         const float* sQ, const float* sK, const float* sV,
+                                         int BH, int S, int head_dim, i8tk_stream_t stream);
+
 /* Sequence-sharded form: the same scan over this caller's KV positions, but
  * the result is left as ONE unnormalised online-softmax partial per (b,h):
  *   part[bh] = { m (log2 units), l, 0, 0, acc[0..D) }   -- D+4 floats per row

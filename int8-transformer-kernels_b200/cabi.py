@@ -39,6 +39,8 @@ SIGNATURES = {
     "i8tk_dequantize_int8_to_fp16": (_i, [_vp, _vp, _f, _i64, _vp]),
     "i8tk_decode_workspace_bytes": (_sz, [_i, _i, _i]),
     "i8tk_decode_attention_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "i8tk_decode_static_scratch_bytes": (_sz, []),
+    "i8tk_decode_attention_forward_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "i8tk_decode_attention_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "i8tk_decode_combine_partials": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "i8tk_decode_partial_stride": (_i, [_i]),

@@ -569,6 +569,31 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
     return I8TK_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Scratch for the entry point that allocates nothing: a fixed block of device
+// memory that is part of the library image.  Every GPU that loads the library
+// carries it until the process exits.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 8u << 20;     // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device
+// address.  The address is looked up once per device, with that device current.
+int static_scratch_ptr(void** out) {
+    static void* resolved[64] = {nullptr};
+    int dev = 0;
+    I8TK_CUDA(cudaGetDevice(&dev));
+    I8TK_REQUIRE(dev >= 0 && dev < 64, I8TK_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    if (resolved[dev] == nullptr) {
+        void* p = nullptr;
+        I8TK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        I8TK_REQUIRE(p != nullptr, I8TK_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        resolved[dev] = p;
+    }
+    *out = resolved[dev];
+    return I8TK_OK;
+}
+
 int check_decode_args(const void* Q, const void* K, const void* V, const void* o,
                       const void* sQ, const void* sK, const void* sV, int BH, int S, int D) {
     I8TK_REQUIRE(Q && K && V && o && sQ && sK && sV, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
@@ -623,6 +648,30 @@ extern "C" int i8tk_decode_attention_forward(const int8_t* Q, const int8_t* K, c
                                  workspace, workspace_bytes, st);
     return launch_decode<128>(Q, K, V, static_cast<__half*>(out_f16), nullptr, sQ, sK, sV, BH, S,
                               workspace, workspace_bytes, st);
+}
+
+extern "C" size_t i8tk_decode_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_t* K, const int8_t* V,
+                                                    void* out_f16, const float* sQ, const float* sK,
+                                                    const float* sV, int BH, int S, int head_dim,
+                                                    i8tk_stream_t stream) {
+    int rc = check_decode_args(Q, K, V, out_f16, sQ, sK, sV, BH, S, head_dim);
+    if (rc != I8TK_OK) return rc;
+    const size_t need = workspace_bytes(BH, S, head_dim);
+    I8TK_REQUIRE(need <= kStaticScratchBytes, I8TK_ERR_WORKSPACE,
+                 "this shape needs %zu bytes of scratch; the built-in block holds %zu -- use "
+                 "i8tk_decode_attention_forward with a caller-provided workspace",
+                 need, (size_t)kStaticScratchBytes);
+    void* scratch = nullptr;
+    rc = static_scratch_ptr(&scratch);      // first call on a device resolves the symbol address
+    if (rc != I8TK_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (head_dim == 64)
+        return launch_decode<64>(Q, K, V, static_cast<__half*>(out_f16), nullptr, sQ, sK, sV, BH, S,
+                                 scratch, kStaticScratchBytes, st);
+    return launch_decode<128>(Q, K, V, static_cast<__half*>(out_f16), nullptr, sQ, sK, sV, BH, S,
+                              scratch, kStaticScratchBytes, st);
 }
 
 extern "C" int i8tk_decode_attention_partial(const int8_t* Q, const int8_t* K, const int8_t* V,
