@@ -43,6 +43,17 @@ const char* i8tk_last_error(void);
 /* Library version, major*10000 + minor*100 + patch. */
 int i8tk_version(void);
 
+/* Every device-side wait in this library is bounded.  A kernel that gives up
+ * stores a marker in the first 4 bytes of the workspace it was given and
+ * returns normally (the context stays usable).  i8tk_check_status_word copies
+ * that word back (it synchronises `stream`) and returns
+ * I8TK_ERR_DEVICE_TIMEOUT if the marker is there.  i8tk_selftest_bounded_wait
+ * launches a probe kernel that waits `polls` times (about a microsecond each)
+ * on a barrier nothing signals and then records the marker in *status_word.
+ * Neither has a counterpart in the reference, which checks no CUDA error at all. */
+int i8tk_check_status_word(const void* status_word, i8tk_stream_t stream);
+int i8tk_selftest_bounded_wait(void* status_word, int polls, i8tk_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Per-token symmetric INT8 quantiser.
  * Replaces the torch code tests/test_int8.py:47-63 (quantize_per_token) ==

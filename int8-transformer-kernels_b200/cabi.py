@@ -33,6 +33,8 @@ SIGNATURES = {
     "i8tk_status_string": (ctypes.c_char_p, [_i]),
     "i8tk_last_error": (ctypes.c_char_p, []),
     "i8tk_version": (_i, []),
+    "i8tk_check_status_word": (_i, [_vp, _vp]),
+    "i8tk_selftest_bounded_wait": (_i, [_vp, _i, _vp]),
     "i8tk_quantize_per_token_f32": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "i8tk_quantize_per_token_f16": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "i8tk_quantize_fp16_to_int8": (_i, [_vp, _vp, _vp, _i64, _vp]),

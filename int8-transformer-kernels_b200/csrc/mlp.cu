@@ -31,6 +31,7 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <cstdlib>
 
 namespace i8tk {
 namespace {
@@ -64,6 +65,10 @@ struct EpiParams {
     float* out_absmax;        // [1] or nullptr (atomic max, must start at 0)
     int a_per_row;
     int b_per_col;
+    // fused per-row requantisation (FUSED kernels): int8 C and its row scales
+    int8_t* C8;               // [M, N] int8
+    float* row_scale;         // [M]
+    unsigned int* block_done; // [M / 128] tiles finished per row block (must start at 0)
 };
 
 // ---- tcgen05 / TMA wrappers -------------------------------------------------
@@ -187,7 +192,7 @@ __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
 // C[M,N] fp16 = epilogue( A[M,K] int8 . B[N,K]^T int8 ), persistent over tiles.
 // M % 128 == 0, N % BN == 0, K % 128 == 0.
 // ---------------------------------------------------------------------------
-template <int BN, bool GELU>
+template <int BN, bool GELU, bool FUSED>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                EpiParams ep, int M, int N, int K, uint32_t* __restrict__ status) {
@@ -323,9 +328,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
             float rmax = 0.f;
             const int c0 = half * HC;
-            __half* cblk = ep.C + (size_t)(m0 + q * 32) * N + n0 + c0;   // first row of this warp's block
             unsigned char* cst = cstage_base + ew * (32 * 64);
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c0;
+            uint32_t hv[FUSED ? HC / 2 : 1];              // FUSED: this row's values as packed fp16
             uint32_t r[2][32];
             tmem_ld32(taddr, r[0]);
 #pragma unroll
@@ -348,22 +353,28 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const __half2 h = __floats2half2_rn(v0, v1);
                     packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
                 }
-                // 32 rows x 64 bytes through this warp's staging block so that the
-                // global stores cover whole 64-byte row segments (4 lanes per row).
-                // 16-byte slot j of row r lives at slot j ^ ((r >> 1) & 3): both the
-                // row-wise writes and the 8-rows-at-a-time reads are conflict free.
-                __syncwarp();
+                if constexpr (FUSED) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(cst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
-                        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-                __syncwarp();
+                    for (int j = 0; j < 16; ++j) hv[cc * 16 + j] = packed[j];
+                } else {
+                    // 32 rows x 64 bytes through this warp's staging block so that the
+                    // global stores cover whole 64-byte row segments (4 lanes per row).
+                    // 16-byte slot j of row r lives at slot j ^ ((r >> 1) & 3): both the
+                    // row-wise writes and the 8-rows-at-a-time reads are conflict free.
+                    __half* cblk = ep.C + (size_t)(m0 + q * 32) * N + n0 + c0;
+                    __syncwarp();
 #pragma unroll
-                for (int it = 0; it < 4; ++it) {
-                    const int rr2 = it * 8 + (lane >> 2);
-                    const int j = lane & 3;
-                    const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 64 + ((j ^ ((rr2 >> 1) & 3)) << 4));
-                    *reinterpret_cast<uint4*>(cblk + (size_t)rr2 * N + cc * 32 + j * 8) = v;
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(cst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                            make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (int it = 0; it < 4; ++it) {
+                        const int rr2 = it * 8 + (lane >> 2);
+                        const int j = lane & 3;
+                        const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 64 + ((j ^ ((rr2 >> 1) & 3)) << 4));
+                        *reinterpret_cast<uint4*>(cblk + (size_t)rr2 * N + cc * 32 + j * 8) = v;
+                    }
                 }
             }
             // accumulator buffer drained: hand it back to the MMA warp
@@ -376,6 +387,85 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 float wmax;
                 asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(wmax) : "f"(rmax));
                 if (lane == 0) atomic_max_pos(ep.out_absmax, wmax);
+            }
+
+            if constexpr (FUSED) {
+                // ---- row absmax is complete once every tile of this row block has
+                // published its maxima: count tiles per row block in global memory and
+                // wait (bounded) for the count.  All CTAs are co-resident (grid <= SMs)
+                // and walk the tiles in row-block order, so the tiles being waited for
+                // are running now or next on some other SM. ----
+                const int mb = tile / tiles_n;
+                __threadfence();
+                asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
+                if (et == 0) {
+                    atomicAdd(ep.block_done + mb, 1u);
+                    bool done = false;
+                    for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ep.block_done + mb) : "memory");
+                        if (v >= (unsigned int)tiles_n) { done = true; break; }
+                    }
+                    if (!done) atomicExch(status, kDeviceTimeoutMagic);
+                }
+                asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
+                float amax;
+                asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(amax) : "l"(ep.row_absmax + row) : "memory");
+                amax = fmaxf(amax, 1e-8f);
+                const float inv = 127.f / amax;
+                if (n0 == 0 && half == 0) ep.row_scale[row] = amax / 127.f;
+
+                // ---- quantise the fp16-rounded values (the reference quantises what it
+                // stored as fp16) and write int8, 64 columns = 64 bytes per row at a time
+                // through the same swizzled staging block ----
+                int8_t* c8blk = ep.C8 + (size_t)(m0 + q * 32) * N + n0 + c0;
+#pragma unroll
+                for (int col = 0; col < HC; col += 64) {
+                    constexpr int kFull = 16;                      // words of 4 int8 in a 64-column chunk
+                    const int nw = (HC - col >= 64) ? kFull : (HC - col) / 4;   // 16, or 8 for a 32-column tail
+                    uint32_t w8[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j < nw) {
+                            const int hbase = col / 2 + 2 * j;     // two packed-fp16 words = four values
+                            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&hv[hbase]));
+                            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hv[hbase + 1]));
+                            const int q0 = __float2int_rn(fmaxf(-128.f, fminf(127.f, a.x * inv)));
+                            const int q1 = __float2int_rn(fmaxf(-128.f, fminf(127.f, a.y * inv)));
+                            const int q2 = __float2int_rn(fmaxf(-128.f, fminf(127.f, b.x * inv)));
+                            const int q3 = __float2int_rn(fmaxf(-128.f, fminf(127.f, b.y * inv)));
+                            w8[j] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) |
+                                    ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+                        } else {
+                            w8[j] = 0u;
+                        }
+                    }
+                    const int nslot = nw / 4;                      // 16-byte slots per row: 4 or 2
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (j < nslot)
+                            *reinterpret_cast<uint4*>(cst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                                make_uint4(w8[4 * j], w8[4 * j + 1], w8[4 * j + 2], w8[4 * j + 3]);
+                    __syncwarp();
+                    if (nslot == 4) {
+#pragma unroll
+                        for (int it = 0; it < 4; ++it) {
+                            const int rr2 = it * 8 + (lane >> 2);
+                            const int j = lane & 3;
+                            const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 64 + ((j ^ ((rr2 >> 1) & 3)) << 4));
+                            *reinterpret_cast<uint4*>(c8blk + (size_t)rr2 * N + col + j * 16) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int it = 0; it < 2; ++it) {
+                            const int rr2 = it * 16 + (lane >> 1);
+                            const int j = lane & 1;
+                            const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 64 + ((j ^ ((rr2 >> 1) & 3)) << 4));
+                            *reinterpret_cast<uint4*>(c8blk + (size_t)rr2 * N + col + j * 16) = v;
+                        }
+                    }
+                }
             }
         }
     }
@@ -512,7 +602,7 @@ int sm_count_mlp() {
     return n;
 }
 
-template <int BN, bool GELU>
+template <int BN, bool GELU, bool FUSED>
 int launch_gemm(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, int N, int K,
                 uint32_t* status, cudaStream_t st) {
     using Cfg = GemmCfg<BN>;
@@ -520,7 +610,7 @@ int launch_gemm(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, i
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::SMEM_BYTES));
         attr_done[dev] = true;
     }
@@ -531,13 +621,21 @@ int launch_gemm(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, i
     if (rc != I8TK_OK) return rc;
     const int tiles = (M / BM) * (N / BN);
     const int sms = sm_count_mlp();
-    const int grid = tiles < sms ? tiles : sms;
-    gemm_i8_kernel<BN, GELU><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, status);
+    int grid = tiles < sms ? tiles : sms;
+    if (FUSED) {
+        // CTAs that share a row block wait for one another: keep every round of the
+        // persistent loop on whole row blocks so a block never straddles two rounds.
+        const int tiles_n = N / BN;
+        if (grid > tiles_n) grid = (grid / tiles_n) * tiles_n;
+        I8TK_REQUIRE(tiles_n <= sms, I8TK_ERR_UNSUPPORTED,
+                     "row of %d tiles does not fit one round of %d CTAs", tiles_n, sms);
+    }
+    gemm_i8_kernel<BN, GELU, FUSED><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, status);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }
 
-template <bool GELU>
+template <bool GELU, bool FUSED>
 int launch_gemm_bn(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, int N, int K,
                    uint32_t* status, cudaStream_t st) {
     // Tile width: among the widths that divide N, the one with the least
@@ -553,9 +651,9 @@ int launch_gemm_bn(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M
         const long long cost = ((tiles + sms - 1) / sms) * bn;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
-    if (best == 256) return launch_gemm<256, GELU>(A, BT, ep, M, N, K, status, st);
-    if (best == 192) return launch_gemm<192, GELU>(A, BT, ep, M, N, K, status, st);
-    return launch_gemm<128, GELU>(A, BT, ep, M, N, K, status, st);
+    if (best == 256) return launch_gemm<256, GELU, FUSED>(A, BT, ep, M, N, K, status, st);
+    if (best == 192) return launch_gemm<192, GELU, FUSED>(A, BT, ep, M, N, K, status, st);
+    return launch_gemm<128, GELU, FUSED>(A, BT, ep, M, N, K, status, st);
 }
 
 int requant_grid(long long vecs) {
@@ -571,6 +669,8 @@ struct MlpWorkspace {
     float* hid_absmax;    // [T]
     float* out_absmax;    // [T]   (per-token output)  -- zeroed together with the two below
     float* tensor_absmax; // [1]
+    unsigned int* done1;  // [T/128] row-block tile counters, GEMM1
+    unsigned int* done2;  // [T/128] row-block tile counters, GEMM2
     float* hid_scale;     // [T]
     __half* hid_f16;      // [T, d_ff]
     int8_t* hid_i8;       // [T, d_ff]
@@ -590,6 +690,8 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
     const size_t o_habs = take((size_t)T * 4);
     const size_t o_oabs = take((size_t)T * 4);
     const size_t o_tabs = take(256);
+    const size_t o_d1 = take((size_t)(T / 128 + 1) * 4);
+    const size_t o_d2 = take((size_t)(T / 128 + 1) * 4);
     const size_t zero_end = off;
     const size_t o_hsc = take((size_t)T * 4);
     const size_t o_h16 = take((size_t)T * d_ff * 2);
@@ -607,6 +709,8 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
         w.hid_absmax = reinterpret_cast<float*>(b + o_habs);
         w.out_absmax = reinterpret_cast<float*>(b + o_oabs);
         w.tensor_absmax = reinterpret_cast<float*>(b + o_tabs);
+        w.done1 = reinterpret_cast<unsigned int*>(b + o_d1);
+        w.done2 = reinterpret_cast<unsigned int*>(b + o_d2);
         w.hid_scale = reinterpret_cast<float*>(b + o_hsc);
         w.hid_f16 = reinterpret_cast<__half*>(b + o_h16);
         w.hid_i8 = reinterpret_cast<int8_t*>(b + o_hi8);
@@ -678,26 +782,44 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     const int per_token = (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0;
     const int per_channel = (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0;
 
-    // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), fp16 + row absmax
-    EpiParams e1{scale_x, scale_W1, bias1, w.hid_f16, w.hid_absmax, nullptr, per_token, per_channel};
-    rc = launch_gemm_bn<true>(x, W1T, e1, T, d_ff, d_model, w.status, st);
+    // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token.
+    // Few rows (launch-bound): the epilogue keeps each row's values in registers,
+    // exchanges the row absmax between the CTAs of a row block and writes int8
+    // directly.  Many rows: a row block spans 12-16 CTAs and waiting for all of them
+    // costs more than it saves, so the fp16 hidden goes through a requant pass.
+    static const int fuse_rows_max = [] {
+        const char* e = getenv("I8TK_MLP_FUSE_GEMM1_MAX_ROWS");
+        return e ? atoi(e) : 1024;
+    }();
+    if (T <= fuse_rows_max) {
+        EpiParams e1{scale_x, scale_W1, bias1, nullptr, w.hid_absmax, nullptr, per_token, per_channel,
+                     w.hid_i8, w.hid_scale, w.done1};
+        rc = launch_gemm_bn<true, true>(x, W1T, e1, T, d_ff, d_model, w.status, st);
+        if (rc != I8TK_OK) return rc;
+    } else {
+        EpiParams e1{scale_x, scale_W1, bias1, w.hid_f16, w.hid_absmax, nullptr, per_token, per_channel,
+                     nullptr, nullptr, nullptr};
+        rc = launch_gemm_bn<true, false>(x, W1T, e1, T, d_ff, d_model, w.status, st);
+        if (rc != I8TK_OK) return rc;
+        requant_rows_kernel<false><<<requant_grid((long long)T * d_ff / 16), 256, 0, st>>>(
+            w.hid_f16, w.hid_absmax, w.hid_i8, w.hid_scale, T, d_ff);
+        I8TK_CUDA(cudaGetLastError());
+    }
+    if (out_row_scales) {
+        // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way
+        EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, w.out_absmax, nullptr, 1, per_channel,
+                     out, out_row_scales, w.done2};
+        rc = launch_gemm_bn<false, true>(w.hid_i8, W2T, e2, T, d_model, d_ff, w.status, st);
+        if (rc != I8TK_OK) return rc;
+        return I8TK_OK;
+    }
+    // legacy per-tensor output scale: fp16 out + global absmax, then one requant pass
+    EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, nullptr, w.tensor_absmax, 1, per_channel,
+                 nullptr, nullptr, nullptr};
+    rc = launch_gemm_bn<false, false>(w.hid_i8, W2T, e2, T, d_model, d_ff, w.status, st);
     if (rc != I8TK_OK) return rc;
-    // per-token requant of the hidden
-    requant_rows_kernel<false><<<requant_grid((long long)T * d_ff / 16), 256, 0, st>>>(
-        w.hid_f16, w.hid_absmax, w.hid_i8, w.hid_scale, T, d_ff);
-    I8TK_CUDA(cudaGetLastError());
-    // GEMM2: out = (hidden_i8 . W2) * sh * sW2, fp16 + absmax
-    EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16,
-                 out_row_scales ? w.out_absmax : nullptr,
-                 out_row_scales ? nullptr : w.tensor_absmax, 1, per_channel};
-    rc = launch_gemm_bn<false>(w.hid_i8, W2T, e2, T, d_model, d_ff, w.status, st);
-    if (rc != I8TK_OK) return rc;
-    if (out_row_scales)
-        requant_rows_kernel<false><<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
-            w.out_f16, w.out_absmax, out, out_row_scales, T, d_model);
-    else
-        requant_rows_kernel<true><<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
-            w.out_f16, w.tensor_absmax, out, out_tensor_scale, T, d_model);
+    requant_rows_kernel<true><<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
+        w.out_f16, w.tensor_absmax, out, out_tensor_scale, T, d_model);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }
