@@ -26,8 +26,9 @@
 // * Every wait on an mbarrier is bounded; on a timeout the kernel records a
 //   status word, all roles fall through to the common exit and TMEM is freed.
 //
-// Weights are consumed as [N][K] (K contiguous).  Callers that hold the
-// reference's [K][N] layout get them transposed into the workspace first.
+// Weights are consumed either prepacked as [N][K] (K-major operand) or as the
+// reference holds them, [K][N], through MN-major operand descriptors -- no
+// transpose pass in either case.
 #include "common.cuh"
 
 #include <cuda.h>
@@ -124,10 +125,20 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
            (2ull << 61);
 }
 
+// Same for an MN-major operand (the weight as the caller holds it: [K][N] with N
+// contiguous).  TMA lays each 128-wide slab of N down as rows of 128 bytes, one
+// row per k, swizzled in 8-row groups: 8-row groups are 1024 bytes apart
+// (stride-byte-offset), 128-wide slabs `slab_bytes` apart (leading-byte-offset).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t slab_bytes) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((slab_bytes >> 4) & 0x3FFFu) << 16) |
+           (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
 // Instruction descriptor: D = s32 (2 @ bit 4), A = B = signed int8 (1 @ bits 7, 10),
 // both K-major, N/8 @ bit 17, M/16 @ bit 24.
-__host__ __device__ constexpr uint32_t idesc_i8(int M, int N) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+__host__ __device__ constexpr uint32_t idesc_i8(int M, int N, bool b_mn_major = false) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread
@@ -195,7 +206,7 @@ __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
 template <int BN, bool GELU, bool FUSED>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               EpiParams ep, int M, int N, int K, uint32_t* __restrict__ status) {
+               EpiParams ep, int M, int N, int K, int b_mn, uint32_t* __restrict__ status) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
 
@@ -257,14 +268,22 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t sa = base_s + st * Cfg::STAGE_BYTES;
                     mbar_expect_tx(full0 + 8 * st, Cfg::STAGE_BYTES);
                     tma_load_2d(sa, &tmA, kb * BK, m0, full0 + 8 * st);
-                    tma_load_2d(sa + Cfg::A_BYTES, &tmB, kb * BK, n0, full0 + 8 * st);
+                    if (!b_mn) {
+                        tma_load_2d(sa + Cfg::A_BYTES, &tmB, kb * BK, n0, full0 + 8 * st);
+                    } else {
+                        // weight held as [K][N]: one box of 128 k-rows x 128 n-bytes per 128-wide slab
+#pragma unroll
+                        for (int j = 0; j < BN / 128; ++j)
+                            tma_load_2d(sa + Cfg::A_BYTES + j * (128 * BK), &tmB, n0 + j * 128, kb * BK,
+                                        full0 + 8 * st);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (elect_one()) {
-            constexpr uint32_t idesc = idesc_i8(BM, BN);
+            const uint32_t idesc = idesc_i8(BM, BN, b_mn != 0);
             int it = 0, lt = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
@@ -285,10 +304,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tc_fence_after();
                     const uint32_t sa = base_s + st * Cfg::STAGE_BYTES;
                     const uint64_t da = smem_desc_sw128(sa);
-                    const uint64_t db = smem_desc_sw128(sa + Cfg::A_BYTES);
+                    const uint64_t db = b_mn ? smem_desc_sw128_mn(sa + Cfg::A_BYTES, 128 * BK)
+                                             : smem_desc_sw128(sa + Cfg::A_BYTES);
+                    // per instruction 32 of K: K-major operands advance 32 bytes (+2 in 16-byte
+                    // units); the MN-major one advances 32 rows of 128 bytes (+256)
+                    const uint32_t db_step = b_mn ? 256u : 2u;
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k)     // 32 bytes of K per instruction: +2 in 16-byte units
-                        mma_i8(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < BK / 32; ++k)
+                        mma_i8(tmem_d, da + 2 * k, db + (uint64_t)(db_step * k), idesc, (kb | k) != 0);
                     tc_commit(empty0 + 8 * st);           // stage reusable when these MMAs retire
                 }
                 if (ok) tc_commit(tfull0 + 8 * buf);      // accumulator complete
@@ -595,6 +618,21 @@ int make_map(CUtensorMap* map, const int8_t* ptr, int rows, int cols, int box_ro
     return I8TK_OK;
 }
 
+// int8 weight [K][N] row-major (N contiguous): box of 128 k-rows x 128 n-bytes, 128-byte swizzle
+int make_map_mn(CUtensorMap* map, const int8_t* ptr, int K, int N) {
+    EncodeTiledFn fn = encode_fn();
+    I8TK_REQUIRE(fn != nullptr, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
+    const cuuint64_t strides[1] = {(cuuint64_t)N};
+    const cuuint32_t box[2] = {128u, (cuuint32_t)BK};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(ptr), dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    I8TK_REQUIRE(r == CUDA_SUCCESS, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return I8TK_OK;
+}
+
 int sm_count_mlp() {
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 148;
@@ -603,7 +641,7 @@ int sm_count_mlp() {
 }
 
 template <int BN, bool GELU, bool FUSED>
-int launch_gemm(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, int N, int K,
+int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                 uint32_t* status, cudaStream_t st) {
     using Cfg = GemmCfg<BN>;
     static bool attr_done[64] = {false};
@@ -617,7 +655,7 @@ int launch_gemm(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, i
     CUtensorMap tmA, tmB;
     int rc = make_map(&tmA, A, M, K, BM);
     if (rc != I8TK_OK) return rc;
-    rc = make_map(&tmB, BT, N, K, BN);
+    rc = b_mn ? make_map_mn(&tmB, B, K, N) : make_map(&tmB, B, N, K, BN);
     if (rc != I8TK_OK) return rc;
     const int tiles = (M / BM) * (N / BN);
     const int sms = sm_count_mlp();
@@ -630,13 +668,13 @@ int launch_gemm(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, i
         I8TK_REQUIRE(tiles_n <= sms, I8TK_ERR_UNSUPPORTED,
                      "row of %d tiles does not fit one round of %d CTAs", tiles_n, sms);
     }
-    gemm_i8_kernel<BN, GELU, FUSED><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, status);
+    gemm_i8_kernel<BN, GELU, FUSED><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }
 
 template <bool GELU, bool FUSED>
-int launch_gemm_bn(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M, int N, int K,
+int launch_gemm_bn(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                    uint32_t* status, cudaStream_t st) {
     // Tile width: among the widths that divide N, the one with the least
     // (rounds of CTAs over the SMs) x (tile width); ties go to the wider tile.
@@ -647,13 +685,14 @@ int launch_gemm_bn(const int8_t* A, const int8_t* BT, const EpiParams& ep, int M
     for (int i = 0; i < 3; ++i) {
         const int bn = widths[i];
         if (N % bn) continue;
+        if (b_mn && bn % 128) continue;          // [K][N] weights come in 128-wide slabs
         const long long tiles = (long long)(M / BM) * (N / bn);
         const long long cost = ((tiles + sms - 1) / sms) * bn;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
-    if (best == 256) return launch_gemm<256, GELU, FUSED>(A, BT, ep, M, N, K, status, st);
-    if (best == 192) return launch_gemm<192, GELU, FUSED>(A, BT, ep, M, N, K, status, st);
-    return launch_gemm<128, GELU, FUSED>(A, BT, ep, M, N, K, status, st);
+    if (best == 256) return launch_gemm<256, GELU, FUSED>(A, B, b_mn, ep, M, N, K, status, st);
+    if (best == 192) return launch_gemm<192, GELU, FUSED>(A, B, b_mn, ep, M, N, K, status, st);
+    return launch_gemm<128, GELU, FUSED>(A, B, b_mn, ep, M, N, K, status, st);
 }
 
 int requant_grid(long long vecs) {
@@ -766,16 +805,25 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     I8TK_REQUIRE(aligned_to(workspace, 256), I8TK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
+    // Weights as the caller holds them ([K][N], N contiguous) are read in place through
+    // MN-major operand descriptors; I8TK_MLP_TRANSPOSE_WEIGHTS=1 restores the older route
+    // that transposes them into the workspace on every call (kept for A/B checks).
+    static const bool force_transpose = [] {
+        const char* e = getenv("I8TK_MLP_TRANSPOSE_WEIGHTS");
+        return e && atoi(e) != 0;
+    }();
     const int8_t* W1T = W1;
     const int8_t* W2T = W2;
+    bool b_mn = !(flags & I8TK_MLP_PREPACKED);
     int rc;
-    if (!(flags & I8TK_MLP_PREPACKED)) {
+    if (b_mn && force_transpose) {
         rc = transpose_i8(W1, w.w1t, d_model, d_ff, st);
         if (rc != I8TK_OK) return rc;
         rc = transpose_i8(W2, w.w2t, d_ff, d_model, st);
         if (rc != I8TK_OK) return rc;
         W1T = w.w1t;
         W2T = w.w2t;
+        b_mn = false;
     }
     I8TK_CUDA(cudaMemsetAsync(w.hid_absmax, 0, w.zero_bytes, st));
 
@@ -794,12 +842,12 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     if (T <= fuse_rows_max) {
         EpiParams e1{scale_x, scale_W1, bias1, nullptr, w.hid_absmax, nullptr, per_token, per_channel,
                      w.hid_i8, w.hid_scale, w.done1};
-        rc = launch_gemm_bn<true, true>(x, W1T, e1, T, d_ff, d_model, w.status, st);
+        rc = launch_gemm_bn<true, true>(x, W1T, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
     } else {
         EpiParams e1{scale_x, scale_W1, bias1, w.hid_f16, w.hid_absmax, nullptr, per_token, per_channel,
                      nullptr, nullptr, nullptr};
-        rc = launch_gemm_bn<true, false>(x, W1T, e1, T, d_ff, d_model, w.status, st);
+        rc = launch_gemm_bn<true, false>(x, W1T, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
         requant_rows_kernel<false><<<requant_grid((long long)T * d_ff / 16), 256, 0, st>>>(
             w.hid_f16, w.hid_absmax, w.hid_i8, w.hid_scale, T, d_ff);
@@ -809,14 +857,14 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
         // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way
         EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, w.out_absmax, nullptr, 1, per_channel,
                      out, out_row_scales, w.done2};
-        rc = launch_gemm_bn<false, true>(w.hid_i8, W2T, e2, T, d_model, d_ff, w.status, st);
+        rc = launch_gemm_bn<false, true>(w.hid_i8, W2T, b_mn, e2, T, d_model, d_ff, w.status, st);
         if (rc != I8TK_OK) return rc;
         return I8TK_OK;
     }
     // legacy per-tensor output scale: fp16 out + global absmax, then one requant pass
     EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, nullptr, w.tensor_absmax, 1, per_channel,
                  nullptr, nullptr, nullptr};
-    rc = launch_gemm_bn<false, false>(w.hid_i8, W2T, e2, T, d_model, d_ff, w.status, st);
+    rc = launch_gemm_bn<false, false>(w.hid_i8, W2T, b_mn, e2, T, d_model, d_ff, w.status, st);
     if (rc != I8TK_OK) return rc;
     requant_rows_kernel<true><<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
         w.out_f16, w.tensor_absmax, out, out_tensor_scale, T, d_model);
