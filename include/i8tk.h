@@ -146,6 +146,32 @@ int i8tk_decode_attention_partial(const int8_t* Q, const int8_t* K, const int8_t
 int i8tk_decode_combine_partials(const float* parts, int nparts, int BH, int head_dim,
                                  void* out_f16, i8tk_stream_t stream);
 
+/* KV-sequence-sharded decode with the exchange fused into the merge kernel:
+ * every rank (one process per GPU) calls this at the same step with its own
+ * chunk of the KV sequence (S_local positions, may be 0).  The kernel merges
+ * the local partials, stores the merged (m, l, acc) row of each (b,h) straight
+ * into every rank's gather buffer through peer-mapped pointers (NVLink), sets a
+ * per-CTA flag there, waits -- bounded -- for the other ranks' flags and writes
+ * the final fp16 result on every rank.  No collective library is involved.
+ *   peer_parts  device array of `world` pointers: rank r's gather buffer,
+ *               2 * world * BH * (D+4) floats, mapped into this process
+ *   peer_flags  device array of `world` pointers: rank r's flag array,
+ *               world * i8tk_decode_exchange_ctas(BH) 32-bit words, zeroed once
+ *   epoch       1 on the first call, +1 on every call, the same on all ranks
+ * The buffers must be peer-accessible allocations (e.g. torch symmetric
+ * memory).  Extends the partial/combine hand-off of
+ * kernels/int8_decode_attention.cu:389-426 across GPUs; no counterpart in the
+ * reference, which is single-GPU. */
+int i8tk_decode_exchange_ctas(int BH);
+int i8tk_decode_attention_seq_sharded(const int8_t* Q, const int8_t* K, const int8_t* V,
+                                      void* out_f16,
+                                      const float* sQ, const float* sK, const float* sV,
+                                      int BH, int S_local, int head_dim,
+                                      void* workspace, size_t workspace_bytes,
+                                      const void* peer_parts, const void* peer_flags,
+                                      int rank, int world, unsigned int epoch,
+                                      i8tk_stream_t stream);
+
 /* Floats per (b,h) row of a partial: head_dim + 4. */
 int i8tk_decode_partial_stride(int head_dim);
 

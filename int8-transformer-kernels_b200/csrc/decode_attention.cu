@@ -459,6 +459,136 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, Decode
 }
 
 // ---------------------------------------------------------------------------
+// Pass 2 for the KV-sequence-sharded path, fused with the exchange between
+// GPUs.  Every rank runs this kernel at the same time (one process per GPU).
+// CTA c of every rank handles the same four (b,h) rows:
+//   1. merge this rank's own partial rows of a (b,h) into one (m, l, acc) row,
+//   2. store that row into slot [rank] of EVERY rank's gather buffer -- plain
+//      stores through peer-mapped pointers, NVLink/NVSwitch carries them --
+//   3. fence, then set flag [rank][c] = epoch on every rank,
+//   4. wait (bounded) until flags [r][c] of all ranks r show this epoch in the
+//      local flag array, then merge the world-size rows and write fp16.
+// No collective library call, no host round trip; the only data crossing the
+// links are the rows themselves (B*H*(D+4) floats per rank pair).
+// `peer_parts[r]` / `peer_flags[r]` are rank r's buffers as mapped into this
+// process ([2][world][BH][D+4] floats and [world][gridDim.x] words, flags zeroed
+// once at set-up); `epoch` starts at 1 and increases by one per call on all ranks.
+// ---------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128)
+decode_exchange_kernel(const float* __restrict__ rows, int BH, DecodePlan plan, int empty,
+                       float* const* __restrict__ peer_parts, uint32_t* const* __restrict__ peer_flags,
+                       int rank, int world, uint32_t epoch, __half* __restrict__ out,
+                       uint32_t* __restrict__ status) {
+    constexpr int ROW = D + 4;
+    constexpr int DPL = D / 32;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int bh = blockIdx.x * 4 + warp;
+    const bool active = bh < BH;
+
+    // ---- 1. local merge ------------------------------------------------------
+    float gm = -INFINITY, L = 0.f;
+    float a[DPL];
+#pragma unroll
+    for (int k = 0; k < DPL; ++k) a[k] = 0.f;
+    if (active && !empty) {
+        const long long fb = (long long)bh * plan.tpb;
+        const int c_first = (int)(fb / plan.tpc);
+        const int n = ((int)((fb + plan.tpb - 1) / plan.tpc) - c_first + 1) * kConsumers;
+        auto row_ptr = [&](int i) -> const float* {
+            const int cta = c_first + i / kConsumers;
+            const int seg = bh - (int)(((long long)cta * plan.tpc) / plan.tpb);
+            return rows + (((size_t)cta * plan.maxseg + seg) * kConsumers + i % kConsumers) * ROW;
+        };
+        for (int i = lane; i < n; i += 32) {
+            const float2 ml = *reinterpret_cast<const float2*>(row_ptr(i));
+            if (ml.y > 0.f) gm = fmaxf(gm, ml.x);
+        }
+        gm = warp_max(gm);
+        for (int i = 0; i < n; ++i) {
+            const float* r = row_ptr(i);
+            const float2 ml = *reinterpret_cast<const float2*>(r);
+            if (ml.y <= 0.f) continue;
+            const float wgt = ex2_approx(ml.x - gm);
+            L = fmaf(ml.y, wgt, L);
+#pragma unroll
+            for (int k = 0; k < DPL; ++k) a[k] = fmaf(r[4 + lane * DPL + k], wgt, a[k]);
+        }
+        if (!(L > 0.f)) gm = -INFINITY;
+    }
+
+    // ---- 2. push the row to every rank (own slot included) ---------------------
+    if (active) {
+        for (int p = 0; p < world; ++p) {
+            float* dst = peer_parts[p] + (((size_t)(epoch & 1u) * world + rank) * BH + bh) * ROW;
+            if (lane == 0) *reinterpret_cast<float4*>(dst) = make_float4(gm, L, 0.f, 0.f);
+            if constexpr (DPL == 4)
+                *reinterpret_cast<float4*>(dst + 4 + lane * 4) = make_float4(a[0], a[1], a[2], a[3]);
+            else
+                *reinterpret_cast<float2*>(dst + 4 + lane * 2) = make_float2(a[0], a[1]);
+        }
+    }
+    // ---- 3. publish -------------------------------------------------------------
+    __threadfence_system();
+    __syncthreads();
+    const int slot = blockIdx.x;
+    if (threadIdx.x < world) {
+        uint32_t* f = peer_flags[threadIdx.x] + (size_t)rank * gridDim.x + slot;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    }
+    // ---- 4. wait for every rank's rows of this CTA, then merge -------------------
+    if (threadIdx.x < world) {
+        const uint32_t* f = peer_flags[rank] + (size_t)threadIdx.x * gridDim.x + slot;
+        bool seen = false;
+        for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int32_t)(v - epoch) >= 0) { seen = true; break; }
+        }
+        if (!seen) atomicExch(status, kDeviceTimeoutMagic);
+    }
+    __syncthreads();
+    if (!active) return;
+
+    // two gather buffers, alternated by epoch parity: a fast rank may already be pushing the
+    // next call's rows while a slow one is still reading this call's
+    const float* mine = peer_parts[rank] + (size_t)(epoch & 1u) * world * BH * ROW;
+    float gm2 = -INFINITY;
+    for (int r = lane; r < world; r += 32) {
+        const float* rp = mine + ((size_t)r * BH + bh) * ROW;
+        const float m_r = __ldcg(rp), l_r = __ldcg(rp + 1);
+        if (l_r > 0.f) gm2 = fmaxf(gm2, m_r);
+    }
+    gm2 = warp_max(gm2);
+    float L2 = 0.f;
+    float b[DPL];
+#pragma unroll
+    for (int k = 0; k < DPL; ++k) b[k] = 0.f;
+    for (int r = 0; r < world; ++r) {
+        const float* rp = mine + ((size_t)r * BH + bh) * ROW;
+        const float m_r = __ldcg(rp), l_r = __ldcg(rp + 1);
+        if (l_r <= 0.f) continue;
+        const float wgt = ex2_approx(m_r - gm2);
+        L2 = fmaf(l_r, wgt, L2);
+#pragma unroll
+        for (int k = 0; k < DPL; ++k) b[k] = fmaf(__ldcg(rp + 4 + lane * DPL + k), wgt, b[k]);
+    }
+    const float inv = 1.0f / L2;
+    __half* o = out + (size_t)bh * D + lane * DPL;
+    if constexpr (DPL == 4) {
+        __half2 h0 = __floats2half2_rn(b[0] * inv, b[1] * inv);
+        __half2 h1 = __floats2half2_rn(b[2] * inv, b[3] * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&h0);
+        pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        *reinterpret_cast<uint2*>(o) = pk;
+    } else {
+        *reinterpret_cast<__half2*>(o) = __floats2half2_rn(b[0] * inv, b[1] * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
 // Optional timing probe: events recorded on the launch stream immediately
@@ -672,6 +802,59 @@ extern "C" int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_
                                  scratch, kStaticScratchBytes, st);
     return launch_decode<128>(Q, K, V, static_cast<__half*>(out_f16), nullptr, sQ, sK, sV, BH, S,
                               scratch, kStaticScratchBytes, st);
+}
+
+extern "C" int i8tk_decode_exchange_ctas(int BH) { return BH > 0 ? (BH + 3) / 4 : 0; }
+
+extern "C" int i8tk_decode_attention_seq_sharded(const int8_t* Q, const int8_t* K, const int8_t* V,
+                                                 void* out_f16, const float* sQ, const float* sK,
+                                                 const float* sV, int BH, int S_local, int head_dim,
+                                                 void* workspace, size_t workspace_bytes,
+                                                 const void* peer_parts, const void* peer_flags,
+                                                 int rank, int world, unsigned int epoch,
+                                                 i8tk_stream_t stream) {
+    I8TK_REQUIRE(Q && out_f16 && sQ && workspace && peer_parts && peer_flags, I8TK_ERR_INVALID_ARGUMENT,
+                 "null pointer argument");
+    I8TK_REQUIRE(BH > 0 && S_local >= 0, I8TK_ERR_INVALID_ARGUMENT, "BH must be positive and S_local >= 0");
+    I8TK_REQUIRE(world >= 1 && world <= 32 && rank >= 0 && rank < world, I8TK_ERR_INVALID_ARGUMENT,
+                 "need 0 <= rank < world <= 32 (rank=%d world=%d)", rank, world);
+    I8TK_REQUIRE(epoch != 0, I8TK_ERR_INVALID_ARGUMENT, "epoch starts at 1");
+    I8TK_REQUIRE(head_dim == 64 || head_dim == 128, I8TK_ERR_UNSUPPORTED,
+                 "decode attention supports head_dim 64 or 128 (got %d)", head_dim);
+    I8TK_REQUIRE(aligned_to(workspace, 256) && workspace_bytes >= 256, I8TK_ERR_WORKSPACE,
+                 "workspace must be 256-byte aligned and at least 256 bytes");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t* status = reinterpret_cast<uint32_t*>(workspace);
+    float* rows = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 256);
+    DecodePlan p{};
+    if (S_local > 0) {
+        const int rc = check_decode_args(Q, K, V, out_f16, sQ, sK, sV, BH, S_local, head_dim);
+        if (rc != I8TK_OK) return rc;
+        p = make_plan(BH, S_local, head_dim, sm_count());
+        const size_t need = 256 + rows_bytes(p, head_dim);
+        I8TK_REQUIRE(workspace_bytes >= need, I8TK_ERR_WORKSPACE,
+                     "decode workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
+        const bool bulk = (S_local % 4 == 0) && aligned_to(sK, 16) && aligned_to(sV, 16);
+        int rc2;
+        if (head_dim == 64)
+            rc2 = bulk ? launch_partial<64, true>(Q, K, V, sQ, sK, sV, rows, S_local, p, status, st)
+                       : launch_partial<64, false>(Q, K, V, sQ, sK, sV, rows, S_local, p, status, st);
+        else
+            rc2 = bulk ? launch_partial<128, true>(Q, K, V, sQ, sK, sV, rows, S_local, p, status, st)
+                       : launch_partial<128, false>(Q, K, V, sQ, sK, sV, rows, S_local, p, status, st);
+        if (rc2 != I8TK_OK) return rc2;
+    }
+    const int grid = (BH + 3) / 4;
+    float* const* pp = static_cast<float* const*>(peer_parts);
+    uint32_t* const* pf = static_cast<uint32_t* const*>(peer_flags);
+    if (head_dim == 64)
+        decode_exchange_kernel<64><<<grid, 128, 0, st>>>(rows, BH, p, S_local == 0, pp, pf, rank, world,
+                                                         epoch, static_cast<__half*>(out_f16), status);
+    else
+        decode_exchange_kernel<128><<<grid, 128, 0, st>>>(rows, BH, p, S_local == 0, pp, pf, rank, world,
+                                                          epoch, static_cast<__half*>(out_f16), status);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
 }
 
 extern "C" int i8tk_decode_attention_partial(const int8_t* Q, const int8_t* K, const int8_t* V,

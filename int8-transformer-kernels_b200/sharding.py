@@ -69,3 +69,71 @@ def decode_attention_seq_sharded(Q, K_local, V_local, sQ, sK_local, sV_local, gr
     parts = torch.empty(world * B, H, D + 4, dtype=torch.float32, device=Q.device)
     dist.all_gather_into_tensor(parts, part.contiguous(), group=group)
     return combine_fn(parts.view(world, B, H, D + 4))
+
+
+class SeqShardedDecoder:
+    """KV-sequence-sharded decode with the exchange fused into the merge kernel.
+
+    Set up once per (B, H, D) and process group; every call runs, on each rank,
+    the streaming kernel over the local KV chunk and then ONE kernel that merges
+    the local partials, stores the merged rows into every rank's gather buffer
+    through peer-mapped pointers (NVLink), signals, waits (bounded) for the other
+    ranks and writes the fp16 result (``i8tk_decode_attention_seq_sharded``).
+    The gather buffers and flags live in torch symmetric memory; no NCCL call is
+    made on the data path.  All ranks must call in the same order.
+    """
+
+    def __init__(self, B, H, D, device, group=None, max_local_positions=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import cabi
+        self._cabi = cabi
+        self._lib = cabi.load()
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.B, self.H, self.D = B, H, D
+        self.device = torch.device(device)
+        BH = B * H
+        ctas = self._lib.i8tk_decode_exchange_ctas(BH)
+        self._parts = symm_mem.empty(2 * self.world * BH * (D + 4), dtype=torch.float32, device=self.device)
+        self._flags = symm_mem.empty(self.world * ctas, dtype=torch.int32, device=self.device)
+        self._parts.zero_()
+        self._flags.zero_()
+        self._parts_hdl = symm_mem.rendezvous(self._parts, self.group)
+        self._flags_hdl = symm_mem.rendezvous(self._flags, self.group)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)              # every rank's flags are zero before anyone signals
+        self._epoch = 0
+        self._ws = None
+        self._ws_bytes = 0
+
+    def _workspace(self, BH, S_local):
+        need = max(256, self._lib.i8tk_decode_workspace_bytes(BH, S_local, self.D) if S_local > 0 else 256)
+        if need > self._ws_bytes:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+            self._ws_bytes = need
+        return self._ws
+
+    def __call__(self, Q, K_local, V_local, sQ, sK_local, sV_local):
+        B, H, D = Q.shape
+        assert (B, H, D) == (self.B, self.H, self.D), "shape differs from the one set up"
+        S_local = int(K_local.shape[2])
+        BH = B * H
+        ws = self._workspace(BH, S_local)
+        out = torch.empty(B, H, D, dtype=torch.float16, device=self.device)
+        self._epoch += 1
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.i8tk_decode_attention_seq_sharded(
+            Q.data_ptr(), K_local.data_ptr() if S_local else None, V_local.data_ptr() if S_local else None,
+            out.data_ptr(), sQ.data_ptr(), sK_local.data_ptr() if S_local else None,
+            sV_local.data_ptr() if S_local else None, BH, S_local, D, ws.data_ptr(), self._ws_bytes,
+            self._parts_hdl.buffer_ptrs_dev, self._flags_hdl.buffer_ptrs_dev, self.rank, self.world,
+            self._epoch, stream)
+        self._cabi.check(rc, "i8tk_decode_attention_seq_sharded")
+        return out
+
+    def check(self):
+        """Synchronises and raises if a bounded device-side wait gave up (a rank never arrived)."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        if self._ws is not None:
+            self._cabi.check(self._lib.i8tk_check_status_word(self._ws.data_ptr(), stream), "seq-sharded decode")
