@@ -186,6 +186,26 @@ int i8tk_decode_set_probe_events(void* start_event, void* stop_event);
 int i8tk_decode_plan(int BH, int S, int head_dim, int* nctas, int* tiles_per_cta);
 
 /* ------------------------------------------------------------------------
+ * INT8 prefill attention (seq_q == seq_kv, no causal mask), per-token scales.
+ * Replaces int8_attention_forward (kernels/int8_ext.cu:28-32,
+ * kernels/int8_attention.cu:926-1028).
+ *   Q, K, V  [batch, heads, seq_len, head_dim] int8, contiguous
+ *   sQ, sK, sV  fp32 [batch*heads*seq_len]
+ *   out      [batch, heads, seq_len, head_dim] fp16
+ * score[i][j] = (q_i.k_j) * sQ_i * sK_j / sqrt(D); P*sV and V go through fp16
+ * into an fp32 accumulator, as in the reference.  head_dim 64 or 128 and
+ * seq_len a multiple of 128 (the reference's tensor-core path needs 64; its
+ * scalar fallback for other shapes is not reproduced): anything else returns
+ * I8TK_ERR_UNSUPPORTED.  workspace: i8tk_attention_workspace_bytes() bytes,
+ * 256-byte aligned (holds the status word).
+ * ---------------------------------------------------------------------- */
+size_t i8tk_attention_workspace_bytes(void);
+int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V, void* out_f16,
+                           const float* sQ, const float* sK, const float* sV,
+                           int batch, int heads, int seq_len, int head_dim,
+                           void* workspace, size_t workspace_bytes, i8tk_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Fused INT8 MLP:  out = requant( (requant(GELU((x.W1)*sx*sW1 + b1))) . W2 * sh * sW2 )
  * Replaces int8_mlp_forward, int8_mlp_forward_per_channel,
  * int8_mlp_forward_per_channel_bias and int8_mlp_forward_prepacked

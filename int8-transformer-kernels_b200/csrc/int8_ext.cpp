@@ -127,6 +127,43 @@ torch::Tensor int8_decode_combine_partials_torch(torch::Tensor parts) {
     return out;
 }
 
+// ---- prefill attention (kernels/int8_ext.cu:83-129) -----------------------------
+torch::Tensor int8_attention_forward_torch(torch::Tensor Q, torch::Tensor K, torch::Tensor V,
+                                           torch::Tensor scale_Q, torch::Tensor scale_K,
+                                           torch::Tensor scale_V) {
+    TORCH_CHECK(Q.device().is_cuda(), "Q must be a CUDA tensor");
+    TORCH_CHECK(Q.dtype() == torch::kInt8, "Q must be int8");
+    TORCH_CHECK(K.dtype() == torch::kInt8, "K must be int8");
+    TORCH_CHECK(V.dtype() == torch::kInt8, "V must be int8");
+    TORCH_CHECK(Q.is_contiguous(), "Q must be contiguous");
+    TORCH_CHECK(K.is_contiguous(), "K must be contiguous");
+    TORCH_CHECK(V.is_contiguous(), "V must be contiguous");
+    TORCH_CHECK(Q.dim() == 4, "expected (batch, heads, seq_len, head_dim)");
+    TORCH_CHECK(Q.sizes() == K.sizes() && Q.sizes() == V.sizes(), "Q/K/V shape mismatch");
+    TORCH_CHECK(scale_Q.dtype() == torch::kFloat32, "scale_Q must be float32");
+    TORCH_CHECK(scale_K.dtype() == torch::kFloat32, "scale_K must be float32");
+    TORCH_CHECK(scale_V.dtype() == torch::kFloat32, "scale_V must be float32");
+    TORCH_CHECK(scale_Q.device().is_cuda(), "scale_Q must be CUDA");
+    const int64_t batch = Q.size(0), heads = Q.size(1), seq_len = Q.size(2), head_dim = Q.size(3);
+    const int64_t n_tokens = batch * heads * seq_len;
+    TORCH_CHECK(n_tokens < (1ll << 31), "shape too large");
+    auto sQ = scale_Q.contiguous().view({n_tokens});
+    auto sK = scale_K.contiguous().view({n_tokens});
+    auto sV = scale_V.contiguous().view({n_tokens});
+    c10::cuda::CUDAGuard guard(Q.device());
+    auto out = torch::empty({batch, heads, seq_len, head_dim},
+                            torch::TensorOptions().dtype(torch::kFloat16).device(Q.device()));
+    const size_t wbytes = i8tk_attention_workspace_bytes();
+    auto ws = make_workspace(wbytes, Q.device());
+    check_status(i8tk_attention_forward(Q.data_ptr<int8_t>(), K.data_ptr<int8_t>(), V.data_ptr<int8_t>(),
+                                        out.data_ptr(), sQ.data_ptr<float>(), sK.data_ptr<float>(),
+                                        sV.data_ptr<float>(), static_cast<int>(batch), static_cast<int>(heads),
+                                        static_cast<int>(seq_len), static_cast<int>(head_dim), ws.data_ptr(),
+                                        wbytes, current_stream()),
+                 "int8_attention_forward");
+    return out;
+}
+
 // ---- per-token quantiser (tests/test_int8.py:47-63) ---------------------------
 std::tuple<torch::Tensor, torch::Tensor> quantize_per_token_torch(torch::Tensor t) {
     TORCH_CHECK(t.device().is_cuda(), "t must be a CUDA tensor");
@@ -159,6 +196,8 @@ std::tuple<torch::Tensor, torch::Tensor> quantize_per_token_torch(torch::Tensor 
 #include "int8_ext_mlp.inc"
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("int8_attention_forward", &int8_attention_forward_torch,
+          "INT8 attention with per-token quantization (CUDA) — returns FP16");
     m.def("int8_decode_attention_forward", &int8_decode_attention_forward_torch,
           "INT8 flash-decoding attention (seq_q==1, INT8 KV cache) — returns FP16");
     m.def("int8_decode_attention_partial", &int8_decode_attention_partial_torch,

@@ -29,9 +29,8 @@
 // Weights are consumed either prepacked as [N][K] (K-major operand) or as the
 // reference holds them, [K][N], through MN-major operand descriptors -- no
 // transpose pass in either case.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
-#include <cuda.h>
 #include <cstdlib>
 
 namespace i8tk {
@@ -71,114 +70,6 @@ struct EpiParams {
     float* row_scale;         // [M]
     unsigned int* block_done; // [M / 128] tiles finished per row block (must start at 0)
 };
-
-// ---- tcgen05 / TMA wrappers -------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_dst), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-// mbarrier arrives once all tcgen05 operations issued so far by this thread retire
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar) : "memory");
-}
-
-// D[tmem] (+)= A[smem] * B[smem], int8 x int8 -> int32
-__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                       uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
-// 128 bytes, 8-row groups 1024 bytes apart (stride-byte-offset), descriptor
-// version 1 (sm_100), swizzle mode 2 (128 B).  Addresses in 16-byte units.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
-           (2ull << 61);
-}
-
-// Same for an MN-major operand (the weight as the caller holds it: [K][N] with N
-// contiguous).  TMA lays each 128-wide slab of N down as rows of 128 bytes, one
-// row per k, swizzled in 8-row groups: 8-row groups are 1024 bytes apart
-// (stride-byte-offset), 128-wide slabs `slab_bytes` apart (leading-byte-offset).
-__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t slab_bytes) {
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((slab_bytes >> 4) & 0x3FFFu) << 16) |
-           (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// Instruction descriptor: D = s32 (2 @ bit 4), A = B = signed int8 (1 @ bits 7, 10),
-// both K-major, N/8 @ bit 17, M/16 @ bit 24.
-__host__ __device__ constexpr uint32_t idesc_i8(int M, int N, bool b_mn_major = false) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
-           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-
-// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-// Waits for this thread's outstanding tcgen05.ld.  The registers of the block
-// about to be used are listed as in/out operands so the compiler cannot move
-// a read of them above the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.wait::ld.sync.aligned;"
-        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
-          "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
-          "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]),
-          "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]),
-          "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-        :
-        : "memory");
-}
-
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
-}
 
 // GELU, tanh form: 0.5 x (1 + tanh(y)), y = kC (x + kA x^3)
 // (kernels/int8_common.cuh:9-13).  One MUFU op per element: the epilogue is
@@ -583,24 +474,6 @@ int transpose_i8(const int8_t* in, int8_t* out, int R, int C, cudaStream_t st) {
     transpose_i8_kernel<<<grid, 256, 0, st>>>(in, out, R, C);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
-}
-
-// ---- host: tensor maps ------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
 }
 
 // int8 matrix [rows][cols] row-major, box of box_rows x 128 bytes, 128-byte swizzle

@@ -1,0 +1,433 @@
+// INT8 prefill attention (seq_q == seq_kv, no causal mask) for B200.
+//
+// Replaces int8_attention_forward of the reference (kernels/int8_attention.cu:926-1028,
+// kernel :227-645).  Same arithmetic contract --
+//   score[i][j] = (q_i . k_j) * sQ_i * sK_j / sqrt(D)          (int8 x int8 -> int32)
+//   out_i       = sum_j softmax(score_i)_j * sV_j * v_j          (P*sV and V in fp16, fp32 accumulate)
+// -- on the 5th-generation tensor cores:
+//
+// * One CTA per (b*h, 128 query rows).  QK^T is tcgen05.mma kind::i8 into a
+//   128x128 int32 accumulator in tensor memory (two buffers); PV is tcgen05.mma
+//   kind::f16 accumulating the 128xD fp32 output in tensor memory across all KV
+//   tiles.
+// * Q, K and raw V tiles arrive by TMA (swizzled K-major rows); four converter
+//   warps turn each int8 V tile into fp16 in the MN-major swizzled layout the
+//   PV instruction reads (int8 -> fp16 is exact).
+// * Four softmax warps own one query row per thread: they read the scores with
+//   tcgen05.ld, apply the scales in log2 units, keep a LAZY running maximum
+//   (it only moves when the true maximum exceeds it by 2^8, so p <= 256 stays
+//   comfortably inside fp16), write P*sV as fp16 into the swizzled K-major
+//   operand buffer, and rescale the output accumulator in tensor memory
+//   (tcgen05.ld / tcgen05.st) only on the rare tiles where the maximum moved.
+// * Every mbarrier wait is bounded; on expiry a status word is set and all
+//   roles fall through to the common exit, which frees tensor memory.
+//
+// Supported: head_dim 64 or 128, seq_len a multiple of 128.
+#include "tcgen05.cuh"
+
+#include <cmath>
+
+namespace i8tk {
+namespace {
+
+constexpr int kQT = 128;                 // query rows per CTA
+constexpr int kKT = 128;                 // KV positions per tile
+constexpr int kPrefillThreads = 320;     // TMA, MMA, 4 softmax, 4 converter warps
+constexpr float kLazyStep = 8.0f;        // log2 units the true max may run ahead of the reference max
+
+template <int D>
+struct PrefillCfg {
+    static constexpr int TILE_BYTES = kKT * D;             // one int8 tile (Q, K or raw V)
+    static constexpr int V16_BYTES = kKT * D * 2;          // fp16 V tile
+    static constexpr int P_BYTES = kQT * kKT * 2;          // fp16 P tile: two 64-wide K blocks
+    static constexpr int SLAB_BYTES = kKT * 128;           // 128 rows of 128 bytes
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_K = OFF_Q + TILE_BYTES;
+    static constexpr int OFF_VRAW = OFF_K + 2 * TILE_BYTES;
+    static constexpr int OFF_V16 = OFF_VRAW + 2 * TILE_BYTES;
+    static constexpr int OFF_P = OFF_V16 + 2 * V16_BYTES;
+    static constexpr int OFF_SCALES = OFF_P + P_BYTES;     // 4 warps x (sK[128] | sV[128]) fp32
+    static constexpr int OFF_BARS = OFF_SCALES + 4 * 2 * kKT * 4;
+    static constexpr int NUM_BARS = 20;
+    static constexpr int SMEM_BYTES = 1024 + OFF_BARS + NUM_BARS * 8 + 16;
+    static constexpr int TMEM_COLS = 512;                  // S0 | S1 | O (D columns)
+    static constexpr int TM_S0 = 0, TM_S1 = 128, TM_O = 256;
+};
+
+enum Bar : int {
+    B_QFULL = 0,
+    B_KFULL = 1,      // [2]
+    B_KEMPTY = 3,     // [2]
+    B_VRFULL = 5,     // [2]
+    B_VREMPTY = 7,    // [2]
+    B_SFULL = 9,      // [2]
+    B_SEMPTY = 11,    // [2]
+    B_PFULL = 13,
+    B_V16FULL = 14,   // [2]
+    B_V16EMPTY = 16,  // [2]
+    B_PVDONE = 18,
+};
+
+// four int8 (biased by XOR 0x80 -> u = v + 128) to four fp16, exactly:
+// prmt builds the halves 0x64uu = 1024 + u, one HSUB2 removes 1024 + 128
+__device__ __forceinline__ void i8x4_to_h2x2(uint32_t raw, uint32_t& lo, uint32_t& hi) {
+    const uint32_t b = raw ^ 0x80808080u;
+    const uint32_t p0 = prmt(b, 0x64646464u, 0x4140u);
+    const uint32_t p1 = prmt(b, 0x64646464u, 0x4342u);
+    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+    const __half2 h0 = __hsub2(*reinterpret_cast<const __half2*>(&p0), bias);
+    const __half2 h1 = __hsub2(*reinterpret_cast<const __half2*>(&p1), bias);
+    lo = *reinterpret_cast<const uint32_t*>(&h0);
+    hi = *reinterpret_cast<const uint32_t*>(&h1);
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV, const float* __restrict__ sQ,
+                         const float* __restrict__ sK, const float* __restrict__ sV,
+                         __half* __restrict__ out, int S, float score_scale_log2,
+                         uint32_t* __restrict__ status) {
+    using Cfg = PrefillCfg<D>;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw_s = smem_u32(smem_raw);
+    const uint32_t base_s = (raw_s + 1023u) & ~1023u;       // swizzle patterns are functions of address bits
+    unsigned char* base = smem_raw + (base_s - raw_s);
+    const uint32_t bars = base_s + Cfg::OFF_BARS;
+    auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
+    const uint32_t tmem_slot = bars + Cfg::NUM_BARS * 8;
+    volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(base + Cfg::OFF_BARS + Cfg::NUM_BARS * 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int bh = blockIdx.y;
+    const int q0 = blockIdx.x * kQT;
+    const int nt = S / kKT;                                 // KV tiles
+    const int row_base = bh * S;                            // first row of this (b,h) in the [BH*S, D] views
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(B_QFULL), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(B_KFULL + i), 1);
+            mbar_init(bar(B_KEMPTY + i), 1);
+            mbar_init(bar(B_VRFULL + i), 1);
+            mbar_init(bar(B_VREMPTY + i), 4);
+            mbar_init(bar(B_SFULL + i), 1);
+            mbar_init(bar(B_SEMPTY + i), 4);
+            mbar_init(bar(B_V16FULL + i), 4);
+            mbar_init(bar(B_V16EMPTY + i), 1);
+        }
+        mbar_init(bar(B_PFULL), 4);
+        mbar_init(bar(B_PVDONE), 1);
+        fence_mbar_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_p;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (elect_one()) {
+            mbar_expect_tx(bar(B_QFULL), Cfg::TILE_BYTES);
+            tma_load_2d(base_s + Cfg::OFF_Q, &tmQ, 0, row_base + q0, bar(B_QFULL));
+            for (int j = 0; j < nt; ++j) {
+                const int st = j & 1;
+                const uint32_t par = ((j >> 1) & 1) ^ 1;
+                if (!mbar_wait_spin_bounded(bar(B_KEMPTY + st), par) ||
+                    !mbar_wait_spin_bounded(bar(B_VREMPTY + st), par)) {
+                    atomicExch(status, kDeviceTimeoutMagic);
+                    break;
+                }
+                mbar_expect_tx(bar(B_KFULL + st), Cfg::TILE_BYTES);
+                tma_load_2d(base_s + Cfg::OFF_K + st * Cfg::TILE_BYTES, &tmK, 0, row_base + j * kKT,
+                            bar(B_KFULL + st));
+                mbar_expect_tx(bar(B_VRFULL + st), Cfg::TILE_BYTES);
+                tma_load_2d(base_s + Cfg::OFF_VRAW + st * Cfg::TILE_BYTES, &tmV, 0, row_base + j * kKT,
+                            bar(B_VRFULL + st));
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = idesc_i8(kQT, kKT);
+            constexpr uint32_t idesc_pv = idesc_f16(kQT, D, true);
+            bool ok = mbar_wait_spin_bounded(bar(B_QFULL), 0);
+            auto issue_pv = [&](int t) -> bool {
+                // O (+)= P_t . V_t : 8 steps of 16 KV positions
+                if (!mbar_wait_spin_bounded(bar(B_PFULL), t & 1)) return false;
+                if (!mbar_wait_spin_bounded(bar(B_V16FULL + (t & 1)), (t >> 1) & 1)) return false;
+                tc_fence_after();
+                const uint32_t v16 = base_s + Cfg::OFF_V16 + (t & 1) * Cfg::V16_BYTES;
+                const uint64_t db0 = smem_desc_sw128_mn(v16, Cfg::SLAB_BYTES);
+#pragma unroll
+                for (int i = 0; i < kKT / 16; ++i) {
+                    // A: K-major fp16, 64-wide blocks 16 KB apart, 32 bytes per step inside a block
+                    const uint64_t da = smem_desc_sw128(base_s + Cfg::OFF_P + (i >> 2) * Cfg::SLAB_BYTES) + 2 * (i & 3);
+                    // B: MN-major fp16, 16 rows of 128 bytes per step
+                    const uint64_t db = db0 + (uint64_t)(128 * i);
+                    mma_f16(tmem_base + Cfg::TM_O, da, db, idesc_pv, (t | i) != 0);
+                }
+                tc_commit(bar(B_V16EMPTY + (t & 1)));
+                tc_commit(bar(B_PVDONE));
+                return true;
+            };
+            for (int j = 0; j < nt && ok; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait_spin_bounded(bar(B_KFULL + st), (j >> 1) & 1) ||
+                    !mbar_wait_spin_bounded(bar(B_SEMPTY + st), ((j >> 1) & 1) ^ 1)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t ks = base_s + Cfg::OFF_K + st * Cfg::TILE_BYTES;
+                const uint64_t da = (D == 128) ? smem_desc_sw128(base_s + Cfg::OFF_Q) : smem_desc_sw64(base_s + Cfg::OFF_Q);
+                const uint64_t db = (D == 128) ? smem_desc_sw128(ks) : smem_desc_sw64(ks);
+#pragma unroll
+                for (int k = 0; k < D / 32; ++k)
+                    mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * k, db + 2 * k, idesc_qk, k != 0);
+                tc_commit(bar(B_KEMPTY + st));
+                tc_commit(bar(B_SFULL + st));
+                if (j > 0) ok = issue_pv(j - 1);
+            }
+            if (ok) ok = issue_pv(nt - 1);
+            if (!ok) atomicExch(status, kDeviceTimeoutMagic);
+        }
+    } else if (warp < 6) {
+        // ================= softmax: one query row per thread =================
+        const int q = warp & 3;                          // TMEM lane quarter of this warp
+        const int r = q * 32 + lane;                     // row inside the tile
+        float* wsc = reinterpret_cast<float*>(base + Cfg::OFF_SCALES) + (warp - 2) * 2 * kKT;   // sK | sV of a tile
+        const float qscale = sQ[(size_t)row_base + q0 + r] * score_scale_log2;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        unsigned char* Pm = base + Cfg::OFF_P;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nt; ++j) {
+            const int st = j & 1;
+            // this tile's per-position scales, private to the warp
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < kKT / 32; ++i) {
+                wsc[i * 32 + lane] = sK[(size_t)row_base + j * kKT + i * 32 + lane];
+                wsc[kKT + i * 32 + lane] = sV[(size_t)row_base + j * kKT + i * 32 + lane];
+            }
+            __syncwarp();
+            const bool got = mbar_wait_spin_bounded(bar(B_SFULL + st), (j >> 1) & 1);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S1 : Cfg::TM_S0);
+
+            // ---- pass A: true row maximum of this tile (log2 units) ----
+            float mx = -INFINITY;
+            {
+                uint32_t sr[32];
+#pragma unroll 1
+                for (int cc = 0; cc < kKT / 32; ++cc) {
+                    tmem_ld32(s_addr + cc * 32, sr);
+                    tmem_ld_wait(sr);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        mx = fmaxf(mx, (float)(int)sr[i] * (qscale * wsc[cc * 32 + i]));
+                }
+            }
+            // lazy reference maximum: move it only when the true one ran ahead by kLazyStep
+            const bool move = mx > m_ref + kLazyStep;
+            const float m_new = move ? mx : m_ref;
+            const float corr = move ? ex2_approx(m_ref - m_new) : 1.0f;
+            l *= corr;
+            const bool warp_moves = __any_sync(0xffffffffu, move);
+
+            // ---- P buffer free and O quiescent once PV of the previous tile retired ----
+            if (j > 0) {
+                const bool got2 = mbar_wait_spin_bounded(bar(B_PVDONE), (j - 1) & 1);
+                if (!__all_sync(0xffffffffu, got2)) { ok = false; break; }
+                tc_fence_after();
+                if (warp_moves) {
+                    uint32_t o[32];
+#pragma unroll 1
+                    for (int cc = 0; cc < D / 32; ++cc) {
+                        tmem_ld32(lane_addr + Cfg::TM_O + cc * 32, o);
+                        tmem_ld_wait(o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tmem_st32(lane_addr + Cfg::TM_O + cc * 32, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            m_ref = m_new;
+
+            // ---- pass B: p = 2^(x - m_ref), P*sV as fp16 into the swizzled K-major operand ----
+            {
+                uint32_t sr[32];
+#pragma unroll 1
+                for (int cc = 0; cc < kKT / 32; ++cc) {
+                    tmem_ld32(s_addr + cc * 32, sr);
+                    tmem_ld_wait(sr);
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float x0 = (float)(int)sr[i] * (qscale * wsc[cc * 32 + i]);
+                        const float x1 = (float)(int)sr[i + 1] * (qscale * wsc[cc * 32 + i + 1]);
+                        const float p0 = ex2_approx(x0 - m_ref);
+                        const float p1 = ex2_approx(x1 - m_ref);
+                        l += p0 + p1;
+                        pk[i >> 1] = pack_h2(p0 * wsc[kKT + cc * 32 + i], p1 * wsc[kKT + cc * 32 + i + 1]);
+                    }
+                    // 64-wide K block cc/2, 16-byte chunks (cc%2)*4 .. +3 of row r, XOR-swizzled by r%8
+                    unsigned char* prow = Pm + (cc >> 1) * Cfg::SLAB_BYTES + r * 128;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int chunk = ((cc & 1) * 4 + k) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(prow + chunk * 16) =
+                            make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            fence_proxy_async();                         // generic-proxy writes of P visible to the tensor core
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar(B_SEMPTY + st));
+                mbar_arrive(bar(B_PFULL));
+            }
+        }
+        // ---- epilogue: O / l -> fp16 ----
+        if (ok) {
+            const bool got = mbar_wait_spin_bounded(bar(B_PVDONE), (nt - 1) & 1);
+            ok = __all_sync(0xffffffffu, got);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            __half* orow = out + ((size_t)row_base + q0 + r) * D;
+            uint32_t o[32];
+#pragma unroll 1
+            for (int cc = 0; cc < D / 32; ++cc) {
+                tmem_ld32(lane_addr + Cfg::TM_O + cc * 32, o);
+                tmem_ld_wait(o);
+                uint32_t hp[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2)
+                    hp[i >> 1] = pack_h2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    *reinterpret_cast<uint4*>(orow + cc * 32 + k * 8) =
+                        make_uint4(hp[4 * k], hp[4 * k + 1], hp[4 * k + 2], hp[4 * k + 3]);
+            }
+        } else if (lane == 0) {
+            atomicExch(status, kDeviceTimeoutMagic);
+        }
+    } else {
+        // ================= converter: raw int8 V tile -> fp16, MN-major swizzled =================
+        const int r = threadIdx.x - 6 * 32;              // KV row of the tile handled by this thread
+        for (int j = 0; j < nt; ++j) {
+            const int st = j & 1;
+            bool got = mbar_wait_spin_bounded(bar(B_VRFULL + st), (j >> 1) & 1);
+            if (got && j >= 2) got = mbar_wait_spin_bounded(bar(B_V16EMPTY + st), ((j >> 1) - 1) & 1);
+            if (!__all_sync(0xffffffffu, got)) {
+                if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
+                break;
+            }
+            const unsigned char* raw = base + Cfg::OFF_VRAW + st * Cfg::TILE_BYTES + r * D;
+            unsigned char* dst = base + Cfg::OFF_V16 + st * Cfg::V16_BYTES + r * 128;
+#pragma unroll
+            for (int i = 0; i < D / 16; ++i) {
+                // undo the TMA swizzle of the raw tile: 128-byte rows XOR by r%8, 64-byte rows by (r/2)%4
+                const int src_chunk = (D == 128) ? (i ^ (r & 7)) : (i ^ ((r >> 1) & 3));
+                const uint4 v = *reinterpret_cast<const uint4*>(raw + src_chunk * 16);
+                uint32_t h[8];
+                i8x4_to_h2x2(v.x, h[0], h[1]);
+                i8x4_to_h2x2(v.y, h[2], h[3]);
+                i8x4_to_h2x2(v.z, h[4], h[5]);
+                i8x4_to_h2x2(v.w, h[6], h[7]);
+                // dims i*16 .. i*16+15: slab (i*16)/64, 16-byte chunks 2*(i%4) and +1 of row r
+                unsigned char* drow = dst + (i >> 2) * Cfg::SLAB_BYTES;
+                const int c0 = 2 * (i & 3);
+                *reinterpret_cast<uint4*>(drow + ((c0 ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                *reinterpret_cast<uint4*>(drow + (((c0 + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar(B_V16FULL + st));
+                mbar_arrive(bar(B_VREMPTY + st));
+            }
+        }
+    }
+
+    // common exit: every role ends here, then the allocating warp frees tensor memory
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+template <int D>
+int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, const float* sQ,
+                   const float* sK, const float* sV, int BH, int S, uint32_t* status, cudaStream_t st) {
+    using Cfg = PrefillCfg<D>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    I8TK_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        I8TK_CUDA(cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES));
+        attr_done[dev] = true;
+    }
+    const CUtensorMapSwizzle sw = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    CUtensorMap tmQ, tmK, tmV;
+    const unsigned long long rows = (unsigned long long)BH * S;
+    const void* ptrs[3] = {Q, K, V};
+    CUtensorMap* maps[3] = {&tmQ, &tmK, &tmV};
+    for (int i = 0; i < 3; ++i) {
+        const int rc = encode_map_2d_u8(maps[i], ptrs[i], rows, D, kKT, D, sw);
+        I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
+    }
+    const float score_scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+    dim3 grid(S / kQT, BH);
+    prefill_attention_kernel<D><<<grid, kPrefillThreads, Cfg::SMEM_BYTES, st>>>(tmQ, tmK, tmV, sQ, sK, sV, out, S,
+                                                                              score_scale_log2, status);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
+
+}  // namespace
+}  // namespace i8tk
+
+using namespace i8tk;
+
+extern "C" size_t i8tk_attention_workspace_bytes(void) { return 256; }
+
+extern "C" int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V, void* out_f16,
+                                      const float* sQ, const float* sK, const float* sV, int batch,
+                                      int heads, int seq_len, int head_dim, void* workspace,
+                                      size_t workspace_bytes, i8tk_stream_t stream) {
+    I8TK_REQUIRE(Q && K && V && out_f16 && sQ && sK && sV, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(batch > 0 && heads > 0 && seq_len > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
+    I8TK_REQUIRE(head_dim == 64 || head_dim == 128, I8TK_ERR_UNSUPPORTED,
+                 "prefill attention supports head_dim 64 or 128 (got %d)", head_dim);
+    I8TK_REQUIRE(seq_len % 128 == 0, I8TK_ERR_UNSUPPORTED,
+                 "prefill attention needs seq_len to be a multiple of 128 (got %d)", seq_len);
+    I8TK_REQUIRE((long long)batch * heads <= 65535, I8TK_ERR_UNSUPPORTED, "batch*heads must be <= 65535");
+    I8TK_REQUIRE((long long)batch * heads * seq_len < (1ll << 31), I8TK_ERR_UNSUPPORTED, "too many rows");
+    I8TK_REQUIRE(aligned_to(Q, 16) && aligned_to(K, 16) && aligned_to(V, 16) && aligned_to(out_f16, 16),
+                 I8TK_ERR_ALIGNMENT, "Q, K, V and out must be 16-byte aligned");
+    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= 256 && aligned_to(workspace, 256),
+                 I8TK_ERR_WORKSPACE, "workspace of 256 bytes, 256-byte aligned, is required");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t* status = static_cast<uint32_t*>(workspace);
+    const int BH = batch * heads;
+    if (head_dim == 64)
+        return launch_prefill<64>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, st);
+    return launch_prefill<128>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, st);
+}

@@ -104,3 +104,29 @@ def combine_partials(ms, ls, accs):
     ACC = (accs * w[..., None]).sum(axis=0)
     out = (ACC / L[..., None]).astype(np.float32)
     return gm, L, ACC, out
+
+
+def prefill_attention(Qi, Ki, Vi, sQ, sK, sV, dtype=np.float64):
+    """Non-causal attention on the dequantised values, seq_q == seq_kv.
+
+    Restates the reference check of its prefill kernel (``tests/test_int8.py:99-111``:
+    dequantise per token, then ``common/baseline.py:7-22`` ``softmax(Q K^T / sqrt(D)) V``),
+    in float64 instead of fp16.  ``Qi``,``Ki``,``Vi`` int8 [B,H,S,D]; scales fp32 [B,H,S]
+    (or flat).  Returns fp32 [B,H,S,D].
+    """
+    B, H, S, D = Qi.shape
+    sQ = np.asarray(sQ, dtype=np.float32).reshape(B, H, S)
+    sK = np.asarray(sK, dtype=np.float32).reshape(B, H, S)
+    sV = np.asarray(sV, dtype=np.float32).reshape(B, H, S)
+    out = np.empty((B, H, S, D), dtype=np.float32)
+    inv = dtype(1.0) / np.sqrt(dtype(D))
+    for b in range(B):
+        for h in range(H):
+            q = dequantize(Qi[b, h], sQ[b, h]).astype(dtype)
+            k = dequantize(Ki[b, h], sK[b, h]).astype(dtype)
+            v = dequantize(Vi[b, h], sV[b, h]).astype(dtype)
+            s = (q @ k.T) * inv
+            s -= s.max(axis=1, keepdims=True)
+            p = np.exp(s)
+            out[b, h] = ((p @ v) / p.sum(axis=1, keepdims=True)).astype(np.float32)
+    return out
