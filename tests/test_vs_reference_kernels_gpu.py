@@ -33,6 +33,7 @@ def ref():
     lib.ref_mlp_forward_per_channel_bias.argtypes = [vp] * 9 + [i] * 4
     lib.ref_mlp_forward_prepacked.argtypes = [vp] * 7 + [i] * 4
     lib.ref_mlp_get_output_scale.restype = ctypes.c_float
+    lib.ref_attention_forward.argtypes = [vp] * 7 + [i] * 4
     return lib
 
 
@@ -136,3 +137,26 @@ def test_mlp_speed_beside_reference_kernel(ref, capsys):
         print(f"\nMLP M{M} {dm}->{dff}: ours {t_ours:.1f} us ({tops / t_ours:.0f} TOPS), reference kernel "
               f"{t_ref:.1f} us ({tops / t_ref:.0f} TOPS), x{t_ref / t_ours:.2f}")
     assert t_ours < t_ref
+
+
+def test_prefill_speed_beside_reference_kernel(ref, capsys):
+    lines = []
+    for (B, H, S, D) in [(8, 8, 4096, 64), (4, 8, 4096, 128)]:
+        g = torch.Generator(device="cuda").manual_seed(2)
+        e = ext()
+        t = []
+        for _ in range(3):
+            xi, sx = e.quantize_per_token(torch.randn(B, H, S, D, device="cuda", dtype=torch.float16, generator=g))
+            t.append((xi, sx.reshape(-1).contiguous()))
+        (Qi, sQ), (Ki, sK), (Vi, sV) = t
+        out = torch.empty(B, H, S, D, dtype=torch.float16, device="cuda")
+        t_ours = _time(lambda: e.int8_attention_forward(Qi, Ki, Vi, sQ, sK, sV), iters=10)
+        t_ref = _time(lambda: ref.ref_attention_forward(Qi.data_ptr(), Ki.data_ptr(), Vi.data_ptr(), out.data_ptr(),
+                                                        sQ.data_ptr(), sK.data_ptr(), sV.data_ptr(), B, H, S, D),
+                      iters=10)
+        tops = 4.0 * B * H * S * S * D / 1e6
+        lines.append(f"prefill B{B} H{H} S{S} D{D}: ours {t_ours:.0f} us ({tops / t_ours:.0f} TOPS), "
+                     f"reference kernel {t_ref:.0f} us ({tops / t_ref:.0f} TOPS), x{t_ref / t_ours:.2f}")
+        assert t_ours < t_ref
+    with capsys.disabled():
+        print("\n" + "\n".join(lines))
