@@ -455,8 +455,38 @@ def sweep(torch, ext, cabi, world, rank, barrier, dist):
         del Ki, Vi, sK, sV
         torch.cuda.empty_cache()
     elif rank == 0:
+        res.extend(quantiser_and_prefill_sweep(torch, ext))
         res.extend(mlp_sweep(torch, ext, cabi))
     return res
+
+
+def quantiser_and_prefill_sweep(torch, ext):
+    """Per-token quantiser (HBM-bound: bytes in + codes out + scales) and prefill attention
+    (4*B*H*S^2*D ops), device-timed."""
+    out = []
+    for dt, rows, cols, tag in ((torch.float32, 32 * 12 * 8192, 64, "K/V of cfg1 ctx8192, fp32 in"),
+                                (torch.float32, 64 * 32 * 2048, 128, "quarter of cfg2 K/V, fp32 in"),
+                                (torch.float16, 65536, 1024, "MLP activations, fp16 in")):
+        x = torch.randn(rows, cols, device="cuda", dtype=dt)
+        steps = 20
+        el = timed_steps(torch, lambda: ext.quantize_per_token(x), steps, 3)
+        byts = rows * cols * (x.element_size() + 1) + rows * 4
+        out.append({"workload": f"quantize_per_token [{rows}, {cols}] ({tag})", "us_per_step": el / steps * 1e6,
+                    "GBps": byts * steps / el / 1e9, "l2_resident": byts < 100e6})
+        del x
+        torch.cuda.empty_cache()
+    for (b, h, s, d) in ((8, 8, 4096, 64), (4, 8, 4096, 128)):
+        g = torch.Generator(device="cuda").manual_seed(0)
+        t = []
+        for _ in range(3):
+            xi, sx = ext.quantize_per_token(torch.randn(b, h, s, d, device="cuda", dtype=torch.float16, generator=g))
+            t.extend([xi, sx.reshape(-1).contiguous()])
+        steps = 10
+        el = timed_steps(torch, lambda: ext.int8_attention_forward(t[0], t[2], t[4], t[1], t[3], t[5]), steps, 3)
+        ops = 4.0 * b * h * s * s * d
+        out.append({"workload": f"prefill int8 attention B{b} H{h} S{s} D{d}", "us_per_step": el / steps * 1e6,
+                    "TOPS": ops * steps / el / 1e12})
+    return out
 
 
 def mlp_sweep(torch, ext, cabi):
