@@ -78,29 +78,6 @@ __device__ __forceinline__ int dot16(const int4& q, const int4& k) {
     return d;
 }
 
-// Packed fp32x2 arithmetic (one instruction for two lanes of a register pair).
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pack2(float a, float b) {
-    float2 t = make_float2(a, b);
-    return *reinterpret_cast<f32x2*>(&t);
-}
-__device__ __forceinline__ float2 unpack2(f32x2 v) { return *reinterpret_cast<float2*>(&v); }
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    f32x2 d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
-    f32x2 d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    f32x2 d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-
 // acc[0..1] (four floats) += w * int8x4(word).  The word is XORed with
 // 0x80808080 so its bytes are u = v + 128 in [0, 255]; prmt drops byte j into
 // the low mantissa of 0x4B000000 (= 2^23), and adding -(2^23 + 128) recovers v

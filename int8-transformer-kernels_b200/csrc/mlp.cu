@@ -19,10 +19,18 @@
 //   completes on mbarriers; a stage is handed back to the TMA warp by
 //   tcgen05.commit when the MMAs that read it have retired.
 // * Warp roles in a persistent CTA (one per SM): warp 0 = TMA producer, warp 1 =
-//   TMEM allocator + MMA issuer, warps 2..9 = epilogue (two warps per TMEM lane
-//   quarter, each taking half of the tile's columns: tcgen05.ld 32 lanes x 32
+//   TMEM allocator + MMA issuer, warps 2..17 = epilogue (four warps per TMEM lane
+//   quarter, each taking a quarter of the tile's columns: tcgen05.ld 32 lanes x 16
 //   columns at a time, the next load in flight while the current block goes
-//   registers -> dequant / bias / GELU / absmax -> fp16).
+//   registers -> dequant / bias / GELU / absmax -> fp16, in packed fp32x2 math).
+// * Fused requantisation: a tile's fp16 values wait in shared memory (a stash of
+//   32 rows x BN/4 columns per warp) while the maxima of its rows are exchanged
+//   with the other SMs that work on the same 128 rows -- one word per (row, tile)
+//   in global memory that is its own "written" flag, no fence, atomic or counter.
+//   With a short K loop (GEMM1) the tile is quantised one tile later, the maxima
+//   having been read ahead of time into registers that the drain has freed; with
+//   a long one (GEMM2) at once, under the MMAs of the next tile.  int8 rows leave
+//   as 16-byte stores that cover whole row segments.
 // * Every wait on an mbarrier is bounded; on a timeout the kernel records a
 //   status word, all roles fall through to the common exit and TMEM is freed.
 //
@@ -32,6 +40,7 @@
 #include "tcgen05.cuh"
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace i8tk {
 namespace {
@@ -39,21 +48,27 @@ namespace {
 constexpr int BM = 128;          // rows per tile (= TMEM lanes)
 constexpr int BK = 128;          // K bytes per stage: one 128-byte swizzle row
 constexpr int kEpiWarp0 = 2;     // first epilogue warp
-constexpr int kEpiWarps = 8;     // two per TMEM lane quarter, each takes half of the columns
-constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kEpiWarps = 16;    // four per TMEM lane quarter, each takes a quarter of the columns
+constexpr int kSlices = kEpiWarps / 4;
 constexpr int kGemmThreads = (kEpiWarp0 + kEpiWarps) * 32;
 
-template <int BN>
+// FUSED kernels keep a whole tile of fp16 values in shared memory (the stash of the fused
+// requantisation), paid for with one pipeline stage at the wider tiles.
+template <int BN, bool FUSED>
 struct GemmCfg {
-    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : 6);
+    static constexpr int STAGES = (BN == 256) ? (FUSED ? 3 : 4) : (BN == 192 ? 4 : (FUSED ? 5 : 6));
+    static constexpr int HC = BN / kSlices;                  // columns per epilogue warp
     static constexpr int A_BYTES = BM * BK;
     static constexpr int B_BYTES = BN * BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;   // two accumulator buffers, power of two
-    static constexpr int AUX_BYTES = 2 * 2 * BN * 4;         // [buf][scale|bias][BN] fp32
-    static constexpr int CSTAGE_BYTES = kEpiWarps * 32 * 64; // per epilogue warp: 32 rows x 32 fp16
+    static constexpr int AUX_BYTES = kEpiWarps * 2 * HC * 4;        // per epilogue warp: [scale|bias][HC] fp32
+    static constexpr int CMB_BYTES = 2 * kEpiWarps * 32 * 4;        // [2][quarter][slice][32 rows] row maxima
+    // per epilogue warp: 32 rows x HC fp16 (FUSED), or 32 rows x 16 fp16 of store staging
+    static constexpr int CSTAGE_WARP_BYTES = FUSED ? 32 * HC * 2 : 32 * 32;
+    static constexpr int CSTAGE_BYTES = kEpiWarps * CSTAGE_WARP_BYTES;
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES + BAR_BYTES + CSTAGE_BYTES;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES + CMB_BYTES + BAR_BYTES + CSTAGE_BYTES;
 };
 
 struct EpiParams {
@@ -68,22 +83,129 @@ struct EpiParams {
     // fused per-row requantisation (FUSED kernels): int8 C and its row scales
     int8_t* C8;               // [M, N] int8
     float* row_scale;         // [M]
-    unsigned int* block_done; // [M / 128] tiles finished per row block (must start at 0)
+    // [M / 128][N / BN][128] row maxima, one word per (row, tile), which every bit set
+    // marks as not yet written (the caller fills the array with 0xFF bytes)
+    uint32_t* row_parts;
 };
 
 // GELU, tanh form: 0.5 x (1 + tanh(y)), y = kC (x + kA x^3)
-// (kernels/int8_common.cuh:9-13).  One MUFU op per element: the epilogue is
-// bound by the special-function unit, not by the tensor cores.  tanh.approx
-// has a relative error of about 2^-11, the same size as the fp16 rounding the
-// value goes through next.
-__device__ __forceinline__ float gelu_tanh(float x) {
+// (kernels/int8_common.cuh:9-13).  tanh.approx has a relative error of about
+// 2^-11, the same size as the fp16 rounding the value goes through next.
+#ifdef I8TK_GEMM_TRACE
+// Development aid (not compiled into the library): per-CTA clock stamps of the GEMM roles.
+constexpr int kTraceSlots = 128;
+__device__ long long g_gemm_trace[148 * kTraceSlots];
+#define I8TK_TRACE(slot) do { if ((slot) < kTraceSlots && blockIdx.x < 148) g_gemm_trace[blockIdx.x * kTraceSlots + (slot)] = clock64(); } while (0)
+#else
+#define I8TK_TRACE(slot) do { } while (0)
+#endif
+
+// GELU on a packed pair: five packed fp32 instructions and two MUFU.TANH.
+__device__ __forceinline__ f32x2 gelu_tanh2(f32x2 x) {
     constexpr float kC = 0.7978845608028654f, kA = 0.044715f;
-    const float u = x * x;
-    const float y = x * fmaf(u, kC * kA, kC);
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(y));
-    const float hx = 0.5f * x;
-    return fmaf(hx, t, hx);
+    const f32x2 u = mul2(x, x);
+    const f32x2 y = mul2(x, fma2(u, pack2(kC * kA, kC * kA), pack2(kC, kC)));
+    const float2 yy = unpack2(y);
+    float t0, t1;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(yy.x));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(yy.y));
+    const f32x2 hx = mul2(x, pack2(0.5f, 0.5f));
+    return fma2(hx, pack2(t0, t1), hx);
+}
+
+// int32 accumulator -> fp32 (cvt.rn.f32.s32).  An integer/FMA-pipe emulation through 2^23
+// magic numbers was measured and is slower: the conversion unit is not the bottleneck.
+__device__ __forceinline__ float i2f(uint32_t acc) { return (float)(int)acc; }
+
+// Read-only load that is issued where it is written: the compiler may not sink it down to
+// its first use, which is the point of loading a tile ahead.
+__device__ __forceinline__ float ld_nc_now(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
+// Row maxima travel between the SMs that share a row block as plain words in global
+// memory: one word per (row, half tile), written once with a relaxed store and read with
+// relaxed loads that go to L2.  A maximum is a non-negative float, so its sign bit is
+// clear; the array starts as all ones, and a set sign bit therefore means "not written
+// yet".  The word is its own flag: no fence, counter or atomic is involved.
+__device__ __forceinline__ void publish_row_max(uint32_t* slot, float rmax) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(slot), "r"(__float_as_uint(rmax) & 0x7FFFFFFFu) : "memory");
+}
+// Lane = row.  `col` points at this lane's row in part 0; part k of the same row is 128
+// words further (the array is [row block][part][128 rows], so a warp reads and writes whole
+// 128-byte lines).  Waits (bounded) until all `parts` words are written and returns their
+// maximum; false in *ok when the wait ran out.
+constexpr int kGatherAhead = 16;   // parts per row that can be looked at ahead of time
+__device__ __forceinline__ void gather_issue(const uint32_t* col, int parts, uint32_t (&g)[kGatherAhead]) {
+#pragma unroll
+    for (int k = 0; k < kGatherAhead; ++k) {
+        g[k] = 0u;
+        if (k < parts)
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(g[k]) : "l"(col + k * 128) : "memory");
+    }
+}
+// True (for the whole warp) when the early look found every word written; *mx is then the row's maximum.
+__device__ __forceinline__ bool gather_check(const uint32_t (&g)[kGatherAhead], float* mx) {
+    uint32_t any = 0u;
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < kGatherAhead; ++k) {
+        any |= g[k];
+        m = fmaxf(m, __uint_as_float(g[k]));
+    }
+    *mx = m;
+    return __all_sync(0xffffffffu, (any & 0x80000000u) == 0u);
+}
+__device__ __forceinline__ float gather_row_max(const uint32_t* col, int parts, bool* ok) {
+    float mx = 0.f;
+    bool ready = false;
+    for (uint32_t spin = 0; spin < (1u << 16); ++spin) {
+        uint32_t any = 0u;
+        mx = 0.f;
+#pragma unroll 8
+        for (int k = 0; k < parts; ++k) {
+            uint32_t a;
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(a) : "l"(col + k * 128) : "memory");
+            any |= a;
+            mx = fmaxf(mx, __uint_as_float(a));
+        }
+        ready = (any & 0x80000000u) == 0u;
+        if (__all_sync(0xffffffffu, ready)) break;
+    }
+    *ok = ready;
+    return mx;
+}
+
+// 16-byte slot of chunk j of row r in a warp's stash (rows of HC fp16, HC / 8 chunks): XOR
+// with low row bits spreads a column of chunks over the banks and stays inside the row.
+template <int HC>
+__device__ __forceinline__ int stash_swz(int r, int j) {
+    constexpr int kChunks = HC / 8;
+    constexpr int kMask = (kChunks % 8 == 0) ? 7 : ((kChunks % 4 == 0) ? 3 : 1);
+    return j ^ (r & kMask);
+}
+
+// Eight fp16 values (one 16-byte chunk) * inv -> eight int8, round to nearest even: adding
+// 1.5 * 2^23 leaves the integer in the low mantissa bits, whose low byte is the int8 code.
+template <bool CLAMP>
+__device__ __forceinline__ uint2 quant8_f16(uint4 h, f32x2 inv2) {
+    const f32x2 magic2 = pack2(12582912.f, 12582912.f);
+    const __half2* hp = reinterpret_cast<const __half2*>(&h);
+    uint32_t b[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __half22float2(hp[k]);
+        f32x2 t = mul2(pack2(f.x, f.y), inv2);
+        if (CLAMP) {
+            const float2 tt = unpack2(t);
+            t = pack2(fmaxf(-128.f, fminf(127.f, tt.x)), fmaxf(-128.f, fminf(127.f, tt.y)));
+        }
+        const float2 rr = unpack2(add2(t, magic2));
+        b[k] = prmt(__float_as_uint(rr.x), __float_as_uint(rr.y), 0x0040u);
+    }
+    return make_uint2(prmt(b[0], b[1], 0x5410u), prmt(b[2], b[3], 0x5410u));
 }
 
 __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
@@ -94,11 +216,11 @@ __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
 // C[M,N] fp16 = epilogue( A[M,K] int8 . B[N,K]^T int8 ), persistent over tiles.
 // M % 128 == 0, N % BN == 0, K % 128 == 0.
 // ---------------------------------------------------------------------------
-template <int BN, bool GELU, bool FUSED>
+template <int BN, bool GELU, bool FUSED, bool DEFER>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                EpiParams ep, int M, int N, int K, int b_mn, uint32_t* __restrict__ status) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, FUSED>;
     constexpr int STAGES = Cfg::STAGES;
 
     extern __shared__ unsigned char smem_raw[];
@@ -107,16 +229,16 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t base_s = (raw_s + 1023u) & ~1023u;
     unsigned char* base = smem_raw + (base_s - raw_s);
     float* aux = reinterpret_cast<float*>(base + STAGES * Cfg::STAGE_BYTES);
-    const uint32_t bars = base_s + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES;
+    float* cmb = reinterpret_cast<float*>(base + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES);
+    constexpr int kBarOff = STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES + Cfg::CMB_BYTES;
+    const uint32_t bars = base_s + kBarOff;
     const uint32_t full0 = bars;                       // [STAGES]  TMA landed
     const uint32_t empty0 = bars + STAGES * 8;         // [STAGES]  MMAs done with the stage
     const uint32_t tfull0 = bars + 2 * STAGES * 8;     // [2]       accumulator complete
     const uint32_t tempty0 = tfull0 + 16;              // [2]       accumulator drained
     const uint32_t tmem_slot = tempty0 + 16;
-    volatile uint32_t* tmem_slot_p =
-        reinterpret_cast<volatile uint32_t*>(base + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES +
-                                             (2 * STAGES + 4) * 8);
-    unsigned char* cstage_base = base + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES + Cfg::BAR_BYTES;
+    volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(base + kBarOff + (2 * STAGES + 4) * 8);
+    unsigned char* cstage_base = base + kBarOff + Cfg::BAR_BYTES;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -125,6 +247,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int kblocks = K / BK;
 
     if (threadIdx.x == 0) {
+        I8TK_TRACE(0);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
@@ -140,12 +263,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
+    if (threadIdx.x == 0) I8TK_TRACE(1);
 
     if (warp == 0) {
         // ================= TMA producer =================
         if (elect_one()) {
             int it = 0;
             bool ok = true;
+            I8TK_TRACE(2);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile / tiles_n) * BM;
                 const int n0 = (tile % tiles_n) * BN;
@@ -184,6 +309,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     break;
                 }
                 tc_fence_after();
+                I8TK_TRACE(8 + 10 * lt + 0);
                 const uint32_t tmem_d = tmem_base + buf * BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % STAGES;
@@ -193,6 +319,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         break;
                     }
                     tc_fence_after();
+                    if (kb == 0) I8TK_TRACE(8 + 10 * lt + 1);
                     const uint32_t sa = base_s + st * Cfg::STAGE_BYTES;
                     const uint64_t da = smem_desc_sw128(sa);
                     const uint64_t db = b_mn ? smem_desc_sw128_mn(sa + Cfg::A_BYTES, 128 * BK)
@@ -206,32 +333,105 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tc_commit(empty0 + 8 * st);           // stage reusable when these MMAs retire
                 }
                 if (ok) tc_commit(tfull0 + 8 * buf);      // accumulator complete
+                I8TK_TRACE(8 + 10 * lt + 2);
             }
         }
     } else {
         // ================= epilogue =================
-        const int ew = warp - kEpiWarp0;                  // 0..7
+        const int ew = warp - kEpiWarp0;                  // 0..15
         const int q = warp & 3;                           // TMEM lane quarter this warp may read
-        const int half = ew >> 2;                         // which half of the tile's columns
-        constexpr int HC = BN / 2;                        // columns per warp
-        constexpr int NCH = HC / 32;                      // 32-column blocks per warp
-        const int et = threadIdx.x - kEpiWarp0 * 32;      // 0..255
+        const int slice = ew >> 2;                        // which quarter of the tile's columns
+        constexpr int HC = Cfg::HC;                       // columns per warp
+        constexpr int NCH = HC / 16;                      // 16-column blocks per warp
+        constexpr int NPF = (HC + 31) / 32;
+        const int c0 = slice * HC;
+        float* sb = aux + ew * (2 * HC);                  // this warp's column scales ...
+        float* bb = sb + HC;                              // ... and bias, in shared memory
+        unsigned char* cst = cstage_base + ew * Cfg::CSTAGE_WARP_BYTES;
+
+        // Column scales, bias and the row scale are fetched one tile ahead (registers), and
+        // dropped into this warp's block of shared memory just before the tile that uses them.
+        float pf_s[NPF], pf_b[NPF], pf_sa = 0.f;
+        auto prefetch = [&](int tile) {
+            const int pm0 = (tile / tiles_n) * BM, pn0 = (tile % tiles_n) * BN;
+#pragma unroll
+            for (int j = 0; j < NPF; ++j) {
+                const int cj = j * 32 + lane;
+                const int col = pn0 + c0 + (cj < HC ? cj : 0);
+                pf_s[j] = ld_nc_now(ep.b_per_col ? ep.scale_b + col : ep.scale_b);
+                pf_b[j] = ep.bias ? ld_nc_now(ep.bias + col) : 0.f;
+            }
+            pf_sa = ld_nc_now(ep.a_per_row ? ep.scale_a + pm0 + q * 32 + lane : ep.scale_a);
+        };
+        if ((int)blockIdx.x < num_tiles) prefetch(blockIdx.x);
+
+        // Requantisation of a tile whose fp16 values sit in this warp's stash: wait for the
+        // maxima of its row block, then 16 columns (16 bytes of int8) per lane and step, a row
+        // segment of HC bytes across consecutive lanes.
+        [[maybe_unused]] int trace_lt = 0;
+        [[maybe_unused]] uint32_t gahead[(FUSED && DEFER) ? kGatherAhead : 1];
+        [[maybe_unused]] auto finalize = [&](int fm0, int fn0, bool looked_ahead) {
+            if constexpr (FUSED) {
+                bool ok = true;
+                float amax = 0.f;
+                bool have = false;
+                if constexpr (DEFER) {
+                    if (looked_ahead) have = gather_check(gahead, &amax);
+                }
+                if (!have) amax = gather_row_max(ep.row_parts + (size_t)fm0 * tiles_n + q * 32 + lane, tiles_n, &ok);
+                if (!ok) atomicExch(status, kDeviceTimeoutMagic);
+                if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * trace_lt + 6);
+                amax = fmaxf(amax, 1e-8f);
+                const float inv_l = 127.f / amax;
+                if (fn0 == 0 && slice == 0) ep.row_scale[fm0 + q * 32 + lane] = amax / 127.f;
+                constexpr int SEGS = HC / 16;              // 16-column segments per row
+                int8_t* c8blk = ep.C8 + (size_t)(fm0 + q * 32) * N + fn0 + c0;
+                auto body = [&](auto clamp_tag) {
+                    constexpr bool kClamp = decltype(clamp_tag)::value;
+#pragma unroll
+                    for (int it = 0; it < SEGS; ++it) {
+                        const int item = it * 32 + lane;
+                        const int r = item / SEGS, seg = item % SEGS;
+                        const float inv = __shfl_sync(0xffffffffu, inv_l, r);
+                        const f32x2 inv2 = pack2(inv, inv);
+                        const unsigned char* rowp = cst + r * (HC * 2);
+                        const uint4 h0 = *reinterpret_cast<const uint4*>(rowp + (stash_swz<HC>(r, 2 * seg) << 4));
+                        const uint4 h1 = *reinterpret_cast<const uint4*>(rowp + (stash_swz<HC>(r, 2 * seg + 1) << 4));
+                        const uint2 w0 = quant8_f16<kClamp>(h0, inv2);
+                        const uint2 w1 = quant8_f16<kClamp>(h1, inv2);
+                        *reinterpret_cast<uint4*>(c8blk + (size_t)r * N + seg * 16) = make_uint4(w0.x, w0.y, w1.x, w1.y);
+                    }
+                };
+                // values above the fp16 range were stored as inf: only then can a product
+                // leave [-128, 127], so ordinary rows skip the clamp
+                if (__any_sync(0xffffffffu, !(amax <= 65504.f))) body(std::true_type{});
+                else body(std::false_type{});
+                __syncwarp();                              // stash reads done before it is rewritten
+                if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * trace_lt + 7);
+            }
+        };
+
+        int p_m0 = -1, p_n0 = 0;                          // DEFER: tile waiting in the stash
         int lt = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
             const int buf = lt & 1;
             const int m0 = (tile / tiles_n) * BM;
             const int n0 = (tile % tiles_n) * BN;
-            const int row = m0 + q * 32 + lane;
 
-            // column scales and bias of this tile -> shared memory
-            float* sb = aux + buf * 2 * BN;
-            float* bb = sb + BN;
-            for (int j = et; j < BN; j += kEpiThreads) {
-                sb[j] = ep.b_per_col ? ep.scale_b[n0 + j] : ep.scale_b[0];
-                bb[j] = ep.bias ? ep.bias[n0 + j] : 0.f;
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < NPF; ++j) {
+                const int cj = j * 32 + lane;
+                if (cj < HC) {
+                    sb[cj] = pf_s[j];
+                    bb[cj] = pf_b[j];
+                }
             }
-            const float sa = ep.a_per_row ? ep.scale_a[row] : ep.scale_a[0];
-            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+            const float sa = pf_sa;
+            const f32x2 sa2 = pack2(sa, sa);
+            __syncwarp();
+            if (tile + (int)gridDim.x < num_tiles) prefetch(tile + gridDim.x);
+            if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 9);
 
             const bool got = mbar_wait_spin_bounded(tfull0 + 8 * buf, (lt >> 1) & 1);
             if (!__all_sync(0xffffffffu, got)) {
@@ -239,55 +439,61 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 break;
             }
             tc_fence_after();
+            if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 3);
 
             float rmax = 0.f;
-            const int c0 = half * HC;
-            unsigned char* cst = cstage_base + ew * (32 * 64);
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c0;
             uint32_t hv[FUSED ? HC / 2 : 1];              // FUSED: this row's values as packed fp16
-            uint32_t r[2][32];
-            tmem_ld32(taddr, r[0]);
+            uint32_t r[2][16];
+            tmem_ld16(taddr, r[0]);
 #pragma unroll
             for (int cc = 0; cc < NCH; ++cc) {
                 tmem_ld_wait(r[cc & 1]);                                   // block cc is in r[cc & 1]
-                if (cc + 1 < NCH) tmem_ld32(taddr + (cc + 1) * 32, r[(cc + 1) & 1]);
+                if (cc + 1 < NCH) tmem_ld16(taddr + (cc + 1) * 16, r[(cc + 1) & 1]);
+                if constexpr (FUSED && DEFER) {
+                    // the other accumulator block is dead from here on: its registers take an
+                    // early look at the previous tile's row maxima while this block is worked on
+                    if (cc == NCH - 1 && p_m0 >= 0 && tiles_n <= kGatherAhead)
+                        gather_issue(ep.row_parts + (size_t)p_m0 * tiles_n + q * 32 + lane, tiles_n, gahead);
+                }
                 const uint32_t* rr = r[cc & 1];
-                uint32_t packed[16];
+                uint32_t packed[8];
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const float2 s2 = *reinterpret_cast<const float2*>(sb + c0 + cc * 32 + j);
-                    const float2 b2 = *reinterpret_cast<const float2*>(bb + c0 + cc * 32 + j);
-                    float v0 = (float)(int)rr[j] * sa * s2.x + b2.x;
-                    float v1 = (float)(int)rr[j + 1] * sa * s2.y + b2.y;
+                for (int j = 0; j < 16; j += 4) {
+                    const float4 s4 = *reinterpret_cast<const float4*>(sb + cc * 16 + j);
+                    const float4 b4 = *reinterpret_cast<const float4*>(bb + cc * 16 + j);
+                    f32x2 v01 = fma2(mul2(pack2(i2f(rr[j]), i2f(rr[j + 1])), sa2), pack2(s4.x, s4.y), pack2(b4.x, b4.y));
+                    f32x2 v23 = fma2(mul2(pack2(i2f(rr[j + 2]), i2f(rr[j + 3])), sa2), pack2(s4.z, s4.w), pack2(b4.z, b4.w));
                     if (GELU) {
-                        v0 = gelu_tanh(v0);
-                        v1 = gelu_tanh(v1);
+                        v01 = gelu_tanh2(v01);
+                        v23 = gelu_tanh2(v23);
                     }
-                    rmax = fmaxf(rmax, fmaxf(fabsf(v0), fabsf(v1)));
-                    const __half2 h = __floats2half2_rn(v0, v1);
-                    packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                    const float2 a = unpack2(v01), b = unpack2(v23);
+                    rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(a.x), fabsf(a.y))), fmaxf(fabsf(b.x), fabsf(b.y)));
+                    const __half2 ha = __floats2half2_rn(a.x, a.y);
+                    const __half2 hb = __floats2half2_rn(b.x, b.y);
+                    packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&ha);
+                    packed[(j >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hb);
                 }
                 if constexpr (FUSED) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) hv[cc * 16 + j] = packed[j];
+                    for (int j = 0; j < 8; ++j) hv[cc * 8 + j] = packed[j];
                 } else {
-                    // 32 rows x 64 bytes through this warp's staging block so that the
-                    // global stores cover whole 64-byte row segments (4 lanes per row).
-                    // 16-byte slot j of row r lives at slot j ^ ((r >> 1) & 3): both the
-                    // row-wise writes and the 8-rows-at-a-time reads are conflict free.
+                    // 32 rows x 32 bytes through this warp's staging block, so that two lanes
+                    // store each row's 32 bytes and a store instruction covers 16 rows
                     __half* cblk = ep.C + (size_t)(m0 + q * 32) * N + n0 + c0;
                     __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        *reinterpret_cast<uint4*>(cst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                    for (int j = 0; j < 2; ++j)
+                        *reinterpret_cast<uint4*>(cst + lane * 32 + ((j ^ ((lane >> 2) & 1)) << 4)) =
                             make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
                     __syncwarp();
 #pragma unroll
-                    for (int it = 0; it < 4; ++it) {
-                        const int rr2 = it * 8 + (lane >> 2);
-                        const int j = lane & 3;
-                        const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 64 + ((j ^ ((rr2 >> 1) & 3)) << 4));
-                        *reinterpret_cast<uint4*>(cblk + (size_t)rr2 * N + cc * 32 + j * 8) = v;
+                    for (int it = 0; it < 2; ++it) {
+                        const int rr2 = it * 16 + (lane >> 1);
+                        const int j = lane & 1;
+                        const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 32 + ((j ^ ((rr2 >> 2) & 1)) << 4));
+                        *reinterpret_cast<uint4*>(cblk + (size_t)rr2 * N + cc * 16 + j * 8) = v;
                     }
                 }
             }
@@ -295,8 +501,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+            if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 4);
 
-            if (ep.row_absmax) atomic_max_pos(ep.row_absmax + row, rmax);
+            if (ep.row_absmax) atomic_max_pos(ep.row_absmax + m0 + q * 32 + lane, rmax);
             if (ep.out_absmax) {
                 float wmax;
                 asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(wmax) : "f"(rmax));
@@ -304,83 +511,42 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
 
             if constexpr (FUSED) {
-                // ---- row absmax is complete once every tile of this row block has
-                // published its maxima: count tiles per row block in global memory and
-                // wait (bounded) for the count.  All CTAs are co-resident (grid <= SMs)
-                // and walk the tiles in row-block order, so the tiles being waited for
-                // are running now or next on some other SM. ----
-                const int mb = tile / tiles_n;
-                __threadfence();
-                asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
-                if (et == 0) {
-                    atomicAdd(ep.block_done + mb, 1u);
-                    bool done = false;
-                    for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
-                        unsigned int v;
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ep.block_done + mb) : "memory");
-                        if (v >= (unsigned int)tiles_n) { done = true; break; }
-                    }
-                    if (!done) atomicExch(status, kDeviceTimeoutMagic);
+                // ---- the four warps that share these 32 rows combine their maxima in shared
+                // memory (double buffered, one named barrier per lane quarter) and the first
+                // of them publishes one word per row for this tile ----
+                float* cq = cmb + (buf * 4 + q) * (kSlices * 32);
+                cq[slice * 32 + lane] = rmax;
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + q), "n"(kSlices * 32) : "memory");
+                if (slice == 0) {
+                    float m4 = rmax;
+#pragma unroll
+                    for (int k = 1; k < kSlices; ++k) m4 = fmaxf(m4, cq[k * 32 + lane]);
+                    publish_row_max(ep.row_parts + ((size_t)m0 * tiles_n + (tile % tiles_n) * 128) + q * 32 + lane, m4);
                 }
-                asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
-                float amax;
-                asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(amax) : "l"(ep.row_absmax + row) : "memory");
-                amax = fmaxf(amax, 1e-8f);
-                const float inv = 127.f / amax;
-                if (n0 == 0 && half == 0) ep.row_scale[row] = amax / 127.f;
-
-                // ---- quantise the fp16-rounded values (the reference quantises what it
-                // stored as fp16) and write int8, 64 columns = 64 bytes per row at a time
-                // through the same swizzled staging block ----
-                int8_t* c8blk = ep.C8 + (size_t)(m0 + q * 32) * N + n0 + c0;
+                trace_lt = lt;
+                if constexpr (DEFER) {
+                    // requantise the PREVIOUS tile: by now every CTA that shares its row block
+                    // has published, so its maxima are there at the first look
+                    if (p_m0 >= 0) finalize(p_m0, p_n0, tiles_n <= kGatherAhead);
+                }
 #pragma unroll
-                for (int col = 0; col < HC; col += 64) {
-                    constexpr int kFull = 16;                      // words of 4 int8 in a 64-column chunk
-                    const int nw = (HC - col >= 64) ? kFull : (HC - col) / 4;   // 16, or 8 for a 32-column tail
-                    uint32_t w8[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (j < nw) {
-                            const int hbase = col / 2 + 2 * j;     // two packed-fp16 words = four values
-                            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&hv[hbase]));
-                            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hv[hbase + 1]));
-                            const int q0 = __float2int_rn(fmaxf(-128.f, fminf(127.f, a.x * inv)));
-                            const int q1 = __float2int_rn(fmaxf(-128.f, fminf(127.f, a.y * inv)));
-                            const int q2 = __float2int_rn(fmaxf(-128.f, fminf(127.f, b.x * inv)));
-                            const int q3 = __float2int_rn(fmaxf(-128.f, fminf(127.f, b.y * inv)));
-                            w8[j] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) |
-                                    ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
-                        } else {
-                            w8[j] = 0u;
-                        }
-                    }
-                    const int nslot = nw / 4;                      // 16-byte slots per row: 4 or 2
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (j < nslot)
-                            *reinterpret_cast<uint4*>(cst + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
-                                make_uint4(w8[4 * j], w8[4 * j + 1], w8[4 * j + 2], w8[4 * j + 3]);
-                    __syncwarp();
-                    if (nslot == 4) {
-#pragma unroll
-                        for (int it = 0; it < 4; ++it) {
-                            const int rr2 = it * 8 + (lane >> 2);
-                            const int j = lane & 3;
-                            const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 64 + ((j ^ ((rr2 >> 1) & 3)) << 4));
-                            *reinterpret_cast<uint4*>(c8blk + (size_t)rr2 * N + col + j * 16) = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int it = 0; it < 2; ++it) {
-                            const int rr2 = it * 16 + (lane >> 1);
-                            const int j = lane & 1;
-                            const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 64 + ((j ^ ((rr2 >> 1) & 3)) << 4));
-                            *reinterpret_cast<uint4*>(c8blk + (size_t)rr2 * N + col + j * 16) = v;
-                        }
-                    }
+                for (int jc = 0; jc < HC / 8; ++jc)
+                    *reinterpret_cast<uint4*>(cst + lane * (HC * 2) + (stash_swz<HC>(lane, jc) << 4)) =
+                        make_uint4(hv[4 * jc], hv[4 * jc + 1], hv[4 * jc + 2], hv[4 * jc + 3]);
+                __syncwarp();
+                if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 8);
+                if constexpr (DEFER) {
+                    p_m0 = m0;
+                    p_n0 = n0;
+                } else {
+                    // at once: with a long K loop the MMAs of the next tile cover the wait
+                    finalize(m0, n0, false);
                 }
             }
+            if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 5);
+        }
+        if constexpr (FUSED && DEFER) {
+            if (p_m0 >= 0) finalize(p_m0, p_n0, false);
         }
     }
 
@@ -391,6 +557,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+    if (threadIdx.x == 0) I8TK_TRACE(3);
 }
 
 // ---------------------------------------------------------------------------
@@ -513,15 +680,16 @@ int sm_count_mlp() {
     return n;
 }
 
-template <int BN, bool GELU, bool FUSED>
+template <int BN, bool GELU, bool FUSED, bool DEFER>
 int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                 uint32_t* status, cudaStream_t st) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, FUSED>;
+    static_assert(Cfg::SMEM_BYTES <= 232448, "tile configuration exceeds the shared memory of an SM");
     static bool attr_done[64] = {false};
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU, FUSED, DEFER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::SMEM_BYTES));
         attr_done[dev] = true;
     }
@@ -541,16 +709,14 @@ int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep
         I8TK_REQUIRE(tiles_n <= sms, I8TK_ERR_UNSUPPORTED,
                      "row of %d tiles does not fit one round of %d CTAs", tiles_n, sms);
     }
-    gemm_i8_kernel<BN, GELU, FUSED><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status);
+    gemm_i8_kernel<BN, GELU, FUSED, DEFER><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }
 
-template <bool GELU, bool FUSED>
-int launch_gemm_bn(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
-                   uint32_t* status, cudaStream_t st) {
-    // Tile width: among the widths that divide N, the one with the least
-    // (rounds of CTAs over the SMs) x (tile width); ties go to the wider tile.
+// Tile width: among the widths that divide N, the one with the least
+// (rounds of CTAs over the SMs) x (tile width); ties go to the wider tile.
+int pick_bn(int M, int N, bool b_mn) {
     const int sms = sm_count_mlp();
     const int widths[3] = {256, 192, 128};
     int best = 128;
@@ -563,9 +729,16 @@ int launch_gemm_bn(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams&
         const long long cost = ((tiles + sms - 1) / sms) * bn;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
-    if (best == 256) return launch_gemm<256, GELU, FUSED>(A, B, b_mn, ep, M, N, K, status, st);
-    if (best == 192) return launch_gemm<192, GELU, FUSED>(A, B, b_mn, ep, M, N, K, status, st);
-    return launch_gemm<128, GELU, FUSED>(A, B, b_mn, ep, M, N, K, status, st);
+    return best;
+}
+
+template <bool GELU, bool FUSED, bool DEFER>
+int launch_gemm_bn(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
+                   uint32_t* status, cudaStream_t st) {
+    const int best = pick_bn(M, N, b_mn);
+    if (best == 256) return launch_gemm<256, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
+    if (best == 192) return launch_gemm<192, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
+    return launch_gemm<128, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
 }
 
 int requant_grid(long long vecs) {
@@ -578,19 +751,17 @@ int requant_grid(long long vecs) {
 // workspace carve-up
 struct MlpWorkspace {
     uint32_t* status;
-    float* hid_absmax;    // [T]
-    float* out_absmax;    // [T]   (per-token output)  -- zeroed together with the two below
-    float* tensor_absmax; // [1]
-    unsigned int* done1;  // [T/128] row-block tile counters, GEMM1
-    unsigned int* done2;  // [T/128] row-block tile counters, GEMM2
+    float* hid_absmax;    // [T]   zeroed together with the one below; used by the routes
+    float* tensor_absmax; // [1]   that keep fp16 intermediates (legacy output scale, A/B route)
+    uint32_t* parts1;     // [T/128][d_ff / BN1][128]     row maxima of GEMM1 per tile; these two
+    uint32_t* parts2;     // [T/128][d_model / BN2][128]  are contiguous and start as 0xFF bytes
     float* hid_scale;     // [T]
     __half* hid_f16;      // [T, d_ff]
     int8_t* hid_i8;       // [T, d_ff]
     __half* out_f16;      // [T, d_model]
-    int8_t* w1t;          // [d_ff, d_model]  (only when the weights are not prepacked)
-    int8_t* w2t;          // [d_model, d_ff]
     size_t bytes;
     size_t zero_bytes;    // hid_absmax .. tensor_absmax
+    size_t ones_bytes;    // parts1 .. parts2
 };
 
 MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
@@ -598,39 +769,31 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
     size_t off = 0;
     auto take = [&](size_t n) { size_t o = off; off = round_up(off + n, 256); return o; };
     unsigned char* b = static_cast<unsigned char*>(base);
+    const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
     const size_t o_status = take(256);
     const size_t o_habs = take((size_t)T * 4);
-    const size_t o_oabs = take((size_t)T * 4);
     const size_t o_tabs = take(256);
-    const size_t o_d1 = take((size_t)(T / 128 + 1) * 4);
-    const size_t o_d2 = take((size_t)(T / 128 + 1) * 4);
     const size_t zero_end = off;
+    const size_t o_p1 = take((size_t)T * (d_ff / pick_bn(T, d_ff, b_mn)) * 4);
+    const size_t o_p2 = take((size_t)T * (d_model / pick_bn(T, d_model, b_mn)) * 4);
+    const size_t ones_end = off;
     const size_t o_hsc = take((size_t)T * 4);
     const size_t o_h16 = take((size_t)T * d_ff * 2);
     const size_t o_hi8 = take((size_t)T * d_ff);
     const size_t o_o16 = take((size_t)T * d_model * 2);
-    size_t o_w1 = 0, o_w2 = 0;
-    if (!(flags & I8TK_MLP_PREPACKED)) {
-        o_w1 = take((size_t)d_model * d_ff);
-        o_w2 = take((size_t)d_model * d_ff);
-    }
     w.bytes = off;
     w.zero_bytes = zero_end - o_habs;
+    w.ones_bytes = ones_end - o_p1;
     if (b) {
         w.status = reinterpret_cast<uint32_t*>(b + o_status);
         w.hid_absmax = reinterpret_cast<float*>(b + o_habs);
-        w.out_absmax = reinterpret_cast<float*>(b + o_oabs);
         w.tensor_absmax = reinterpret_cast<float*>(b + o_tabs);
-        w.done1 = reinterpret_cast<unsigned int*>(b + o_d1);
-        w.done2 = reinterpret_cast<unsigned int*>(b + o_d2);
+        w.parts1 = reinterpret_cast<uint32_t*>(b + o_p1);
+        w.parts2 = reinterpret_cast<uint32_t*>(b + o_p2);
         w.hid_scale = reinterpret_cast<float*>(b + o_hsc);
         w.hid_f16 = reinterpret_cast<__half*>(b + o_h16);
         w.hid_i8 = reinterpret_cast<int8_t*>(b + o_hi8);
         w.out_f16 = reinterpret_cast<__half*>(b + o_o16);
-        if (!(flags & I8TK_MLP_PREPACKED)) {
-            w.w1t = reinterpret_cast<int8_t*>(b + o_w1);
-            w.w2t = reinterpret_cast<int8_t*>(b + o_w2);
-        }
     }
     return w;
 }
@@ -639,6 +802,18 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
 }  // namespace i8tk
 
 using namespace i8tk;
+
+#ifdef I8TK_GEMM_TRACE
+extern "C" int i8tk_debug_gemm_trace(long long* host_dst, int clear) {
+    if (host_dst) I8TK_CUDA(cudaMemcpyFromSymbol(host_dst, g_gemm_trace, sizeof(long long) * 148 * kTraceSlots));
+    if (clear) {
+        void* p = nullptr;
+        I8TK_CUDA(cudaGetSymbolAddress(&p, g_gemm_trace));
+        I8TK_CUDA(cudaMemset(p, 0, sizeof(long long) * 148 * kTraceSlots));
+    }
+    return I8TK_OK;
+}
+#endif
 
 extern "C" int i8tk_transpose_int8_weights(const int8_t* W1, const int8_t* W2, int8_t* W1T,
                                            int8_t* W2T, int d_model, int d_ff, i8tk_stream_t stream) {
@@ -679,65 +854,55 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     // Weights as the caller holds them ([K][N], N contiguous) are read in place through
-    // MN-major operand descriptors; I8TK_MLP_TRANSPOSE_WEIGHTS=1 restores the older route
-    // that transposes them into the workspace on every call (kept for A/B checks).
-    static const bool force_transpose = [] {
-        const char* e = getenv("I8TK_MLP_TRANSPOSE_WEIGHTS");
-        return e && atoi(e) != 0;
-    }();
-    const int8_t* W1T = W1;
-    const int8_t* W2T = W2;
-    bool b_mn = !(flags & I8TK_MLP_PREPACKED);
+    // MN-major operand descriptors; prepacked ones ([N][K]) through K-major descriptors.
+    const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
     int rc;
-    if (b_mn && force_transpose) {
-        rc = transpose_i8(W1, w.w1t, d_model, d_ff, st);
-        if (rc != I8TK_OK) return rc;
-        rc = transpose_i8(W2, w.w2t, d_ff, d_model, st);
-        if (rc != I8TK_OK) return rc;
-        W1T = w.w1t;
-        W2T = w.w2t;
-        b_mn = false;
-    }
-    I8TK_CUDA(cudaMemsetAsync(w.hid_absmax, 0, w.zero_bytes, st));
-
     const int per_token = (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0;
     const int per_channel = (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0;
 
-    // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token.
-    // Few rows (launch-bound): the epilogue keeps each row's values in registers,
-    // exchanges the row absmax between the CTAs of a row block and writes int8
-    // directly.  Many rows: a row block spans 12-16 CTAs and waiting for all of them
-    // costs more than it saves, so the fp16 hidden goes through a requant pass.
-    static const int fuse_rows_max = [] {
-        const char* e = getenv("I8TK_MLP_FUSE_GEMM1_MAX_ROWS");
-        return e ? atoi(e) : 1024;
+    // I8TK_MLP_GEMM1_UNFUSED=1 keeps the older route for GEMM1 (fp16 hidden + a requant
+    // pass) for A/B checks.
+    static const bool gemm1_unfused = [] {
+        const char* e = getenv("I8TK_MLP_GEMM1_UNFUSED");
+        return e && atoi(e) != 0;
     }();
-    if (T <= fuse_rows_max) {
-        EpiParams e1{scale_x, scale_W1, bias1, nullptr, w.hid_absmax, nullptr, per_token, per_channel,
-                     w.hid_i8, w.hid_scale, w.done1};
-        rc = launch_gemm_bn<true, true>(x, W1T, b_mn, e1, T, d_ff, d_model, w.status, st);
+    I8TK_CUDA(cudaMemsetAsync(w.parts1, 0xFF, w.ones_bytes, st));
+    if (gemm1_unfused || !out_row_scales) I8TK_CUDA(cudaMemsetAsync(w.hid_absmax, 0, w.zero_bytes, st));
+
+    // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token inside the
+    // GEMM's epilogue: the fp16 values of a tile wait in shared memory while the row
+    // maxima of its row block (12-16 tiles on as many SMs) are exchanged through global
+    // memory, and are quantised one tile later, when that exchange has long finished.
+    if (!gemm1_unfused) {
+        EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, nullptr, per_token, per_channel,
+                     w.hid_i8, w.hid_scale, w.parts1};
+        rc = launch_gemm_bn<true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
     } else {
         EpiParams e1{scale_x, scale_W1, bias1, w.hid_f16, w.hid_absmax, nullptr, per_token, per_channel,
                      nullptr, nullptr, nullptr};
-        rc = launch_gemm_bn<true, false>(x, W1T, b_mn, e1, T, d_ff, d_model, w.status, st);
+        rc = launch_gemm_bn<true, false, false>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
         requant_rows_kernel<false><<<requant_grid((long long)T * d_ff / 16), 256, 0, st>>>(
             w.hid_f16, w.hid_absmax, w.hid_i8, w.hid_scale, T, d_ff);
         I8TK_CUDA(cudaGetLastError());
     }
+#ifdef I8TK_GEMM_TRACE
+    if (getenv("I8TK_TRACE_GEMM1_ONLY")) return I8TK_OK;
+#endif
     if (out_row_scales) {
-        // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way
-        EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, w.out_absmax, nullptr, 1, per_channel,
-                     out, out_row_scales, w.done2};
-        rc = launch_gemm_bn<false, true>(w.hid_i8, W2T, b_mn, e2, T, d_model, d_ff, w.status, st);
+        // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way, but
+        // at once: with K = d_ff the MMAs of the next tile cover the exchange
+        EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, nullptr, nullptr, 1, per_channel,
+                     out, out_row_scales, w.parts2};
+        rc = launch_gemm_bn<false, true, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
         if (rc != I8TK_OK) return rc;
         return I8TK_OK;
     }
     // legacy per-tensor output scale: fp16 out + global absmax, then one requant pass
     EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, nullptr, w.tensor_absmax, 1, per_channel,
                  nullptr, nullptr, nullptr};
-    rc = launch_gemm_bn<false, false>(w.hid_i8, W2T, b_mn, e2, T, d_model, d_ff, w.status, st);
+    rc = launch_gemm_bn<false, false, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
     if (rc != I8TK_OK) return rc;
     requant_rows_kernel<true><<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
         w.out_f16, w.tensor_absmax, out, out_tensor_scale, T, d_model);
