@@ -680,6 +680,35 @@ int sm_count_mlp() {
     return n;
 }
 
+// CTAs of a persistent launch.  Fused kernels: the CTAs that share a row block wait for
+// one another, so every round of the persistent loop covers whole row blocks.
+int gemm_grid(int M, int N, int bn, bool fused) {
+    const int sms = sm_count_mlp();
+    const int tiles_n = N / bn;
+    const long long tiles = (long long)(M / BM) * tiles_n;
+    int grid = tiles < sms ? (int)tiles : sms;
+    if (fused && grid > tiles_n) grid = (grid / tiles_n) * tiles_n;
+    return grid > 0 ? grid : 1;
+}
+
+// Tile width: among the widths that divide N, the one with the least
+// (rounds of the persistent loop) x (tile width); ties go to the wider tile.
+int pick_bn(int M, int N, bool b_mn, bool fused) {
+    const int widths[3] = {256, 192, 128};
+    int best = 128;
+    long long best_cost = -1;
+    for (int i = 0; i < 3; ++i) {
+        const int bn = widths[i];
+        if (N % bn) continue;
+        if (b_mn && bn % 128) continue;          // [K][N] weights come in 128-wide slabs
+        const long long tiles = (long long)(M / BM) * (N / bn);
+        const int grid = gemm_grid(M, N, bn, fused);
+        const long long cost = ((tiles + grid - 1) / grid) * bn;
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 template <int BN, bool GELU, bool FUSED, bool DEFER>
 int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                 uint32_t* status, cudaStream_t st) {
@@ -698,44 +727,18 @@ int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep
     if (rc != I8TK_OK) return rc;
     rc = b_mn ? make_map_mn(&tmB, B, K, N) : make_map(&tmB, B, N, K, BN);
     if (rc != I8TK_OK) return rc;
-    const int tiles = (M / BM) * (N / BN);
-    const int sms = sm_count_mlp();
-    int grid = tiles < sms ? tiles : sms;
-    if (FUSED) {
-        // CTAs that share a row block wait for one another: keep every round of the
-        // persistent loop on whole row blocks so a block never straddles two rounds.
-        const int tiles_n = N / BN;
-        if (grid > tiles_n) grid = (grid / tiles_n) * tiles_n;
-        I8TK_REQUIRE(tiles_n <= sms, I8TK_ERR_UNSUPPORTED,
-                     "row of %d tiles does not fit one round of %d CTAs", tiles_n, sms);
-    }
+    const int grid = gemm_grid(M, N, BN, FUSED);
+    I8TK_REQUIRE(!FUSED || N / BN <= sm_count_mlp(), I8TK_ERR_UNSUPPORTED,
+                 "row of %d tiles does not fit one round of CTAs", N / BN);
     gemm_i8_kernel<BN, GELU, FUSED, DEFER><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }
 
-// Tile width: among the widths that divide N, the one with the least
-// (rounds of CTAs over the SMs) x (tile width); ties go to the wider tile.
-int pick_bn(int M, int N, bool b_mn) {
-    const int sms = sm_count_mlp();
-    const int widths[3] = {256, 192, 128};
-    int best = 128;
-    long long best_cost = -1;
-    for (int i = 0; i < 3; ++i) {
-        const int bn = widths[i];
-        if (N % bn) continue;
-        if (b_mn && bn % 128) continue;          // [K][N] weights come in 128-wide slabs
-        const long long tiles = (long long)(M / BM) * (N / bn);
-        const long long cost = ((tiles + sms - 1) / sms) * bn;
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
-    }
-    return best;
-}
-
 template <bool GELU, bool FUSED, bool DEFER>
 int launch_gemm_bn(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                    uint32_t* status, cudaStream_t st) {
-    const int best = pick_bn(M, N, b_mn);
+    const int best = pick_bn(M, N, b_mn, FUSED);
     if (best == 256) return launch_gemm<256, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
     if (best == 192) return launch_gemm<192, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
     return launch_gemm<128, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
@@ -774,8 +777,8 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
     const size_t o_habs = take((size_t)T * 4);
     const size_t o_tabs = take(256);
     const size_t zero_end = off;
-    const size_t o_p1 = take((size_t)T * (d_ff / pick_bn(T, d_ff, b_mn)) * 4);
-    const size_t o_p2 = take((size_t)T * (d_model / pick_bn(T, d_model, b_mn)) * 4);
+    const size_t o_p1 = take((size_t)T * (d_ff / pick_bn(T, d_ff, b_mn, true)) * 4);
+    const size_t o_p2 = take((size_t)T * (d_model / pick_bn(T, d_model, b_mn, true)) * 4);
     const size_t ones_end = off;
     const size_t o_hsc = take((size_t)T * 4);
     const size_t o_h16 = take((size_t)T * d_ff * 2);
