@@ -13,18 +13,30 @@
 namespace i8tk {
 namespace {
 
-template <typename T> struct Vec16;          // 16 bytes of input elements
+template <typename T> struct Vec16;          // 16 bytes of input elements, kept as loaded
 template <> struct Vec16<float> {
     static constexpr int N = 4;
-    __device__ static void load(const float* p, float (&v)[4]) {
-        const float4 t = *reinterpret_cast<const float4*>(p);
-        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    __device__ static uint4 load(const float* p) { return *reinterpret_cast<const uint4*>(p); }
+    __device__ static float absmax(const uint4& t) {
+        return fmaxf(fmaxf(fabsf(__uint_as_float(t.x)), fabsf(__uint_as_float(t.y))),
+                     fmaxf(fabsf(__uint_as_float(t.z)), fabsf(__uint_as_float(t.w))));
+    }
+    __device__ static void to_float(const uint4& t, float (&v)[4]) {
+        v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y);
+        v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
     }
 };
 template <> struct Vec16<__half> {
     static constexpr int N = 8;
-    __device__ static void load(const __half* p, float (&v)[8]) {
-        const uint4 t = *reinterpret_cast<const uint4*>(p);
+    __device__ static uint4 load(const __half* p) { return *reinterpret_cast<const uint4*>(p); }
+    // the maximum of fp16 values is exact in fp16: reduce as packed halves, convert once
+    __device__ static float absmax(const uint4& t) {
+        const __half2* h = reinterpret_cast<const __half2*>(&t);
+        const __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+        const float2 f = __half22float2(m);
+        return fmaxf(f.x, f.y);
+    }
+    __device__ static void to_float(const uint4& t, float (&v)[8]) {
         const __half2* h = reinterpret_cast<const __half2*>(&t);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -40,23 +52,36 @@ __device__ __forceinline__ int quant1(float x, float scale) {
     return (int)fminf(fmaxf(r, -128.f), 127.f);
 }
 
-// Same result with the division amortised over the row: `rcp` is the correctly
-// rounded 1/scale; one Newton step (two FMAs) gives the quotient to within an
-// ulp, which can only change the rounded code when the quotient sits on a
-// rounding tie -- there (|frac - 0.5| < 1e-4, about 0.02 % of elements; an ulp
-// of a quotient <= 128 is below 8e-6) the IEEE division is done after all.
-__device__ __forceinline__ int quant1_rcp(float x, float scale, float rcp) {
-    const float q0 = x * rcp;
-    const float e = fmaf(-q0, scale, x);
-    const float q1 = fmaf(e, rcp, q0);
-    float r = rintf(q1);
-    if (fabsf(q1 - r) > 0.4999f) r = rintf(__fdiv_rn(x, scale));
-    return (int)fminf(fmaxf(r, -128.f), 127.f);
-}
-
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
     return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
            ((uint32_t)(d & 0xff) << 24);
+}
+
+// Four codes with the division amortised over the row, bit-identical to quant1.
+// `rcp` is the correctly rounded 1/scale; one Newton step (two FMAs) gives the quotient to
+// within an ulp, which can only change the rounded code when the quotient sits on a rounding
+// tie -- there (|frac - 0.5| < 1e-4, about 0.02 % of elements; an ulp of a quotient <= 128 is
+// below 8e-6) the IEEE division is done after all.  Rounding to nearest even is the addition
+// of 1.5 * 2^23, which leaves the code in the low byte of the sum; |x / scale| <= 127 by
+// construction of the scale, so no clamp is needed.  Packed fp32x2 arithmetic throughout: no
+// conversion or rounding instruction (those run at a quarter of the FMA rate).
+__device__ __forceinline__ uint32_t quant4(float x0, float x1, float x2, float x3, float scale, float rcp) {
+    const f32x2 rcp2 = pack2(rcp, rcp), nscale2 = pack2(-scale, -scale);
+    const f32x2 magic2 = pack2(12582912.f, 12582912.f), nmagic2 = pack2(-12582912.f, -12582912.f);
+    const f32x2 mone2 = pack2(-1.f, -1.f);
+    const f32x2 xa = pack2(x0, x1), xb = pack2(x2, x3);
+    const f32x2 qa0 = mul2(xa, rcp2), qb0 = mul2(xb, rcp2);
+    const f32x2 qa = fma2(fma2(qa0, nscale2, xa), rcp2, qa0);
+    const f32x2 qb = fma2(fma2(qb0, nscale2, xb), rcp2, qb0);
+    const f32x2 ra = add2(qa, magic2), rb = add2(qb, magic2);          // low byte = code
+    const float2 da = unpack2(fma2(add2(ra, nmagic2), mone2, qa));     // q - rne(q)
+    const float2 db = unpack2(fma2(add2(rb, nmagic2), mone2, qb));
+    const float2 fa = unpack2(ra), fb = unpack2(rb);
+    uint32_t w = prmt(prmt(__float_as_uint(fa.x), __float_as_uint(fa.y), 0x0040u),
+                      prmt(__float_as_uint(fb.x), __float_as_uint(fb.y), 0x0040u), 0x5410u);
+    if (fmaxf(fmaxf(fabsf(da.x), fabsf(da.y)), fmaxf(fabsf(db.x), fabsf(db.y))) > 0.4999f)
+        w = pack4(quant1(x0, scale), quant1(x1, scale), quant1(x2, scale), quant1(x3, scale));
+    return w;
 }
 
 // Rows of `cols` elements, cols a multiple of Vec16<T>::N.  A row is handled by a
@@ -78,29 +103,23 @@ quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
     // name all 32 lanes); rows past the end are predicated off.
     for (long long w0 = warp * GPW * R; w0 < rows; w0 += nwarps * GPW * R) {
         const long long r0 = w0 + (long long)group_in_warp * R;
-        float v[R][NV][N];
+        uint4 raw[R][NV];
         float amax[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            amax[r] = 0.f;
             const long long row = r0 + r;
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 const int vi = lane_in_group + j * G;
-                if (row < rows && vi < nvec) {
-                    Vec16<T>::load(x + row * cols + (long long)vi * N, v[r][j]);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < N; ++e) v[r][j][e] = 0.f;
-                }
+                raw[r][j] = (row < rows && vi < nvec) ? Vec16<T>::load(x + row * cols + (long long)vi * N)
+                                                      : make_uint4(0u, 0u, 0u, 0u);
             }
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
+            amax[r] = 0.f;
 #pragma unroll
-            for (int j = 0; j < NV; ++j)
-#pragma unroll
-                for (int e = 0; e < N; ++e) amax[r] = fmaxf(amax[r], fabsf(v[r][j][e]));
+            for (int j = 0; j < NV; ++j) amax[r] = fmaxf(amax[r], Vec16<T>::absmax(raw[r][j]));
 #pragma unroll
             for (int o = G / 2; o > 0; o >>= 1)
                 amax[r] = fmaxf(amax[r], __shfl_xor_sync(0xffffffffu, amax[r], o));
@@ -117,16 +136,14 @@ quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
                 const int vi = lane_in_group + j * G;
                 if (vi >= nvec) continue;
                 int8_t* dst = q + row * cols + (long long)vi * N;
+                float v[N];
+                Vec16<T>::to_float(raw[r][j], v);
                 if constexpr (N == 4) {
-                    *reinterpret_cast<uint32_t*>(dst) =
-                        pack4(quant1_rcp(v[r][j][0], scale, rcp), quant1_rcp(v[r][j][1], scale, rcp),
-                              quant1_rcp(v[r][j][2], scale, rcp), quant1_rcp(v[r][j][3], scale, rcp));
+                    *reinterpret_cast<uint32_t*>(dst) = quant4(v[0], v[1], v[2], v[3], scale, rcp);
                 } else {
                     uint2 pk;
-                    pk.x = pack4(quant1_rcp(v[r][j][0], scale, rcp), quant1_rcp(v[r][j][1], scale, rcp),
-                                 quant1_rcp(v[r][j][2], scale, rcp), quant1_rcp(v[r][j][3], scale, rcp));
-                    pk.y = pack4(quant1_rcp(v[r][j][4], scale, rcp), quant1_rcp(v[r][j][5], scale, rcp),
-                                 quant1_rcp(v[r][j][6], scale, rcp), quant1_rcp(v[r][j][7], scale, rcp));
+                    pk.x = quant4(v[0], v[1], v[2], v[3], scale, rcp);
+                    pk.y = quant4(v[4], v[5], v[6], v[7], scale, rcp);
                     *reinterpret_cast<uint2*>(dst) = pk;
                 }
             }
