@@ -174,6 +174,8 @@ PROFILE_CASES = {
     "decode_d128": (8, 8, 128, 8192),      # 134 MB
     "mlp_m4096_768": (4096, 768, 3072),    # fused MLP forward (L2 resident by nature: 30 MB of operands)
     "mlp_m4096_1024": (4096, 1024, 4096),
+    "prefill_d64": (2, 8, 4096, 64),       # B, H, S, D: 512 CTAs of 128 query rows
+    "prefill_d128": (2, 8, 4096, 128),
 }
 
 
@@ -181,6 +183,19 @@ def run_profile_case(name):
     import torch
     pkg = importlib.import_module("int8-transformer-kernels_b200")
     ext = pkg.int8_ext
+    if name.startswith("prefill"):
+        b, h, sq, d = PROFILE_CASES[name]
+        g = torch.Generator(device="cuda").manual_seed(0)
+        t = []
+        for _ in range(3):
+            xi, sx = ext.quantize_per_token(torch.randn(b, h, sq, d, device="cuda", dtype=torch.float16, generator=g))
+            t.extend([xi, sx.reshape(-1).contiguous()])
+        for _ in range(3):
+            out = ext.int8_attention_forward(t[0], t[2], t[4], t[1], t[3], t[5])
+        torch.cuda.synchronize()
+        print(f"profile case {name}: B{b} H{h} S{sq} D{d}, ops per forward {4 * b * h * sq * sq * d}, "
+              f"checksum {float(out.float().sum()):.4f}")
+        return
     if name.startswith("mlp"):
         M, dm, dff = PROFILE_CASES[name]
         g = torch.Generator(device="cuda").manual_seed(0)

@@ -32,7 +32,9 @@ namespace {
 
 constexpr int kQT = 128;                 // query rows per CTA
 constexpr int kKT = 128;                 // KV positions per tile
-constexpr int kPrefillThreads = 320;     // TMA, MMA, 4 softmax, 4 converter warps
+constexpr int kSoftmaxWarps = 8;         // two per TMEM lane quarter: each thread owns half of a score row
+constexpr int kConvWarp0 = 2 + kSoftmaxWarps;
+constexpr int kPrefillThreads = (kConvWarp0 + 4) * 32;   // TMA, MMA, 8 softmax, 4 converter warps
 constexpr float kLazyStep = 8.0f;        // log2 units the true max may run ahead of the reference max
 
 template <int D>
@@ -46,9 +48,10 @@ struct PrefillCfg {
     static constexpr int OFF_VRAW = OFF_K + 2 * TILE_BYTES;
     static constexpr int OFF_V16 = OFF_VRAW + 2 * TILE_BYTES;
     static constexpr int OFF_P = OFF_V16 + 2 * V16_BYTES;
-    static constexpr int OFF_SCALES = OFF_P + P_BYTES;     // 4 warps x (sK[128] | sV[128]) fp32
-    static constexpr int OFF_BARS = OFF_SCALES + 4 * 2 * kKT * 4;
-    static constexpr int NUM_BARS = 20;
+    static constexpr int OFF_SCALES = OFF_P + 2 * P_BYTES; // 8 warps x 2 tiles x (sK[64] | sV[64]) fp32
+    static constexpr int OFF_XCH = OFF_SCALES + kSoftmaxWarps * 2 * 128 * 4;   // [2][2 halves][128 rows] fp32
+    static constexpr int OFF_BARS = OFF_XCH + 2 * 2 * kQT * 4;
+    static constexpr int NUM_BARS = 22;
     static constexpr int SMEM_BYTES = 1024 + OFF_BARS + NUM_BARS * 8 + 16;
     static constexpr int TMEM_COLS = 512;                  // S0 | S1 | O (D columns)
     static constexpr int TM_S0 = 0, TM_S1 = 128, TM_O = 256;
@@ -62,10 +65,10 @@ enum Bar : int {
     B_VREMPTY = 7,    // [2]
     B_SFULL = 9,      // [2]
     B_SEMPTY = 11,    // [2]
-    B_PFULL = 13,
-    B_V16FULL = 14,   // [2]
-    B_V16EMPTY = 16,  // [2]
-    B_PVDONE = 18,
+    B_PFULL = 13,     // [2]
+    B_V16FULL = 15,   // [2]
+    B_V16EMPTY = 17,  // [2]
+    B_PVDONE = 19,    // [2]
 };
 
 // four int8 (biased by XOR 0x80 -> u = v + 128) to four fp16, exactly:
@@ -118,12 +121,12 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             mbar_init(bar(B_VRFULL + i), 1);
             mbar_init(bar(B_VREMPTY + i), 4);
             mbar_init(bar(B_SFULL + i), 1);
-            mbar_init(bar(B_SEMPTY + i), 4);
+            mbar_init(bar(B_SEMPTY + i), kSoftmaxWarps);
             mbar_init(bar(B_V16FULL + i), 4);
             mbar_init(bar(B_V16EMPTY + i), 1);
+            mbar_init(bar(B_PFULL + i), kSoftmaxWarps);
+            mbar_init(bar(B_PVDONE + i), 1);
         }
-        mbar_init(bar(B_PFULL), 4);
-        mbar_init(bar(B_PVDONE), 1);
         fence_mbar_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -161,7 +164,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             bool ok = mbar_wait_spin_bounded(bar(B_QFULL), 0);
             auto issue_pv = [&](int t) -> bool {
                 // O (+)= P_t . V_t : 8 steps of 16 KV positions
-                if (!mbar_wait_spin_bounded(bar(B_PFULL), t & 1)) return false;
+                if (!mbar_wait_spin_bounded(bar(B_PFULL + (t & 1)), (t >> 1) & 1)) return false;
                 if (!mbar_wait_spin_bounded(bar(B_V16FULL + (t & 1)), (t >> 1) & 1)) return false;
                 tc_fence_after();
                 const uint32_t v16 = base_s + Cfg::OFF_V16 + (t & 1) * Cfg::V16_BYTES;
@@ -169,149 +172,229 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 #pragma unroll
                 for (int i = 0; i < kKT / 16; ++i) {
                     // A: K-major fp16, 64-wide blocks 16 KB apart, 32 bytes per step inside a block
-                    const uint64_t da = smem_desc_sw128(base_s + Cfg::OFF_P + (i >> 2) * Cfg::SLAB_BYTES) + 2 * (i & 3);
+                    const uint64_t da = smem_desc_sw128(base_s + Cfg::OFF_P + (t & 1) * Cfg::P_BYTES + (i >> 2) * Cfg::SLAB_BYTES) + 2 * (i & 3);
                     // B: MN-major fp16, 16 rows of 128 bytes per step
                     const uint64_t db = db0 + (uint64_t)(128 * i);
                     mma_f16(tmem_base + Cfg::TM_O, da, db, idesc_pv, (t | i) != 0);
                 }
                 tc_commit(bar(B_V16EMPTY + (t & 1)));
-                tc_commit(bar(B_PVDONE));
+                tc_commit(bar(B_PVDONE + (t & 1)));
                 return true;
             };
-            for (int j = 0; j < nt && ok; ++j) {
-                const int st = j & 1;
-                if (!mbar_wait_spin_bounded(bar(B_KFULL + st), (j >> 1) & 1) ||
-                    !mbar_wait_spin_bounded(bar(B_SEMPTY + st), ((j >> 1) & 1) ^ 1)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t ks = base_s + Cfg::OFF_K + st * Cfg::TILE_BYTES;
-                const uint64_t da = (D == 128) ? smem_desc_sw128(base_s + Cfg::OFF_Q) : smem_desc_sw64(base_s + Cfg::OFF_Q);
-                const uint64_t db = (D == 128) ? smem_desc_sw128(ks) : smem_desc_sw64(ks);
+            // Q.K^T runs two tiles ahead of P.V: the softmax warps convert the scores of tile j+1
+            // while they exponentiate tile j, so S(j+1) has to be on its way before P(j-1) is complete.
+            for (int j = 0; j < nt + 2 && ok; ++j) {
+                if (j < nt) {
+                    const int st = j & 1;
+                    if (!mbar_wait_spin_bounded(bar(B_KFULL + st), (j >> 1) & 1) ||
+                        !mbar_wait_spin_bounded(bar(B_SEMPTY + st), ((j >> 1) & 1) ^ 1)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t ks = base_s + Cfg::OFF_K + st * Cfg::TILE_BYTES;
+                    const uint64_t da = (D == 128) ? smem_desc_sw128(base_s + Cfg::OFF_Q) : smem_desc_sw64(base_s + Cfg::OFF_Q);
+                    const uint64_t db = (D == 128) ? smem_desc_sw128(ks) : smem_desc_sw64(ks);
 #pragma unroll
-                for (int k = 0; k < D / 32; ++k)
-                    mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * k, db + 2 * k, idesc_qk, k != 0);
-                tc_commit(bar(B_KEMPTY + st));
-                tc_commit(bar(B_SFULL + st));
-                if (j > 0) ok = issue_pv(j - 1);
+                    for (int k = 0; k < D / 32; ++k)
+                        mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * k, db + 2 * k, idesc_qk, k != 0);
+                    tc_commit(bar(B_KEMPTY + st));
+                    tc_commit(bar(B_SFULL + st));
+                }
+                if (j >= 2) ok = issue_pv(j - 2);
             }
-            if (ok) ok = issue_pv(nt - 1);
             if (!ok) atomicExch(status, kDeviceTimeoutMagic);
         }
-    } else if (warp < 6) {
-        // ================= softmax: one query row per thread =================
+    } else if (warp < kConvWarp0) {
+        // ================= softmax: half a query row (64 KV positions of every tile) per thread =================
+        const int sw = warp - 2;                         // 0..7
         const int q = warp & 3;                          // TMEM lane quarter of this warp
+        const int half = sw >> 2;                        // columns half*64 .. +63 of every score tile
         const int r = q * 32 + lane;                     // row inside the tile
-        float* wsc = reinterpret_cast<float*>(base + Cfg::OFF_SCALES) + (warp - 2) * 2 * kKT;   // sK | sV of a tile
-        const float qscale = sQ[(size_t)row_base + q0 + r] * score_scale_log2;
+        float* wsc = reinterpret_cast<float*>(base + Cfg::OFF_SCALES) + sw * 256;   // [tile & 1][sK[64] | sV[64]] of these columns
+        float* xch = reinterpret_cast<float*>(base + Cfg::OFF_XCH);                 // [2][half][row]
+        const float qscale = sQ[(size_t)row_base + q0 + r] * score_scale_log2;     // > 0
+        const f32x2 qs2 = pack2(qscale, qscale);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        unsigned char* Pm = base + Cfg::OFF_P;
-        float m_ref = -INFINITY, l = 0.f;
+        unsigned char* prow0 = base + Cfg::OFF_P + half * Cfg::SLAB_BYTES + r * 128;  // this row in this half's 64-wide K block
+        // int32 -> fp32 without the conversion unit: |q.k| <= 127*127*128 < 2^22, so adding the
+        // score to the bit pattern of 1.5*2^23 and subtracting 1.5*2^23 as a float is exact
+        constexpr uint32_t kMagicI = 0x4B400000u;
+        const f32x2 nmagic2 = pack2(-12582912.f, -12582912.f);
+        float m_ref = -INFINITY;
+        f32x2 l2 = 0ull;
         bool ok = true;
-        for (int j = 0; j < nt; ++j) {
-            const int st = j & 1;
-            // this tile's per-position scales, private to the warp
+        // this warp's per-position scales, fetched ahead of the tile that uses them
+        float pk0, pk1, pv0, pv1;
+        auto prefetch = [&](int j) {
+            const size_t o = (size_t)row_base + j * kKT + half * 64 + lane;
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk0) : "l"(sK + o));
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk1) : "l"(sK + o + 32));
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pv0) : "l"(sV + o));
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pv1) : "l"(sV + o + 32));
+        };
+        auto commit_scales = [&](int j) {                // prefetched registers -> this warp's block for tile j
+            float* w = wsc + (j & 1) * 128;
+            w[lane] = pk0;
+            w[32 + lane] = pk1;
+            w[64 + lane] = pv0;
+            w[96 + lane] = pv1;
             __syncwarp();
-#pragma unroll
-            for (int i = 0; i < kKT / 32; ++i) {
-                wsc[i * 32 + lane] = sK[(size_t)row_base + j * kKT + i * 32 + lane];
-                wsc[kKT + i * 32 + lane] = sV[(size_t)row_base + j * kKT + i * 32 + lane];
-            }
-            __syncwarp();
-            const bool got = mbar_wait_spin_bounded(bar(B_SFULL + st), (j >> 1) & 1);
-            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S1 : Cfg::TM_S0);
+        };
+        // y = (q.k) * sK for 8 columns of a score block held in registers, and their maximum
+        auto convert8 = [&](const uint32_t* sr8, const float* k8, f32x2* y4, float& mx) {
+            const float4 ka = *reinterpret_cast<const float4*>(k8);
+            const float4 kb = *reinterpret_cast<const float4*>(k8 + 4);
+            const f32x2 t01 = add2(pack2(__uint_as_float(sr8[0] + kMagicI), __uint_as_float(sr8[1] + kMagicI)), nmagic2);
+            const f32x2 t23 = add2(pack2(__uint_as_float(sr8[2] + kMagicI), __uint_as_float(sr8[3] + kMagicI)), nmagic2);
+            const f32x2 t45 = add2(pack2(__uint_as_float(sr8[4] + kMagicI), __uint_as_float(sr8[5] + kMagicI)), nmagic2);
+            const f32x2 t67 = add2(pack2(__uint_as_float(sr8[6] + kMagicI), __uint_as_float(sr8[7] + kMagicI)), nmagic2);
+            y4[0] = mul2(t01, pack2(ka.x, ka.y));
+            y4[1] = mul2(t23, pack2(ka.z, ka.w));
+            y4[2] = mul2(t45, pack2(kb.x, kb.y));
+            y4[3] = mul2(t67, pack2(kb.z, kb.w));
+            const float2 a = unpack2(y4[0]), b = unpack2(y4[1]), c = unpack2(y4[2]), d = unpack2(y4[3]);
+            mx = fmaxf(fmaxf(fmaxf(mx, fmaxf(a.x, a.y)), fmaxf(b.x, b.y)), fmaxf(fmaxf(c.x, c.y), fmaxf(d.x, d.y)));
+        };
+        // p = 2^(y*qscale - m_ref) for 8 columns; P*sV as one 16-byte chunk of fp16
+        auto exp8 = [&](const f32x2* y4, const float* v8, f32x2 nm2, unsigned char* dst) {
+            const float4 va = *reinterpret_cast<const float4*>(v8);
+            const float4 vb = *reinterpret_cast<const float4*>(v8 + 4);
+            const float2 a = unpack2(fma2(y4[0], qs2, nm2)), b = unpack2(fma2(y4[1], qs2, nm2));
+            const float2 c = unpack2(fma2(y4[2], qs2, nm2)), d = unpack2(fma2(y4[3], qs2, nm2));
+            const f32x2 p01 = pack2(ex2_approx(a.x), ex2_approx(a.y)), p23 = pack2(ex2_approx(b.x), ex2_approx(b.y));
+            const f32x2 p45 = pack2(ex2_approx(c.x), ex2_approx(c.y)), p67 = pack2(ex2_approx(d.x), ex2_approx(d.y));
+            l2 = add2(l2, add2(add2(p01, p23), add2(p45, p67)));
+            const float2 w01 = unpack2(mul2(p01, pack2(va.x, va.y))), w23 = unpack2(mul2(p23, pack2(va.z, va.w)));
+            const float2 w45 = unpack2(mul2(p45, pack2(vb.x, vb.y))), w67 = unpack2(mul2(p67, pack2(vb.z, vb.w)));
+            *reinterpret_cast<uint4*>(dst) =
+                make_uint4(pack_h2(w01.x, w01.y), pack_h2(w23.x, w23.y), pack_h2(w45.x, w45.y), pack_h2(w67.x, w67.y));
+        };
 
-            // ---- pass A: true row maximum of this tile (log2 units) ----
-            float mx = -INFINITY;
-            {
-                uint32_t sr[32];
-#pragma unroll 1
-                for (int cc = 0; cc < kKT / 32; ++cc) {
-                    tmem_ld32(s_addr + cc * 32, sr);
-                    tmem_ld_wait(sr);
+        // ---- prologue: scores of tile 0 into registers ----
+        f32x2 y[32];
+        float mx = -INFINITY;
+        prefetch(0);
+        commit_scales(0);
+        if (nt > 1) prefetch(1);
+        {
+            const bool got = mbar_wait_spin_bounded(bar(B_SFULL), 0);
+            ok = __all_sync(0xffffffffu, got);
+            if (ok) {
+                tc_fence_after();
+                uint32_t sr[2][16];
+                const uint32_t s_addr = lane_addr + Cfg::TM_S0 + half * 64;
+                tmem_ld16(s_addr, sr[0]);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        mx = fmaxf(mx, (float)(int)sr[i] * (qscale * wsc[cc * 32 + i]));
+                for (int cc = 0; cc < 4; ++cc) {
+                    tmem_ld_wait(sr[cc & 1]);
+                    if (cc < 3) tmem_ld16(s_addr + (cc + 1) * 16, sr[(cc + 1) & 1]);
+                    convert8(&sr[cc & 1][0], wsc + cc * 16, &y[cc * 8], mx);
+                    convert8(&sr[cc & 1][8], wsc + cc * 16 + 8, &y[cc * 8 + 4], mx);
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_SEMPTY));
             }
+        }
+
+        for (int j = 0; j < nt && ok; ++j) {
+            const int st = j & 1;
+            const bool has_next = j + 1 < nt;
+            // ---- row maximum across the two halves (shared memory, one named barrier per lane quarter) ----
+            xch[(st * 2 + half) * kQT + r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+            mx = fmaxf(mx, xch[(st * 2 + (half ^ 1)) * kQT + r]) * qscale;     // log2 units
+
             // lazy reference maximum: move it only when the true one ran ahead by kLazyStep
             const bool move = mx > m_ref + kLazyStep;
             const float m_new = move ? mx : m_ref;
             const float corr = move ? ex2_approx(m_ref - m_new) : 1.0f;
-            l *= corr;
+            if (move) l2 = mul2(l2, pack2(corr, corr));
             const bool warp_moves = __any_sync(0xffffffffu, move);
 
-            // ---- P buffer free and O quiescent once PV of the previous tile retired ----
-            if (j > 0) {
-                const bool got2 = mbar_wait_spin_bounded(bar(B_PVDONE), (j - 1) & 1);
+            // ---- this tile's P buffer is free once PV of tile j-2 retired; the output accumulator
+            // is touched only when the maximum moved, and then PV of tile j-1 must have retired too ----
+            if (j >= 2) {
+                const bool got2 = mbar_wait_spin_bounded(bar(B_PVDONE + st), ((j - 2) >> 1) & 1);
                 if (!__all_sync(0xffffffffu, got2)) { ok = false; break; }
+            }
+            if (j > 0 && warp_moves) {
+                const bool got3 = mbar_wait_spin_bounded(bar(B_PVDONE + (st ^ 1)), ((j - 1) >> 1) & 1);
+                if (!__all_sync(0xffffffffu, got3)) { ok = false; break; }
                 tc_fence_after();
-                if (warp_moves) {
-                    uint32_t o[32];
+                uint32_t o[32];                          // this thread rescales its half of the output columns
 #pragma unroll 1
-                    for (int cc = 0; cc < D / 32; ++cc) {
-                        tmem_ld32(lane_addr + Cfg::TM_O + cc * 32, o);
-                        tmem_ld_wait(o);
+                for (int cc = 0; cc < D / 64; ++cc) {
+                    const uint32_t oa = lane_addr + Cfg::TM_O + half * (D / 2) + cc * 32;
+                    tmem_ld32(oa, o);
+                    tmem_ld_wait(o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                        tmem_st32(lane_addr + Cfg::TM_O + cc * 32, o);
-                    }
-                    tmem_st_wait();
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    tmem_st32(oa, o);
                 }
+                tmem_st_wait();
             }
             m_ref = m_new;
 
-            // ---- pass B: p = 2^(x - m_ref), P*sV as fp16 into the swizzled K-major operand ----
-            {
-                uint32_t sr[32];
-#pragma unroll 1
-                for (int cc = 0; cc < kKT / 32; ++cc) {
-                    tmem_ld32(s_addr + cc * 32, sr);
-                    tmem_ld_wait(sr);
-                    uint32_t pk[16];
+            // ---- exponentials of this tile (special-function unit) interleaved, 8 columns at a time,
+            // with the conversion of the NEXT tile's scores (integer and FMA pipes), which take over
+            // the registers the exponentials have just released ----
+            unsigned char* prow = prow0 + st * Cfg::P_BYTES;
+            const float* vsc = wsc + st * 128 + 64;
+            const f32x2 nm2 = pack2(-m_ref, -m_ref);
+            mx = -INFINITY;
+            if (has_next) {
+                commit_scales(j + 1);
+                if (j + 2 < nt) prefetch(j + 2);
+                const bool got = mbar_wait_spin_bounded(bar(B_SFULL + (st ^ 1)), ((j + 1) >> 1) & 1);
+                if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+                tc_fence_after();
+                const float* ksc = wsc + (st ^ 1) * 128;
+                const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S0 : Cfg::TM_S1) + half * 64;
+                uint32_t sr[2][16];
+                tmem_ld16(s_addr, sr[0]);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float x0 = (float)(int)sr[i] * (qscale * wsc[cc * 32 + i]);
-                        const float x1 = (float)(int)sr[i + 1] * (qscale * wsc[cc * 32 + i + 1]);
-                        const float p0 = ex2_approx(x0 - m_ref);
-                        const float p1 = ex2_approx(x1 - m_ref);
-                        l += p0 + p1;
-                        pk[i >> 1] = pack_h2(p0 * wsc[kKT + cc * 32 + i], p1 * wsc[kKT + cc * 32 + i + 1]);
-                    }
-                    // 64-wide K block cc/2, 16-byte chunks (cc%2)*4 .. +3 of row r, XOR-swizzled by r%8
-                    unsigned char* prow = Pm + (cc >> 1) * Cfg::SLAB_BYTES + r * 128;
+                for (int cc = 0; cc < 4; ++cc) {
+                    tmem_ld_wait(sr[cc & 1]);
+                    if (cc < 3) tmem_ld16(s_addr + (cc + 1) * 16, sr[(cc + 1) & 1]);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int chunk = ((cc & 1) * 4 + k) ^ (r & 7);
-                        *reinterpret_cast<uint4*>(prow + chunk * 16) =
-                            make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+                    for (int h = 0; h < 2; ++h) {
+                        const int c = cc * 2 + h;        // 16-byte chunk of P / 8 columns
+                        exp8(&y[c * 4], vsc + c * 8, nm2, prow + ((c ^ (r & 7)) << 4));
+                        convert8(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx);
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_SEMPTY + (st ^ 1)));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) exp8(&y[c * 4], vsc + c * 8, nm2, prow + ((c ^ (r & 7)) << 4));
             }
             tc_fence_before();
             fence_proxy_async();                         // generic-proxy writes of P visible to the tensor core
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar(B_SEMPTY + st));
-                mbar_arrive(bar(B_PFULL));
-            }
+            if (lane == 0) mbar_arrive(bar(B_PFULL + st));
         }
-        // ---- epilogue: O / l -> fp16 ----
+        // ---- epilogue: O / l -> fp16, each thread its half of the output columns ----
         if (ok) {
-            const bool got = mbar_wait_spin_bounded(bar(B_PVDONE), (nt - 1) & 1);
+            const bool got = mbar_wait_spin_bounded(bar(B_PVDONE + ((nt - 1) & 1)), ((nt - 1) >> 1) & 1);
             ok = __all_sync(0xffffffffu, got);
         }
         if (ok) {
             tc_fence_after();
+            const float2 lp = unpack2(l2);
+            float l = lp.x + lp.y;
+            xch[half * kQT + r] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+            l += xch[(half ^ 1) * kQT + r];
             const float inv = 1.0f / l;
-            __half* orow = out + ((size_t)row_base + q0 + r) * D;
+            __half* orow = out + ((size_t)row_base + q0 + r) * D + half * (D / 2);
             uint32_t o[32];
 #pragma unroll 1
-            for (int cc = 0; cc < D / 32; ++cc) {
-                tmem_ld32(lane_addr + Cfg::TM_O + cc * 32, o);
+            for (int cc = 0; cc < D / 64; ++cc) {
+                tmem_ld32(lane_addr + Cfg::TM_O + half * (D / 2) + cc * 32, o);
                 tmem_ld_wait(o);
                 uint32_t hp[16];
 #pragma unroll
@@ -327,7 +410,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         }
     } else {
         // ================= converter: raw int8 V tile -> fp16, MN-major swizzled =================
-        const int r = threadIdx.x - 6 * 32;              // KV row of the tile handled by this thread
+        const int r = threadIdx.x - kConvWarp0 * 32;     // KV row of the tile handled by this thread
         for (int j = 0; j < nt; ++j) {
             const int st = j & 1;
             bool got = mbar_wait_spin_bounded(bar(B_VRFULL + st), (j >> 1) & 1);
