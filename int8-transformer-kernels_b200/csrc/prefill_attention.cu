@@ -10,15 +10,22 @@
 //   128x128 int32 accumulator in tensor memory (two buffers); PV is tcgen05.mma
 //   kind::f16 accumulating the 128xD fp32 output in tensor memory across all KV
 //   tiles.
-// * Q, K and raw V tiles arrive by TMA (swizzled K-major rows); four converter
+// * Q, K and raw V tiles arrive by TMA (swizzled K-major rows); two converter
 //   warps turn each int8 V tile into fp16 in the MN-major swizzled layout the
 //   PV instruction reads (int8 -> fp16 is exact).
-// * Four softmax warps own one query row per thread: they read the scores with
-//   tcgen05.ld, apply the scales in log2 units, keep a LAZY running maximum
-//   (it only moves when the true maximum exceeds it by 2^8, so p <= 256 stays
-//   comfortably inside fp16), write P*sV as fp16 into the swizzled K-major
-//   operand buffer, and rescale the output accumulator in tensor memory
-//   (tcgen05.ld / tcgen05.st) only on the rare tiles where the maximum moved.
+// * Eight softmax warps, two per TMEM lane quarter, each thread owning 64 KV
+//   positions of one query row.  The scores are read from tensor memory once
+//   (tcgen05.ld), converted without the conversion unit (|q.k| < 2^22, so the
+//   integer is added to the bit pattern of 1.5*2^23 and 1.5*2^23 subtracted as a
+//   float), scaled by sK and kept in registers; the row maximum is combined across
+//   the two halves through shared memory.  A LAZY running maximum (it only moves
+//   when the true maximum exceeds it by 2^8, so p <= 256 stays comfortably inside
+//   fp16) makes rescaling the output accumulator in tensor memory (tcgen05.ld /
+//   tcgen05.st) rare.  The exponentials of tile j (special-function unit) are
+//   interleaved, eight columns at a time, with the conversion of tile j+1's scores
+//   (integer and FMA pipes), which take over the registers just released; Q.K^T
+//   therefore runs two tiles ahead of P.V.  P*sV goes as fp16 into one of two
+//   swizzled K-major operand buffers.  Packed fp32x2 arithmetic throughout.
 // * Every mbarrier wait is bounded; on expiry a status word is set and all
 //   roles fall through to the common exit, which frees tensor memory.
 //
@@ -34,7 +41,8 @@ constexpr int kQT = 128;                 // query rows per CTA
 constexpr int kKT = 128;                 // KV positions per tile
 constexpr int kSoftmaxWarps = 8;         // two per TMEM lane quarter: each thread owns half of a score row
 constexpr int kConvWarp0 = 2 + kSoftmaxWarps;
-constexpr int kPrefillThreads = (kConvWarp0 + 4) * 32;   // TMA, MMA, 8 softmax, 4 converter warps
+constexpr int kConvWarps = 2;            // each converter thread takes 128 / (32 * kConvWarps) rows of a V tile
+constexpr int kPrefillThreads = (kConvWarp0 + kConvWarps) * 32;   // TMA, MMA, 8 softmax, 2 converter warps
 constexpr float kLazyStep = 8.0f;        // log2 units the true max may run ahead of the reference max
 
 template <int D>
@@ -84,10 +92,26 @@ __device__ __forceinline__ void i8x4_to_h2x2(uint32_t raw, uint32_t& lo, uint32_
     hi = *reinterpret_cast<const uint32_t*>(&h1);
 }
 
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
+
+#ifdef I8TK_PREFILL_TRACE
+// Development aid (not compiled into the library): clock stamps of one CTA's roles.
+constexpr int kPTraceSlots = 512;
+__device__ long long g_prefill_trace[kPTraceSlots];
+#define I8TK_PTRACE(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (slot) < kPTraceSlots) g_prefill_trace[(slot)] = clock64(); } while (0)
+#else
+#define I8TK_PTRACE(slot) do { } while (0)
+#endif
 
 template <int D>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
@@ -119,10 +143,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             mbar_init(bar(B_KFULL + i), 1);
             mbar_init(bar(B_KEMPTY + i), 1);
             mbar_init(bar(B_VRFULL + i), 1);
-            mbar_init(bar(B_VREMPTY + i), 4);
+            mbar_init(bar(B_VREMPTY + i), kConvWarps);
             mbar_init(bar(B_SFULL + i), 1);
             mbar_init(bar(B_SEMPTY + i), kSoftmaxWarps);
-            mbar_init(bar(B_V16FULL + i), 4);
+            mbar_init(bar(B_V16FULL + i), kConvWarps);
             mbar_init(bar(B_V16EMPTY + i), 1);
             mbar_init(bar(B_PFULL + i), kSoftmaxWarps);
             mbar_init(bar(B_PVDONE + i), 1);
@@ -200,8 +224,9 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                         mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * k, db + 2 * k, idesc_qk, k != 0);
                     tc_commit(bar(B_KEMPTY + st));
                     tc_commit(bar(B_SFULL + st));
+                    I8TK_PTRACE(256 + 4 * j);
                 }
-                if (j >= 2) ok = issue_pv(j - 2);
+                if (j >= 2) { ok = issue_pv(j - 2); I8TK_PTRACE(256 + 4 * (j - 2) + 1); }
             }
             if (!ok) atomicExch(status, kDeviceTimeoutMagic);
         }
@@ -254,7 +279,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             y4[2] = mul2(t45, pack2(kb.x, kb.y));
             y4[3] = mul2(t67, pack2(kb.z, kb.w));
             const float2 a = unpack2(y4[0]), b = unpack2(y4[1]), c = unpack2(y4[2]), d = unpack2(y4[3]);
-            mx = fmaxf(fmaxf(fmaxf(mx, fmaxf(a.x, a.y)), fmaxf(b.x, b.y)), fmaxf(fmaxf(c.x, c.y), fmaxf(d.x, d.y)));
+            mx = max3(max3(mx, a.x, a.y), max3(b.x, b.y, c.x), fmaxf(c.y, fmaxf(d.x, d.y)));
         };
         // p = 2^(y*qscale - m_ref) for 8 columns; P*sV as one 16-byte chunk of fp16
         auto exp8 = [&](const f32x2* y4, const float* v8, f32x2 nm2, unsigned char* dst) {
@@ -301,6 +326,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         for (int j = 0; j < nt && ok; ++j) {
             const int st = j & 1;
             const bool has_next = j + 1 < nt;
+            if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 0);
             // ---- row maximum across the two halves (shared memory, one named barrier per lane quarter) ----
             xch[(st * 2 + half) * kQT + r] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
@@ -336,6 +362,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 tmem_st_wait();
             }
             m_ref = m_new;
+            if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 1);
 
             // ---- exponentials of this tile (special-function unit) interleaved, 8 columns at a time,
             // with the conversion of the NEXT tile's scores (integer and FMA pipes), which take over
@@ -350,6 +377,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 const bool got = mbar_wait_spin_bounded(bar(B_SFULL + (st ^ 1)), ((j + 1) >> 1) & 1);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
                 tc_fence_after();
+                if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 2);
                 const float* ksc = wsc + (st ^ 1) * 128;
                 const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S0 : Cfg::TM_S1) + half * 64;
                 uint32_t sr[2][16];
@@ -372,10 +400,12 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 #pragma unroll
                 for (int c = 0; c < 8; ++c) exp8(&y[c * 4], vsc + c * 8, nm2, prow + ((c ^ (r & 7)) << 4));
             }
+            if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 3);
             tc_fence_before();
             fence_proxy_async();                         // generic-proxy writes of P visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_PFULL + st));
+            if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 4);
         }
         // ---- epilogue: O / l -> fp16, each thread its half of the output columns ----
         if (ok) {
@@ -410,7 +440,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         }
     } else {
         // ================= converter: raw int8 V tile -> fp16, MN-major swizzled =================
-        const int r = threadIdx.x - kConvWarp0 * 32;     // KV row of the tile handled by this thread
+        const int r0 = threadIdx.x - kConvWarp0 * 32;    // first KV row of the tile handled by this thread
         for (int j = 0; j < nt; ++j) {
             const int st = j & 1;
             bool got = mbar_wait_spin_bounded(bar(B_VRFULL + st), (j >> 1) & 1);
@@ -419,6 +449,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
                 break;
             }
+            if (r0 == 0) I8TK_PTRACE(384 + 2 * j);
+#pragma unroll
+            for (int rr = 0; rr < kKT / (32 * kConvWarps); ++rr) {
+            const int r = r0 + rr * (32 * kConvWarps);
             const unsigned char* raw = base + Cfg::OFF_VRAW + st * Cfg::TILE_BYTES + r * D;
             unsigned char* dst = base + Cfg::OFF_V16 + st * Cfg::V16_BYTES + r * 128;
 #pragma unroll
@@ -437,8 +471,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 *reinterpret_cast<uint4*>(drow + ((c0 ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
                 *reinterpret_cast<uint4*>(drow + (((c0 + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
             }
+            }
             fence_proxy_async();
             __syncwarp();
+            if (r0 == 0) I8TK_PTRACE(384 + 2 * j + 1);
             if (lane == 0) {
                 mbar_arrive(bar(B_V16FULL + st));
                 mbar_arrive(bar(B_VREMPTY + st));
@@ -488,6 +524,13 @@ int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* ou
 }  // namespace i8tk
 
 using namespace i8tk;
+
+#ifdef I8TK_PREFILL_TRACE
+extern "C" int i8tk_debug_prefill_trace(long long* host_dst) {
+    I8TK_CUDA(cudaMemcpyFromSymbol(host_dst, g_prefill_trace, sizeof(long long) * kPTraceSlots));
+    return I8TK_OK;
+}
+#endif
 
 extern "C" size_t i8tk_attention_workspace_bytes(void) { return 256; }
 
