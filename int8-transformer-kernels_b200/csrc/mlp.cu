@@ -76,7 +76,6 @@ struct EpiParams {
     const float* scale_b;     // [N] or [1]
     const float* bias;        // [N] or nullptr
     __half* C;                // [M, N] fp16
-    float* row_absmax;        // [M] or nullptr (atomic max, must start at 0)
     float* out_absmax;        // [1] or nullptr (atomic max, must start at 0)
     int a_per_row;
     int b_per_col;
@@ -503,7 +502,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
             if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 4);
 
-            if (ep.row_absmax) atomic_max_pos(ep.row_absmax + m0 + q * 32 + lane, rmax);
             if (ep.out_absmax) {
                 float wmax;
                 asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(wmax) : "f"(rmax));
@@ -561,26 +559,20 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ---------------------------------------------------------------------------
-// Row requantiser: fp16 [M,N] + row absmax -> int8 [M,N] + row scales
-// (kernels/int8_mlp.cu:768-795).  PER_TENSOR: one absmax for the whole tensor,
-// the scale goes to *tensor_scale (kernels/int8_mlp.cu:799-825).
+// Per-tensor requantiser of the legacy output surface: fp16 [M,N] + one absmax for
+// the whole tensor -> int8 [M,N], the scale goes to *tensor_scale
+// (kernels/int8_mlp.cu:799-825).
 // ---------------------------------------------------------------------------
-template <bool PER_TENSOR>
 __global__ void __launch_bounds__(256)
-requant_rows_kernel(const __half* __restrict__ H, const float* __restrict__ absmax,
-                    int8_t* __restrict__ out, float* __restrict__ scales, long long M, int N) {
+requant_tensor_kernel(const __half* __restrict__ H, const float* __restrict__ absmax,
+                      int8_t* __restrict__ out, float* __restrict__ tensor_scale, long long M, int N) {
     const long long total_vec = M * N / 16;
+    const float amax = fmaxf(absmax[0], 1e-8f);
+    const float inv = 127.f / amax;
+    if (blockIdx.x == 0 && threadIdx.x == 0) tensor_scale[0] = amax / 127.f;
     for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total_vec;
          v += (long long)gridDim.x * blockDim.x) {
         const long long e0 = v * 16;
-        const long long row = e0 / N;
-        const float amax = fmaxf(PER_TENSOR ? absmax[0] : absmax[row], 1e-8f);
-        const float inv = 127.f / amax;
-        if (PER_TENSOR) {
-            if (v == 0) scales[0] = amax / 127.f;
-        } else if (e0 % N == 0) {
-            scales[row] = amax / 127.f;
-        }
         const uint4 h0 = *reinterpret_cast<const uint4*>(H + e0);
         const uint4 h1 = *reinterpret_cast<const uint4*>(H + e0 + 8);
         const __half2* hp0 = reinterpret_cast<const __half2*>(&h0);
@@ -754,16 +746,13 @@ int requant_grid(long long vecs) {
 // workspace carve-up
 struct MlpWorkspace {
     uint32_t* status;
-    float* hid_absmax;    // [T]   zeroed together with the one below; used by the routes
-    float* tensor_absmax; // [1]   that keep fp16 intermediates (legacy output scale, A/B route)
+    float* tensor_absmax; // [1]   starts at zero (legacy per-tensor output scale only)
     uint32_t* parts1;     // [T/128][d_ff / BN1][128]     row maxima of GEMM1 per tile; these two
     uint32_t* parts2;     // [T/128][d_model / BN2][128]  are contiguous and start as 0xFF bytes
     float* hid_scale;     // [T]
-    __half* hid_f16;      // [T, d_ff]
     int8_t* hid_i8;       // [T, d_ff]
-    __half* out_f16;      // [T, d_model]
+    __half* out_f16;      // [T, d_model]   (legacy per-tensor output scale only)
     size_t bytes;
-    size_t zero_bytes;    // hid_absmax .. tensor_absmax
     size_t ones_bytes;    // parts1 .. parts2
 };
 
@@ -774,27 +763,21 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
     unsigned char* b = static_cast<unsigned char*>(base);
     const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
     const size_t o_status = take(256);
-    const size_t o_habs = take((size_t)T * 4);
     const size_t o_tabs = take(256);
-    const size_t zero_end = off;
     const size_t o_p1 = take((size_t)T * (d_ff / pick_bn(T, d_ff, b_mn, true)) * 4);
     const size_t o_p2 = take((size_t)T * (d_model / pick_bn(T, d_model, b_mn, true)) * 4);
     const size_t ones_end = off;
     const size_t o_hsc = take((size_t)T * 4);
-    const size_t o_h16 = take((size_t)T * d_ff * 2);
     const size_t o_hi8 = take((size_t)T * d_ff);
     const size_t o_o16 = take((size_t)T * d_model * 2);
     w.bytes = off;
-    w.zero_bytes = zero_end - o_habs;
     w.ones_bytes = ones_end - o_p1;
     if (b) {
         w.status = reinterpret_cast<uint32_t*>(b + o_status);
-        w.hid_absmax = reinterpret_cast<float*>(b + o_habs);
         w.tensor_absmax = reinterpret_cast<float*>(b + o_tabs);
         w.parts1 = reinterpret_cast<uint32_t*>(b + o_p1);
         w.parts2 = reinterpret_cast<uint32_t*>(b + o_p2);
         w.hid_scale = reinterpret_cast<float*>(b + o_hsc);
-        w.hid_f16 = reinterpret_cast<__half*>(b + o_h16);
         w.hid_i8 = reinterpret_cast<int8_t*>(b + o_hi8);
         w.out_f16 = reinterpret_cast<__half*>(b + o_o16);
     }
@@ -863,32 +846,18 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     const int per_token = (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0;
     const int per_channel = (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0;
 
-    // I8TK_MLP_GEMM1_UNFUSED=1 keeps the older route for GEMM1 (fp16 hidden + a requant
-    // pass) for A/B checks.
-    static const bool gemm1_unfused = [] {
-        const char* e = getenv("I8TK_MLP_GEMM1_UNFUSED");
-        return e && atoi(e) != 0;
-    }();
     I8TK_CUDA(cudaMemsetAsync(w.parts1, 0xFF, w.ones_bytes, st));
-    if (gemm1_unfused || !out_row_scales) I8TK_CUDA(cudaMemsetAsync(w.hid_absmax, 0, w.zero_bytes, st));
+    if (!out_row_scales) I8TK_CUDA(cudaMemsetAsync(w.tensor_absmax, 0, sizeof(float), st));
 
     // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token inside the
     // GEMM's epilogue: the fp16 values of a tile wait in shared memory while the row
     // maxima of its row block (12-16 tiles on as many SMs) are exchanged through global
     // memory, and are quantised one tile later, when that exchange has long finished.
-    if (!gemm1_unfused) {
-        EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, nullptr, per_token, per_channel,
+    {
+        EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, per_token, per_channel,
                      w.hid_i8, w.hid_scale, w.parts1};
         rc = launch_gemm_bn<true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
-    } else {
-        EpiParams e1{scale_x, scale_W1, bias1, w.hid_f16, w.hid_absmax, nullptr, per_token, per_channel,
-                     nullptr, nullptr, nullptr};
-        rc = launch_gemm_bn<true, false, false>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
-        if (rc != I8TK_OK) return rc;
-        requant_rows_kernel<false><<<requant_grid((long long)T * d_ff / 16), 256, 0, st>>>(
-            w.hid_f16, w.hid_absmax, w.hid_i8, w.hid_scale, T, d_ff);
-        I8TK_CUDA(cudaGetLastError());
     }
 #ifdef I8TK_GEMM_TRACE
     if (getenv("I8TK_TRACE_GEMM1_ONLY")) return I8TK_OK;
@@ -896,18 +865,18 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     if (out_row_scales) {
         // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way, but
         // at once: with K = d_ff the MMAs of the next tile cover the exchange
-        EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, nullptr, nullptr, 1, per_channel,
+        EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, nullptr, 1, per_channel,
                      out, out_row_scales, w.parts2};
         rc = launch_gemm_bn<false, true, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
         if (rc != I8TK_OK) return rc;
         return I8TK_OK;
     }
     // legacy per-tensor output scale: fp16 out + global absmax, then one requant pass
-    EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, nullptr, w.tensor_absmax, 1, per_channel,
+    EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, w.tensor_absmax, 1, per_channel,
                  nullptr, nullptr, nullptr};
     rc = launch_gemm_bn<false, false, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
     if (rc != I8TK_OK) return rc;
-    requant_rows_kernel<true><<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
+    requant_tensor_kernel<<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
         w.out_f16, w.tensor_absmax, out, out_tensor_scale, T, d_model);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;

@@ -189,12 +189,15 @@ def test_argument_errors():
     assert rc == cabi().ERR_WORKSPACE
 
 
-def test_full_size_config_properties():
-    """M=4096, 768->3072->768 (the benchmark geometry): determinism, row independence
-    (a row's result does not depend on the other rows) and the oracle on sampled rows."""
+@pytest.mark.parametrize("M,dm,dff", [(4096, 768, 3072),     # benchmark geometry: 3 tiles per CTA in GEMM1
+                                      (16384, 1024, 4096),   # 15 tiles per CTA, 16 tiles per row block
+                                      (1024, 256, 8192)])    # 32 tiles per row block: maxima not read ahead
+def test_full_size_config_properties(M, dm, dff):
+    """Large geometries (several tiles per persistent CTA, requantisation deferred by a tile):
+    determinism, row independence (a row's result does not depend on the other rows) and the
+    oracle on sampled rows."""
     torch.manual_seed(0)
     e = ext()
-    M, dm, dff = 4096, 768, 3072
     x = torch.randn(1, M, dm, device="cuda", dtype=torch.float16)
     W1 = torch.randn(dm, dff, device="cuda") * 0.02
     W2 = torch.randn(dff, dm, device="cuda") * 0.02
@@ -206,7 +209,7 @@ def test_full_size_config_properties():
     out, osc = e.int8_mlp_forward_per_channel_bias(xi, w1_t, w2_t, sx.reshape(-1), s1_t, s2_t, b1)
     out_b, osc_b = e.int8_mlp_forward_per_channel_bias(xi, w1_t, w2_t, sx.reshape(-1), s1_t, s2_t, b1)
     assert torch.equal(out, out_b) and torch.equal(osc, osc_b)
-    sub = slice(1024, 1024 + 128)
+    sub = slice(M // 2, M // 2 + 128)
     out_s, osc_s = e.int8_mlp_forward_per_channel_bias(xi[:, sub].contiguous(), w1_t, w2_t,
                                                        sx.reshape(-1)[sub].contiguous(), s1_t, s2_t, b1)
     assert torch.equal(out_s[0], out[0, sub]) and torch.equal(osc_s, osc[sub])

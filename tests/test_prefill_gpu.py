@@ -38,7 +38,8 @@ def _run(args):
 
 
 @pytest.mark.parametrize("B,H,S,D", [(1, 1, 128, 64), (1, 1, 128, 128), (2, 3, 256, 64), (2, 3, 384, 128),
-                                     (2, 8, 512, 64), (2, 8, 512, 128), (1, 4, 1024, 128), (1, 2, 2048, 64)])
+                                     (2, 8, 512, 64), (2, 8, 512, 128), (1, 4, 1024, 128), (1, 2, 2048, 64),
+                                     (1, 2, 640, 64), (1, 1, 896, 128)])
 def test_vs_oracle(B, H, S, D):
     args = _case(B, H, S, D, seed=S + D)
     out = _run(args)
