@@ -174,6 +174,7 @@ PROFILE_CASES = {
     "decode_d128": (8, 8, 128, 8192),      # 134 MB
     "mlp_m4096_768": (4096, 768, 3072),    # fused MLP forward (L2 resident by nature: 30 MB of operands)
     "mlp_m4096_1024": (4096, 1024, 4096),
+    "quantize_f32_64": (3145728, 64),      # rows, cols: 1.0 GB through the per-token quantiser
     "prefill_d64": (2, 8, 4096, 64),       # B, H, S, D: 512 CTAs of 128 query rows
     "prefill_d128": (2, 8, 4096, 128),
 }
@@ -183,6 +184,15 @@ def run_profile_case(name):
     import torch
     pkg = importlib.import_module("int8-transformer-kernels_b200")
     ext = pkg.int8_ext
+    if name.startswith("quantize"):
+        rows, cols = PROFILE_CASES[name]
+        x = torch.randn(rows, cols, device="cuda", dtype=torch.float32)
+        for _ in range(3):
+            qi, sc = ext.quantize_per_token(x)
+        torch.cuda.synchronize()
+        print(f"profile case {name}: [{rows}, {cols}] fp32, bytes per launch {rows * cols * 5 + rows * 4}, "
+              f"checksum {float(sc.sum()):.4f}")
+        return
     if name.startswith("prefill"):
         b, h, sq, d = PROFILE_CASES[name]
         g = torch.Generator(device="cuda").manual_seed(0)

@@ -84,6 +84,52 @@ __device__ __forceinline__ uint32_t quant4(float x0, float x1, float x2, float x
     return w;
 }
 
+// Maxima of R rows, each spread over the G lanes of a group, reduced so that every lane ends
+// up with the complete maximum of ONE row (*rsel): the first log2(R) butterfly steps halve the
+// number of rows a lane carries instead of carrying all R through every step
+// (3 + log2(G/4) shuffles for R = 4 instead of 4 * log2(G)).  Needs R <= G.
+template <int G, int R>
+__device__ __forceinline__ float reduce_rows(const float (&a)[R], int lane_in_group, int* rsel) {
+    static_assert(R == 1 || R == 2 || R == 4, "row batch of 1, 2 or 4");
+    static_assert(R <= G, "more rows than lanes in a group");
+    float c;
+    int sel = 0;
+    int o = G / 2;
+    if constexpr (R == 4) {
+        const bool hi = (lane_in_group & o) != 0;
+        const float r0 = __shfl_xor_sync(0xffffffffu, hi ? a[0] : a[2], o);
+        const float r1 = __shfl_xor_sync(0xffffffffu, hi ? a[1] : a[3], o);
+        const float b0 = fmaxf(hi ? a[2] : a[0], r0);
+        const float b1 = fmaxf(hi ? a[3] : a[1], r1);
+        sel = hi ? 2 : 0;
+        o >>= 1;
+        const bool hi2 = (lane_in_group & o) != 0;
+        const float r2 = __shfl_xor_sync(0xffffffffu, hi2 ? b0 : b1, o);
+        c = fmaxf(hi2 ? b1 : b0, r2);
+        sel += hi2 ? 1 : 0;
+        o >>= 1;
+    } else if constexpr (R == 2) {
+        const bool hi = (lane_in_group & o) != 0;
+        const float r0 = __shfl_xor_sync(0xffffffffu, hi ? a[0] : a[1], o);
+        c = fmaxf(hi ? a[1] : a[0], r0);
+        sel = hi ? 1 : 0;
+        o >>= 1;
+    } else {
+        c = a[0];
+    }
+#pragma unroll
+    for (; o > 0; o >>= 1) c = fmaxf(c, __shfl_xor_sync(0xffffffffu, c, o));
+    *rsel = sel;
+    return c;
+}
+// Lane (within the group) that holds row r's result after reduce_rows.
+template <int G, int R>
+__device__ __forceinline__ int row_owner_lane(int r) {
+    if constexpr (R == 4) return ((r >> 1) ? G / 2 : 0) + ((r & 1) ? G / 4 : 0);
+    if constexpr (R == 2) return r ? G / 2 : 0;
+    return 0;
+}
+
 // Rows of `cols` elements, cols a multiple of Vec16<T>::N.  A row is handled by a
 // group of G lanes (G a power of two <= 32); lane i of the group owns vectors
 // i, i+G, ... (at most NV of them).  Each group keeps R rows in flight.
@@ -96,6 +142,7 @@ quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
     constexpr int GPW = 32 / G;                     // groups per warp
     const int lane_in_group = threadIdx.x % G;
     const int group_in_warp = (threadIdx.x & 31) / G;
+    const int group_lane0 = (threadIdx.x & 31) & ~(G - 1);
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
 
@@ -103,16 +150,18 @@ quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
     // name all 32 lanes); rows past the end are predicated off.
     for (long long w0 = warp * GPW * R; w0 < rows; w0 += nwarps * GPW * R) {
         const long long r0 = w0 + (long long)group_in_warp * R;
+        const int nrows = (int)(rows - r0 < R ? (rows - r0 > 0 ? rows - r0 : 0) : R);   // rows of this group that exist
+        const T* xg = x + r0 * cols + lane_in_group * N;
+        int8_t* qg = q + r0 * cols + lane_in_group * N;
         uint4 raw[R][NV];
         float amax[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            const long long row = r0 + r;
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 const int vi = lane_in_group + j * G;
-                raw[r][j] = (row < rows && vi < nvec) ? Vec16<T>::load(x + row * cols + (long long)vi * N)
-                                                      : make_uint4(0u, 0u, 0u, 0u);
+                raw[r][j] = (r < nrows && vi < nvec) ? Vec16<T>::load(xg + r * cols + j * (G * N))
+                                                     : make_uint4(0u, 0u, 0u, 0u);
             }
         }
 #pragma unroll
@@ -120,22 +169,41 @@ quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
             amax[r] = 0.f;
 #pragma unroll
             for (int j = 0; j < NV; ++j) amax[r] = fmaxf(amax[r], Vec16<T>::absmax(raw[r][j]));
+        }
+        float scale_r[R], rcp_r[R];
+        if constexpr (R <= G) {
+            // one division per lane serves R rows: each lane finishes one row's maximum, turns it
+            // into scale and reciprocal, and the group reads them back by shuffle
+            int rsel;
+            const float am = reduce_rows<G, R>(amax, lane_in_group, &rsel);
+            const float scale = __fdiv_rn(fmaxf(am, 1e-8f), 127.0f);
+            const float rcp = __frcp_rn(scale);
+            if (lane_in_group == row_owner_lane<G, R>(rsel) && rsel < nrows) scales[r0 + rsel] = scale;
 #pragma unroll
-            for (int o = G / 2; o > 0; o >>= 1)
-                amax[r] = fmaxf(amax[r], __shfl_xor_sync(0xffffffffu, amax[r], o));
+            for (int r = 0; r < R; ++r) {
+                scale_r[r] = __shfl_sync(0xffffffffu, scale, group_lane0 + row_owner_lane<G, R>(r));
+                rcp_r[r] = __shfl_sync(0xffffffffu, rcp, group_lane0 + row_owner_lane<G, R>(r));
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+#pragma unroll
+                for (int o = G / 2; o > 0; o >>= 1)
+                    amax[r] = fmaxf(amax[r], __shfl_xor_sync(0xffffffffu, amax[r], o));
+                scale_r[r] = __fdiv_rn(fmaxf(amax[r], 1e-8f), 127.0f);
+                rcp_r[r] = __frcp_rn(scale_r[r]);
+                if (lane_in_group == 0 && r < nrows) scales[r0 + r] = scale_r[r];
+            }
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            const long long row = r0 + r;
-            if (row >= rows) continue;
-            const float scale = __fdiv_rn(fmaxf(amax[r], 1e-8f), 127.0f);
-            const float rcp = __frcp_rn(scale);
-            if (lane_in_group == 0) scales[row] = scale;
+            if (r >= nrows) continue;
+            const float scale = scale_r[r], rcp = rcp_r[r];
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 const int vi = lane_in_group + j * G;
                 if (vi >= nvec) continue;
-                int8_t* dst = q + row * cols + (long long)vi * N;
+                int8_t* dst = qg + r * cols + j * (G * N);
                 float v[N];
                 Vec16<T>::to_float(raw[r][j], v);
                 if constexpr (N == 4) {
