@@ -134,6 +134,14 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     return r;
 }
 
+// Programmatic dependent launch: a kernel launched with launch_after() may start while the
+// kernel before it in the stream is still running; it must call pdl_wait() before it touches
+// anything that kernel writes (the wait returns once that grid has completed and its writes
+// are visible; it returns at once in a kernel launched the ordinary way).  The earlier kernel
+// calls pdl_launch_dependents() to let the later one be scheduled as SMs become free.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Packed fp32x2 arithmetic (one instruction for two lanes of a register pair).
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 pack2(float a, float b) {
@@ -158,5 +166,25 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
 }
 
 #endif  // __CUDACC__
+
+#ifdef __CUDACC__
+// Launch `kernel` so that it may overlap the tail of the previous kernel in `st`
+// (programmatic stream serialisation); see pdl_wait().
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 }  // namespace i8tk

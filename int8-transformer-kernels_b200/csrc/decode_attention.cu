@@ -171,6 +171,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();                    // the merge kernel may be scheduled as SMs drain
     const long long f0 = (long long)blockIdx.x * plan.tpc;
     if (f0 >= plan.total) return;
     const int ntl = (int)min((long long)plan.tpc, plan.total - f0);   // tiles of this CTA
@@ -364,6 +365,7 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, Decode
                       __half* __restrict__ out, float* __restrict__ row_out) {
     constexpr int ROW = D + 4;
     constexpr int DPL = D / 32;
+    pdl_wait();                                 // rows of the scan launched just before this kernel
     const int bh = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (bh >= BH) return;
     const int lane = threadIdx.x & 31;
@@ -463,6 +465,7 @@ decode_exchange_kernel(const float* __restrict__ rows, int BH, DecodePlan plan, 
     const int lane = threadIdx.x & 31;
     const int bh = blockIdx.x * 4 + warp;
     const bool active = bh < BH;
+    pdl_wait();                                 // rows of the scan launched just before this kernel
 
     // ---- 1. local merge ------------------------------------------------------
     float gm = -INFINITY, L = 0.f;
@@ -671,8 +674,9 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
     else
         rc = launch_partial<D, false>(Q, K, V, sQ, sK, sV, rows, S, p, status, stream);
     if (rc != I8TK_OK) return rc;
-    decode_combine_kernel<D, true><<<(BH + 3) / 4, 128, 0, stream>>>(rows, BH, 0, p, out, part);
-    I8TK_CUDA(cudaGetLastError());
+    // the merge may be scheduled while the scan drains: it waits (pdl_wait) for the scan's rows
+    I8TK_CUDA(launch_after(decode_combine_kernel<D, true>, dim3((BH + 3) / 4), dim3(128), 0, stream,
+                           (const float*)rows, BH, 0, p, out, part));
     return I8TK_OK;
 }
 
@@ -824,13 +828,13 @@ extern "C" int i8tk_decode_attention_seq_sharded(const int8_t* Q, const int8_t* 
     const int grid = (BH + 3) / 4;
     float* const* pp = static_cast<float* const*>(peer_parts);
     uint32_t* const* pf = static_cast<uint32_t* const*>(peer_flags);
+    const int empty = S_local == 0 ? 1 : 0;
     if (head_dim == 64)
-        decode_exchange_kernel<64><<<grid, 128, 0, st>>>(rows, BH, p, S_local == 0, pp, pf, rank, world,
-                                                         epoch, static_cast<__half*>(out_f16), status);
+        I8TK_CUDA(launch_after(decode_exchange_kernel<64>, dim3(grid), dim3(128), 0, st, (const float*)rows, BH, p,
+                               empty, pp, pf, rank, world, epoch, static_cast<__half*>(out_f16), status));
     else
-        decode_exchange_kernel<128><<<grid, 128, 0, st>>>(rows, BH, p, S_local == 0, pp, pf, rank, world,
-                                                          epoch, static_cast<__half*>(out_f16), status);
-    I8TK_CUDA(cudaGetLastError());
+        I8TK_CUDA(launch_after(decode_exchange_kernel<128>, dim3(grid), dim3(128), 0, st, (const float*)rows, BH, p,
+                               empty, pp, pf, rank, world, epoch, static_cast<__half*>(out_f16), status));
     return I8TK_OK;
 }
 

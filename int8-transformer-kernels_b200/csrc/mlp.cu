@@ -85,6 +85,7 @@ struct EpiParams {
     // [M / 128][N / BN][128] row maxima, one word per (row, tile), which every bit set
     // marks as not yet written (the caller fills the array with 0xFF bytes)
     uint32_t* row_parts;
+    int a_from_prev;          // A is written by the kernel launched just before this one
 };
 
 // GELU, tanh form: 0.5 x (1 + tanh(y)), y = kC (x + kA x^3)
@@ -263,12 +264,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
     if (threadIdx.x == 0) I8TK_TRACE(1);
+    pdl_launch_dependents();                    // the next GEMM may set itself up as SMs become free
 
     if (warp == 0) {
         // ================= TMA producer =================
         if (elect_one()) {
             int it = 0;
             bool ok = true;
+            if (ep.a_from_prev) pdl_wait();              // A comes from the kernel before this one
             I8TK_TRACE(2);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile / tiles_n) * BM;
@@ -362,6 +365,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             pf_sa = ld_nc_now(ep.a_per_row ? ep.scale_a + pm0 + q * 32 + lane : ep.scale_a);
         };
+        pdl_wait();     // row scales and the row-maxima flags come from the kernels before this one
         if ((int)blockIdx.x < num_tiles) prefetch(blockIdx.x);
 
         // Requantisation of a tile whose fp16 values sit in this warp's stash: wait for the
@@ -593,6 +597,16 @@ requant_tensor_kernel(const __half* __restrict__ H, const float* __restrict__ ab
     }
 }
 
+// Workspace presets of one forward: `words16` 16-byte words of all ones, one float of zero.
+__global__ void __launch_bounds__(256)
+preset_kernel(uint4* __restrict__ ones, size_t words16, float* __restrict__ zero) {
+    pdl_launch_dependents();
+    const uint4 v = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words16; i += (size_t)gridDim.x * blockDim.x)
+        ones[i] = v;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *zero = 0.f;
+}
+
 // int8 [R][C] -> [C][R]; 64x64 tiles, 4-byte global accesses on both sides.
 __global__ void __launch_bounds__(256)
 transpose_i8_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int R, int C) {
@@ -722,8 +736,8 @@ int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep
     const int grid = gemm_grid(M, N, BN, FUSED);
     I8TK_REQUIRE(!FUSED || N / BN <= sm_count_mlp(), I8TK_ERR_UNSUPPORTED,
                  "row of %d tiles does not fit one round of CTAs", N / BN);
-    gemm_i8_kernel<BN, GELU, FUSED, DEFER><<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status);
-    I8TK_CUDA(cudaGetLastError());
+    I8TK_CUDA(launch_after(gemm_i8_kernel<BN, GELU, FUSED, DEFER>, dim3(grid), dim3(kGemmThreads), Cfg::SMEM_BYTES, st,
+                           tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status));
     return I8TK_OK;
 }
 
@@ -846,8 +860,16 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     const int per_token = (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0;
     const int per_channel = (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0;
 
-    I8TK_CUDA(cudaMemsetAsync(w.parts1, 0xFF, w.ones_bytes, st));
-    if (!out_row_scales) I8TK_CUDA(cudaMemsetAsync(w.tensor_absmax, 0, sizeof(float), st));
+    // presets: row-maxima flags all ones, the tensor-wide maximum zero.  A kernel rather than a
+    // memset so that GEMM1 can be launched behind it programmatically and set itself up meanwhile.
+    {
+        const size_t words = w.ones_bytes / 16;
+        int blocks = (int)((words + 255) / 256);
+        if (blocks > 296) blocks = 296;
+        if (blocks < 1) blocks = 1;
+        preset_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<uint4*>(w.parts1), words, w.tensor_absmax);
+        I8TK_CUDA(cudaGetLastError());
+    }
 
     // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token inside the
     // GEMM's epilogue: the fp16 values of a tile wait in shared memory while the row
@@ -855,7 +877,7 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     // memory, and are quantised one tile later, when that exchange has long finished.
     {
         EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, per_token, per_channel,
-                     w.hid_i8, w.hid_scale, w.parts1};
+                     w.hid_i8, w.hid_scale, w.parts1, 0};
         rc = launch_gemm_bn<true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
     }
@@ -866,14 +888,14 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
         // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way, but
         // at once: with K = d_ff the MMAs of the next tile cover the exchange
         EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, nullptr, 1, per_channel,
-                     out, out_row_scales, w.parts2};
+                     out, out_row_scales, w.parts2, 1};
         rc = launch_gemm_bn<false, true, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
         if (rc != I8TK_OK) return rc;
         return I8TK_OK;
     }
     // legacy per-tensor output scale: fp16 out + global absmax, then one requant pass
     EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, w.tensor_absmax, 1, per_channel,
-                 nullptr, nullptr, nullptr};
+                 nullptr, nullptr, nullptr, 1};
     rc = launch_gemm_bn<false, false, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
     if (rc != I8TK_OK) return rc;
     requant_tensor_kernel<<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
