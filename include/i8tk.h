@@ -193,10 +193,10 @@ int i8tk_decode_plan(int BH, int S, int head_dim, int* nctas, int* tiles_per_cta
  *   sQ, sK, sV  fp32 [batch*heads*seq_len]
  *   out      [batch, heads, seq_len, head_dim] fp16
  * score[i][j] = (q_i.k_j) * sQ_i * sK_j / sqrt(D); P*sV and V go through fp16
- * into an fp32 accumulator, as in the reference.  head_dim 64 or 128 and
- * seq_len a multiple of 128 (the reference's tensor-core path needs 64; its
- * scalar fallback for other shapes is not reproduced): anything else returns
- * I8TK_ERR_UNSUPPORTED.  workspace: i8tk_attention_workspace_bytes() bytes,
+ * into an fp32 accumulator, as in the reference.  Any seq_len >= 1 (a partial
+ * last tile of 128 positions is masked; the reference takes a scalar fallback
+ * when seq_len is not a multiple of 64).  head_dim 64 or 128: anything else
+ * returns I8TK_ERR_UNSUPPORTED.  workspace: i8tk_attention_workspace_bytes() bytes,
  * 256-byte aligned (holds the status word).
  * ---------------------------------------------------------------------- */
 size_t i8tk_attention_workspace_bytes(void);

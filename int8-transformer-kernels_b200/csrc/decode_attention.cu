@@ -197,6 +197,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
     if (warp == kConsumers) {
         // ---- producer: one lane walks the tile list and keeps the ring full ----
         if (lane != 0) return;
+        const uint64_t stream_once = l2_policy_evict_first();   // K, V and their scales are read once
         int p_bh = bh0, p_tb = tb0;
         for (int i = 0; i < ntl; ++i) {
             const int st = i % STAGES;
@@ -215,13 +216,13 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
             if constexpr (SCALES_BULK) {
                 const uint32_t sc_bytes = (uint32_t)nrow * 4;       // multiple of 16: S % 4 == 0
                 mbar_expect_tx(bar, 2 * kv_bytes + 2 * sc_bytes);
-                bulk_g2s(dst + 2 * T::TILE_BYTES, sK + row, sc_bytes, bar);
-                bulk_g2s(dst + 2 * T::TILE_BYTES + T::SCALE_BYTES, sV + row, sc_bytes, bar);
+                bulk_g2s_hint(dst + 2 * T::TILE_BYTES, sK + row, sc_bytes, bar, stream_once);
+                bulk_g2s_hint(dst + 2 * T::TILE_BYTES + T::SCALE_BYTES, sV + row, sc_bytes, bar, stream_once);
             } else {
                 mbar_expect_tx(bar, 2 * kv_bytes);
             }
-            bulk_g2s(dst, K + row * D, kv_bytes, bar);
-            bulk_g2s(dst + T::TILE_BYTES, V + row * D, kv_bytes, bar);
+            bulk_g2s_hint(dst, K + row * D, kv_bytes, bar, stream_once);
+            bulk_g2s_hint(dst + T::TILE_BYTES, V + row * D, kv_bytes, bar, stream_once);
             if (++p_tb == tpb) { p_tb = 0; ++p_bh; }
         }
         return;

@@ -29,7 +29,8 @@
 // * Every mbarrier wait is bounded; on expiry a status word is set and all
 //   roles fall through to the common exit, which frees tensor memory.
 //
-// Supported: head_dim 64 or 128, seq_len a multiple of 128.
+// Supported: head_dim 64 or 128, any seq_len (a partial last tile is masked: the operand tiles
+// then hold rows of the next head or TMA's zero fill, whose scores are set to -inf).
 #include "tcgen05.cuh"
 
 #include <cmath>
@@ -134,7 +135,9 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     const int lane = threadIdx.x & 31;
     const int bh = blockIdx.y;
     const int q0 = blockIdx.x * kQT;
-    const int nt = S / kKT;                                 // KV tiles
+    const int nt = (S + kKT - 1) / kKT;                     // KV tiles; the last one may be partial
+    const int tail_valid = S - (nt - 1) * kKT;              // KV positions of the last tile (1..128)
+    const long long total_rows = (long long)gridDim.y * S;  // rows of the [BH*S] scale arrays
     const int row_base = bh * S;                            // first row of this (b,h) in the [BH*S, D] views
 
     if (threadIdx.x == 0) {
@@ -238,7 +241,8 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         const int r = q * 32 + lane;                     // row inside the tile
         float* wsc = reinterpret_cast<float*>(base + Cfg::OFF_SCALES) + sw * 256;   // [tile & 1][sK[64] | sV[64]] of these columns
         float* xch = reinterpret_cast<float*>(base + Cfg::OFF_XCH);                 // [2][half][row]
-        const float qscale = sQ[(size_t)row_base + q0 + r] * score_scale_log2;     // > 0
+        // query rows past the end of a ragged sequence are computed on clamped operands and never stored
+        const float qscale = sQ[min((long long)row_base + q0 + r, total_rows - 1)] * score_scale_log2;     // > 0
         const f32x2 qs2 = pack2(qscale, qscale);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         unsigned char* prow0 = base + Cfg::OFF_P + half * Cfg::SLAB_BYTES + r * 128;  // this row in this half's 64-wide K block
@@ -252,11 +256,13 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         // this warp's per-position scales, fetched ahead of the tile that uses them
         float pk0, pk1, pv0, pv1;
         auto prefetch = [&](int j) {
-            const size_t o = (size_t)row_base + j * kKT + half * 64 + lane;
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk0) : "l"(sK + o));
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk1) : "l"(sK + o + 32));
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pv0) : "l"(sV + o));
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pv1) : "l"(sV + o + 32));
+            // positions past the end of the arrays (ragged last tile of the last head) read the last element
+            const long long o0 = (long long)row_base + j * kKT + half * 64 + lane;
+            const size_t oa = (size_t)min(o0, total_rows - 1), ob = (size_t)min(o0 + 32, total_rows - 1);
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk0) : "l"(sK + oa));
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk1) : "l"(sK + ob));
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pv0) : "l"(sV + oa));
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pv1) : "l"(sV + ob));
         };
         auto commit_scales = [&](int j) {                // prefetched registers -> this warp's block for tile j
             float* w = wsc + (j & 1) * 128;
@@ -280,6 +286,19 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             y4[3] = mul2(t67, pack2(kb.z, kb.w));
             const float2 a = unpack2(y4[0]), b = unpack2(y4[1]), c = unpack2(y4[2]), d = unpack2(y4[3]);
             mx = max3(max3(mx, a.x, a.y), max3(b.x, b.y, c.x), fmaxf(c.y, fmaxf(d.x, d.y)));
+        };
+        // the same for a partial last tile: columns from nv on (nv may be <= 0) do not exist
+        auto convert8_tail = [&](const uint32_t* sr8, const float* k8, f32x2* y4, float& mx, int nv) {
+            float dummy = -INFINITY;
+            convert8(sr8, k8, y4, dummy);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float2 v = unpack2(y4[e]);
+                if (2 * e >= nv) v.x = -INFINITY;
+                if (2 * e + 1 >= nv) v.y = -INFINITY;
+                y4[e] = pack2(v.x, v.y);
+                mx = fmaxf(mx, fmaxf(v.x, v.y));
+            }
         };
         // p = 2^(y*qscale - m_ref) for 8 columns; P*sV as one 16-byte chunk of fp16
         auto exp8 = [&](const f32x2* y4, const float* v8, f32x2 nm2, unsigned char* dst) {
@@ -314,8 +333,13 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 for (int cc = 0; cc < 4; ++cc) {
                     tmem_ld_wait(sr[cc & 1]);
                     if (cc < 3) tmem_ld16(s_addr + (cc + 1) * 16, sr[(cc + 1) & 1]);
-                    convert8(&sr[cc & 1][0], wsc + cc * 16, &y[cc * 8], mx);
-                    convert8(&sr[cc & 1][8], wsc + cc * 16 + 8, &y[cc * 8 + 4], mx);
+                    if (nt == 1 && tail_valid < kKT) {
+                        convert8_tail(&sr[cc & 1][0], wsc + cc * 16, &y[cc * 8], mx, tail_valid - half * 64 - cc * 16);
+                        convert8_tail(&sr[cc & 1][8], wsc + cc * 16 + 8, &y[cc * 8 + 4], mx, tail_valid - half * 64 - cc * 16 - 8);
+                    } else {
+                        convert8(&sr[cc & 1][0], wsc + cc * 16, &y[cc * 8], mx);
+                        convert8(&sr[cc & 1][8], wsc + cc * 16 + 8, &y[cc * 8 + 4], mx);
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -390,7 +414,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                     for (int h = 0; h < 2; ++h) {
                         const int c = cc * 2 + h;        // 16-byte chunk of P / 8 columns
                         exp8(&y[c * 4], vsc + c * 8, nm2, prow + ((c ^ (r & 7)) << 4));
-                        convert8(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx);
+                        if (j + 2 == nt && tail_valid < kKT)
+                            convert8_tail(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx, tail_valid - half * 64 - c * 8);
+                        else
+                            convert8(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx);
                     }
                 }
                 tc_fence_before();
@@ -430,10 +457,12 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 #pragma unroll
                 for (int i = 0; i < 32; i += 2)
                     hp[i >> 1] = pack_h2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                if (q0 + r < S) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    *reinterpret_cast<uint4*>(orow + cc * 32 + k * 8) =
-                        make_uint4(hp[4 * k], hp[4 * k + 1], hp[4 * k + 2], hp[4 * k + 3]);
+                    for (int k = 0; k < 4; ++k)
+                        *reinterpret_cast<uint4*>(orow + cc * 32 + k * 8) =
+                            make_uint4(hp[4 * k], hp[4 * k + 1], hp[4 * k + 2], hp[4 * k + 3]);
+                }
             }
         } else if (lane == 0) {
             atomicExch(status, kDeviceTimeoutMagic);
@@ -513,7 +542,7 @@ int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* ou
         I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
     }
     const float score_scale_log2 = 1.4426950408889634f / sqrtf((float)D);
-    dim3 grid(S / kQT, BH);
+    dim3 grid((S + kQT - 1) / kQT, BH);
     prefill_attention_kernel<D><<<grid, kPrefillThreads, Cfg::SMEM_BYTES, st>>>(tmQ, tmK, tmV, sQ, sK, sV, out, S,
                                                                               score_scale_log2, status);
     I8TK_CUDA(cudaGetLastError());
@@ -542,8 +571,6 @@ extern "C" int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const in
     I8TK_REQUIRE(batch > 0 && heads > 0 && seq_len > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
     I8TK_REQUIRE(head_dim == 64 || head_dim == 128, I8TK_ERR_UNSUPPORTED,
                  "prefill attention supports head_dim 64 or 128 (got %d)", head_dim);
-    I8TK_REQUIRE(seq_len % 128 == 0, I8TK_ERR_UNSUPPORTED,
-                 "prefill attention needs seq_len to be a multiple of 128 (got %d)", seq_len);
     I8TK_REQUIRE((long long)batch * heads <= 65535, I8TK_ERR_UNSUPPORTED, "batch*heads must be <= 65535");
     I8TK_REQUIRE((long long)batch * heads * seq_len < (1ll << 31), I8TK_ERR_UNSUPPORTED, "too many rows");
     I8TK_REQUIRE(aligned_to(Q, 16) && aligned_to(K, 16) && aligned_to(V, 16) && aligned_to(out_f16, 16),

@@ -58,21 +58,20 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 }
 
 // Four codes with the division amortised over the row, bit-identical to quant1.
-// `rcp` is the correctly rounded 1/scale; one Newton step (two FMAs) gives the quotient to
-// within an ulp, which can only change the rounded code when the quotient sits on a rounding
-// tie -- there (|frac - 0.5| < 1e-4, about 0.02 % of elements; an ulp of a quotient <= 128 is
-// below 8e-6) the IEEE division is done after all.  Rounding to nearest even is the addition
-// of 1.5 * 2^23, which leaves the code in the low byte of the sum; |x / scale| <= 127 by
-// construction of the scale, so no clamp is needed.  Packed fp32x2 arithmetic throughout: no
-// conversion or rounding instruction (those run at a quarter of the FMA rate).
+// `rcp` is the correctly rounded 1/scale, so x * rcp is within 2^-23 (relative) of the exact
+// quotient, i.e. within 1.6e-5 of it for |quotient| <= 128, and the IEEE quotient is within
+// 0.8e-5: the two can only round to different codes when x * rcp lies within 2.4e-5 of a
+// rounding tie.  Quotients within 1e-4 of a tie (about 0.02 % of elements) are therefore redone
+// with the IEEE division and the rest need nothing more than the multiply.  Rounding to nearest
+// even is the addition of 1.5 * 2^23, which leaves the code in the low byte of the sum;
+// |x / scale| <= 127 by construction of the scale, so no clamp is needed.  Packed fp32x2
+// arithmetic throughout: no conversion or rounding instruction (those run at a quarter of the
+// FMA rate).
 __device__ __forceinline__ uint32_t quant4(float x0, float x1, float x2, float x3, float scale, float rcp) {
-    const f32x2 rcp2 = pack2(rcp, rcp), nscale2 = pack2(-scale, -scale);
+    const f32x2 rcp2 = pack2(rcp, rcp);
     const f32x2 magic2 = pack2(12582912.f, 12582912.f), nmagic2 = pack2(-12582912.f, -12582912.f);
     const f32x2 mone2 = pack2(-1.f, -1.f);
-    const f32x2 xa = pack2(x0, x1), xb = pack2(x2, x3);
-    const f32x2 qa0 = mul2(xa, rcp2), qb0 = mul2(xb, rcp2);
-    const f32x2 qa = fma2(fma2(qa0, nscale2, xa), rcp2, qa0);
-    const f32x2 qb = fma2(fma2(qb0, nscale2, xb), rcp2, qb0);
+    const f32x2 qa = mul2(pack2(x0, x1), rcp2), qb = mul2(pack2(x2, x3), rcp2);
     const f32x2 ra = add2(qa, magic2), rb = add2(qb, magic2);          // low byte = code
     const float2 da = unpack2(fma2(add2(ra, nmagic2), mone2, qa));     // q - rne(q)
     const float2 db = unpack2(fma2(add2(rb, nmagic2), mone2, qb));
