@@ -342,18 +342,20 @@ def main():
             # events must exist before their handles are read
             a.record(); b_.record()
         torch.cuda.synchronize()
+        # back-to-back calls, as in the timed region above (a synchronise per call would time a
+        # kernel that starts on an idle, clock-ramping GPU); one pair of events per call
         t_until = time.perf_counter() + 1.0
         total, count = 0.0, 0
         while count < n_prof or time.perf_counter() < t_until:
-            a, b_ = ev[count % n_prof]
-            lib.i8tk_decode_set_probe_events(a.cuda_event, b_.cuda_event)
-            cabi.check(lib.i8tk_decode_attention_forward(
-                Qi.data_ptr(), Ki.data_ptr(), Vi.data_ptr(), out.data_ptr(), sQ.data_ptr(),
-                sK.data_ptr(), sV.data_ptr(), BH, S, D, ws.data_ptr(), wbytes, stream))
+            for a, b_ in ev:
+                lib.i8tk_decode_set_probe_events(a.cuda_event, b_.cuda_event)
+                cabi.check(lib.i8tk_decode_attention_forward(
+                    Qi.data_ptr(), Ki.data_ptr(), Vi.data_ptr(), out.data_ptr(), sQ.data_ptr(),
+                    sK.data_ptr(), sV.data_ptr(), BH, S, D, ws.data_ptr(), wbytes, stream))
             lib.i8tk_decode_set_probe_events(None, None)
             torch.cuda.synchronize()
-            total += a.elapsed_time(b_) / 1e3
-            count += 1
+            total += sum(a.elapsed_time(b_) for a, b_ in ev) / 1e3
+            count += len(ev)
         kernel_s = total / count
     clocks = sampler.stop()
 
