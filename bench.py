@@ -484,7 +484,41 @@ def sweep(torch, ext, cabi, world, rank, barrier, dist):
     elif rank == 0:
         res.extend(quantiser_and_prefill_sweep(torch, ext))
         res.extend(mlp_sweep(torch, ext, cabi))
+        res.extend(block_sweep(torch))
     return res
+
+
+def block_sweep(torch):
+    """End-to-end pre-LN block (LayerNorm and projections fp16 in both paths; attention core and
+    MLP either fp16 -- torch SDPA and fp16 GEMMs -- or the INT8 ops), the geometry of the
+    reference's block bench (bench/bench_block.py:209-215): prefill B8 H16 Dh64 d_ff 4096,
+    decode B128 over a prefilled cache.  cos = INT8 block output against the fp16 block."""
+    import torch.nn.functional as F
+    pkg = importlib.import_module("int8-transformer-kernels_b200")
+    blk = pkg.block.Int8Block(1024, 16, 4096)
+    cos = lambda a, b: F.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0).item()
+    out = []
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for S in (512, 2048):
+        x = torch.randn(8, S, 1024, device="cuda", dtype=torch.float16, generator=g)
+        c = cos(blk.forward_prefill(x, True), blk.forward_prefill(x, False))
+        t8 = timed_steps(torch, lambda: blk.forward_prefill(x, True), 10, 3) / 10
+        t16 = timed_steps(torch, lambda: blk.forward_prefill(x, False), 10, 3) / 10
+        out.append({"workload": f"block prefill B8 H16 Dh64 d_ff4096 S{S}", "int8_ms": t8 * 1e3, "fp16_ms": t16 * 1e3,
+                    "speedup_vs_fp16": t16 / t8, "cos_vs_fp16": c})
+    for Skv in (8192, 32768):
+        x = torch.randn(128, 1, 1024, device="cuda", dtype=torch.float16, generator=g)
+        K = torch.randn(128, 16, Skv, 64, device="cuda", dtype=torch.float16, generator=g)
+        V = torch.randn(128, 16, Skv, 64, device="cuda", dtype=torch.float16, generator=g)
+        kv8 = blk.quantize_kv(K, V)
+        c = cos(blk.forward_decode(x, kv8, True), blk.forward_decode(x, (K, V), False))
+        t8 = timed_steps(torch, lambda: blk.forward_decode(x, kv8, True), 10, 3) / 10
+        t16 = timed_steps(torch, lambda: blk.forward_decode(x, (K, V), False), 10, 3) / 10
+        out.append({"workload": f"block decode B128 H16 Dh64 d_ff4096 Skv{Skv}", "int8_ms": t8 * 1e3,
+                    "fp16_ms": t16 * 1e3, "speedup_vs_fp16": t16 / t8, "cos_vs_fp16": c})
+        del K, V, kv8
+        torch.cuda.empty_cache()
+    return out
 
 
 def quantiser_and_prefill_sweep(torch, ext):

@@ -69,6 +69,30 @@ int i8tk_quantize_per_token_f32(const float* x, int8_t* q, float* scales,
 int i8tk_quantize_per_token_f16(const void* x_f16, int8_t* q, float* scales,
                                 int64_t rows, int cols, i8tk_stream_t stream);
 
+/* Producer-side quantisation: the steps either side of the INT8 path that the reference
+ * leaves to eager torch code (several elementwise kernels per tensor,
+ * bench/bench_block.py:59-63,93-94,107-151) and names as its largest remaining cost
+ * (OPTIMIZATION.md:241-246).  No counterpart among the reference's launchers.
+ *
+ * i8tk_layernorm_quantize_f16: y = LayerNorm(x) without affine parameters over the last
+ * dimension (biased variance, `eps` inside the square root, as torch's F.layer_norm), rounded
+ * to fp16 as torch would store it, then quantised per token exactly like
+ * i8tk_quantize_per_token_f16 would quantise that fp16 tensor.
+ *   x [rows, d_model] fp16, 16-byte aligned; q [rows, d_model] int8; scales [rows] fp32.
+ *   d_model a multiple of 8, at most 4096.
+ *
+ * i8tk_kv_append_quantize_f16: the new token's K and V rows, k_new / v_new [BH, head_dim]
+ * fp16, quantised per token and written into the INT8 cache K / V [BH, S_cap, head_dim] at
+ * position pos_per_row[bh] (device int32[BH]) or, when pos_per_row is NULL, at `pos` for every
+ * row; their scales go to sK / sV [BH, S_cap].  Rows whose position is outside [0, S_cap) are
+ * skipped.  head_dim a multiple of 32, at most 256. */
+int i8tk_layernorm_quantize_f16(const void* x_f16, int8_t* q, float* scales,
+                                int64_t rows, int d_model, float eps, i8tk_stream_t stream);
+int i8tk_kv_append_quantize_f16(const void* k_new_f16, const void* v_new_f16,
+                                int8_t* K, int8_t* V, float* sK, float* sV,
+                                const int32_t* pos_per_row, int pos,
+                                int BH, int S_cap, int head_dim, i8tk_stream_t stream);
+
 /* Per-tensor FP16 -> INT8 with a dynamically computed scale, and the inverse.
  * Replaces quantize_fp16_to_int8 / dequantize_int8_to_fp16
  * (kernels/int8_common.cuh:54-59, kernels/quant_utils.cu:57-77).

@@ -8,6 +8,7 @@ with ``importlib.import_module("int8-transformer-kernels_b200")``.
   ``int8_ext``   the compiled binding: same op names / signatures as the reference
   ``cabi``       ctypes view of the raw C ABI (status codes, workspace queries)
   ``sharding``   multi-GPU helpers: (batch, head) sharding and KV-sequence sharding
+  ``block``      a pre-LN transformer block around the ops (the caller either side of the path)
 
 There is no CPU or eager fallback: importing ``int8_ext`` raises if the native
 libraries have not been built (``python build.py`` in this directory).
@@ -40,7 +41,7 @@ def __getattr__(name):
         mod = _load_ext()
         globals()["int8_ext"] = mod
         return mod
-    if name in ("cabi", "sharding"):
+    if name in ("cabi", "sharding", "block"):
         mod = importlib.import_module("." + name, __name__)
         globals()[name] = mod
         return mod

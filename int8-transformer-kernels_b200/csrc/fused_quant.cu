@@ -1,0 +1,186 @@
+// Producer-side quantisation: the two steps either side of the INT8 path that the reference
+// leaves to eager torch code and names as its largest remaining cost
+// (OPTIMIZATION.md:241-246, bench/bench_block.py:107-151).
+//
+// * layernorm_quantize: LayerNorm (no affine, eps 1e-5, as F.layer_norm(x, (d,)) in
+//   bench/bench_block.py:93-94) of an fp16 row, rounded to fp16 as torch stores it, then the
+//   per-token quantiser's arithmetic (tests/test_int8.py:47-63) on that value -- one pass over
+//   the row instead of LayerNorm + abs/amax/div/round/clamp/cast kernels.
+// * kv_append_quantize: the new token's K and V rows ([B*H, D], fp16) quantised per token and
+//   written straight into the INT8 cache at their position, with their scales -- quantise on
+//   write, no intermediate tensors.
+#include "common.cuh"
+
+namespace i8tk {
+namespace {
+
+__device__ __forceinline__ int quant_exact(float x, float scale) {
+    // true division + round-half-even + clamp, exactly as torch does on fp32
+    const float r = rintf(__fdiv_rn(x, scale));
+    return (int)fminf(fmaxf(r, -128.f), 127.f);
+}
+
+constexpr int kLnThreads = 128;
+constexpr int kLnMaxVec = 4;          // 16-byte vectors per thread: d_model <= 128 * 4 * 8 = 4096
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5;
+    __syncthreads();                                  // red[] free again
+    if ((threadIdx.x & 31) == 0) red[w] = v;
+    __syncthreads();
+    return red[0] + red[1] + red[2] + red[3];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int w = threadIdx.x >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[w] = v;
+    __syncthreads();
+    return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+}
+
+// One CTA per row; the row lives in registers between the three reductions.
+__global__ void __launch_bounds__(kLnThreads)
+layernorm_quantize_kernel(const __half* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scales,
+                          int d, float eps) {
+    __shared__ float red[4];
+    const long long row = blockIdx.x;
+    const int nvec = d / 8;
+    const __half* xr = x + row * d;
+    float v[kLnMaxVec][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kLnMaxVec; ++j) {
+        const int vi = threadIdx.x + j * kLnThreads;
+        if (vi < nvec) {
+            const uint4 t = *reinterpret_cast<const uint4*>(xr + vi * 8);
+            const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                v[j][2 * i] = f.x;
+                v[j][2 * i + 1] = f.y;
+                sum += f.x + f.y;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+        }
+    }
+    const float mean = block_sum(sum, red) / (float)d;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kLnMaxVec; ++j) {
+        if (threadIdx.x + j * kLnThreads < nvec) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float c = v[j][i] - mean;
+                ss = fmaf(c, c, ss);
+            }
+        }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red) / (float)d + eps);
+    // normalised value as torch stores it (fp16), which is what the quantiser sees
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < kLnMaxVec; ++j) {
+        if (threadIdx.x + j * kLnThreads < nvec) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[j][i] = __half2float(__float2half_rn((v[j][i] - mean) * rstd));
+                amax = fmaxf(amax, fabsf(v[j][i]));
+            }
+        }
+    }
+    amax = block_max(amax, red);
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+    if (threadIdx.x == 0) scales[row] = scale;
+    int8_t* qr = q + row * d;
+#pragma unroll
+    for (int j = 0; j < kLnMaxVec; ++j) {
+        const int vi = threadIdx.x + j * kLnThreads;
+        if (vi < nvec) {
+            uint32_t w[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                w[k] = (uint32_t)(quant_exact(v[j][4 * k], scale) & 0xff) |
+                       ((uint32_t)(quant_exact(v[j][4 * k + 1], scale) & 0xff) << 8) |
+                       ((uint32_t)(quant_exact(v[j][4 * k + 2], scale) & 0xff) << 16) |
+                       ((uint32_t)(quant_exact(v[j][4 * k + 3], scale) & 0xff) << 24);
+            *reinterpret_cast<uint2*>(qr + vi * 8) = make_uint2(w[0], w[1]);
+        }
+    }
+}
+
+// One warp per (tensor, b*h) row of D fp16 values (D a multiple of 32, <= 256).
+__global__ void __launch_bounds__(128)
+kv_append_quantize_kernel(const __half* __restrict__ k_new, const __half* __restrict__ v_new,
+                          int8_t* __restrict__ K, int8_t* __restrict__ V, float* __restrict__ sK,
+                          float* __restrict__ sV, const int* __restrict__ pos_per_row, int pos0, int BH,
+                          int S_cap, int D) {
+    const int warp = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (warp >= 2 * BH) return;
+    const bool is_v = warp >= BH;
+    const int bh = is_v ? warp - BH : warp;
+    const __half* src = (is_v ? v_new : k_new) + (size_t)bh * D;
+    const int pos = pos_per_row ? pos_per_row[bh] : pos0;
+    if (pos < 0 || pos >= S_cap) return;                   // out of the cache: nothing is written
+    constexpr int kMaxPerLane = 8;
+    const int per_lane = D / 32;
+    float x[kMaxPerLane];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        x[i] = (i < per_lane) ? __half2float(src[lane * per_lane + i]) : 0.f;
+        amax = fmaxf(amax, fabsf(x[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+    int8_t* dst = (is_v ? V : K) + ((size_t)bh * S_cap + pos) * D + lane * per_lane;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+        if (i < per_lane) dst[i] = (int8_t)quant_exact(x[i], scale);
+    if (lane == 0) (is_v ? sV : sK)[(size_t)bh * S_cap + pos] = scale;
+}
+
+}  // namespace
+}  // namespace i8tk
+
+using namespace i8tk;
+
+extern "C" int i8tk_layernorm_quantize_f16(const void* x_f16, int8_t* q, float* scales, int64_t rows,
+                                           int d_model, float eps, i8tk_stream_t stream) {
+    I8TK_REQUIRE(rows >= 0 && d_model >= 8, I8TK_ERR_INVALID_ARGUMENT, "rows must be >= 0 and d_model >= 8");
+    if (rows == 0) return I8TK_OK;
+    I8TK_REQUIRE(x_f16 && q && scales, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(d_model % 8 == 0 && d_model <= kLnThreads * kLnMaxVec * 8, I8TK_ERR_UNSUPPORTED,
+                 "d_model must be a multiple of 8 and at most %d (got %d)", kLnThreads * kLnMaxVec * 8, d_model);
+    I8TK_REQUIRE(rows < (1ll << 31), I8TK_ERR_UNSUPPORTED, "too many rows");
+    I8TK_REQUIRE(aligned_to(x_f16, 16) && aligned_to(q, 8), I8TK_ERR_ALIGNMENT,
+                 "x must be 16-byte and q 8-byte aligned");
+    layernorm_quantize_kernel<<<(unsigned)rows, kLnThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x_f16), q, scales, d_model, eps);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
+
+extern "C" int i8tk_kv_append_quantize_f16(const void* k_new_f16, const void* v_new_f16, int8_t* K, int8_t* V,
+                                           float* sK, float* sV, const int32_t* pos_per_row, int pos,
+                                           int BH, int S_cap, int head_dim, i8tk_stream_t stream) {
+    I8TK_REQUIRE(k_new_f16 && v_new_f16 && K && V && sK && sV, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(BH > 0 && S_cap > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
+    I8TK_REQUIRE(head_dim % 32 == 0 && head_dim >= 32 && head_dim <= 256, I8TK_ERR_UNSUPPORTED,
+                 "head_dim must be a multiple of 32 in [32, 256] (got %d)", head_dim);
+    I8TK_REQUIRE(pos_per_row || (pos >= 0 && pos < S_cap), I8TK_ERR_INVALID_ARGUMENT,
+                 "position %d outside the cache of %d positions", pos, S_cap);
+    kv_append_quantize_kernel<<<(2 * BH + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(k_new_f16), static_cast<const __half*>(v_new_f16), K, V, sK, sV, pos_per_row,
+        pos, BH, S_cap, head_dim);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}

@@ -191,6 +191,50 @@ std::tuple<torch::Tensor, torch::Tensor> quantize_per_token_torch(torch::Tensor 
     return {q, s};
 }
 
+// ---- producer-side quantisation (the eager glue of bench/bench_block.py:59-63,93-94) ----
+std::tuple<torch::Tensor, torch::Tensor> layernorm_quantize_torch(torch::Tensor t, double eps) {
+    TORCH_CHECK(t.device().is_cuda(), "t must be a CUDA tensor");
+    TORCH_CHECK(t.dtype() == torch::kFloat16, "t must be float16");
+    TORCH_CHECK(t.dim() >= 1, "t must have at least one dimension");
+    auto x = t.contiguous();
+    const int64_t cols = x.size(-1);
+    TORCH_CHECK(cols >= 8 && cols % 8 == 0 && cols <= 4096, "last dimension must be a multiple of 8, at most 4096");
+    const int64_t rows = x.numel() / cols;
+    c10::cuda::CUDAGuard guard(x.device());
+    auto q = torch::empty(x.sizes(), torch::TensorOptions().dtype(torch::kInt8).device(x.device()));
+    auto sizes = x.sizes().vec();
+    sizes.pop_back();
+    auto s = torch::empty(sizes, torch::TensorOptions().dtype(torch::kFloat32).device(x.device()));
+    if (rows == 0) return {q, s};
+    check_status(i8tk_layernorm_quantize_f16(x.data_ptr(), q.data_ptr<int8_t>(), s.data_ptr<float>(), rows,
+                                             static_cast<int>(cols), static_cast<float>(eps), current_stream()),
+                 "layernorm_quantize");
+    return {q, s};
+}
+
+// In place: K, V int8 [B,H,S_cap,D] and sK, sV fp32 (numel B*H*S_cap) receive the new token at `pos`.
+void kv_append_quantize_torch(torch::Tensor k_new, torch::Tensor v_new, torch::Tensor K, torch::Tensor V,
+                              torch::Tensor sK, torch::Tensor sV, int64_t pos) {
+    TORCH_CHECK(K.device().is_cuda() && K.dtype() == torch::kInt8 && V.dtype() == torch::kInt8 &&
+                K.dim() == 4 && V.sizes() == K.sizes() && K.is_contiguous() && V.is_contiguous(),
+                "K, V must be contiguous int8 [B,H,S_cap,D] CUDA tensors of one shape");
+    const int64_t B = K.size(0), H = K.size(1), S_cap = K.size(2), D = K.size(3);
+    TORCH_CHECK(k_new.dtype() == torch::kFloat16 && v_new.dtype() == torch::kFloat16 &&
+                k_new.numel() == B * H * D && v_new.numel() == B * H * D,
+                "k_new, v_new must be float16 with B*H*D elements");
+    TORCH_CHECK(sK.dtype() == torch::kFloat32 && sV.dtype() == torch::kFloat32 && sK.is_contiguous() &&
+                sV.is_contiguous() && sK.numel() == B * H * S_cap && sV.numel() == B * H * S_cap,
+                "sK, sV must be contiguous float32 with B*H*S_cap elements");
+    TORCH_CHECK(pos >= 0 && pos < S_cap, "position outside the cache");
+    auto kn = k_new.contiguous(), vn = v_new.contiguous();
+    c10::cuda::CUDAGuard guard(K.device());
+    check_status(i8tk_kv_append_quantize_f16(kn.data_ptr(), vn.data_ptr(), K.data_ptr<int8_t>(), V.data_ptr<int8_t>(),
+                                             sK.data_ptr<float>(), sV.data_ptr<float>(), nullptr,
+                                             static_cast<int>(pos), static_cast<int>(B * H), static_cast<int>(S_cap),
+                                             static_cast<int>(D), current_stream()),
+                 "kv_append_quantize");
+}
+
 }  // namespace
 
 #include "int8_ext_mlp.inc"
@@ -206,5 +250,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "Log-sum-exp merge of gathered decode partials — returns FP16");
     m.def("quantize_per_token", &quantize_per_token_torch,
           "Per-token symmetric INT8 quantisation — returns (int8, fp32 scales)");
+    m.def("layernorm_quantize", &layernorm_quantize_torch, pybind11::arg("t"), pybind11::arg("eps") = 1e-5,
+          "LayerNorm (no affine) + per-token INT8 quantisation of the fp16 result — returns (int8, fp32 scales)");
+    m.def("kv_append_quantize", &kv_append_quantize_torch,
+          "Quantise the new token's K and V rows per token and write them into the INT8 cache at pos (in place)");
     register_mlp_ops(m);
 }

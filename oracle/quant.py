@@ -78,3 +78,18 @@ def requant_rows_kernel_semantics(h_f16, row_absmax):
     v = (h_f16.astype(np.float32) * inv[:, None]).astype(np.float32)
     q = np.rint(np.clip(v, -128.0, 127.0)).astype(np.int8)
     return q, (amax / _F127).astype(np.float32)
+
+
+def layernorm_quantize(x_f16, eps=1e-5):
+    """LayerNorm without affine parameters over the last dimension, stored as fp16, then
+    :func:`quantize_per_token` of that fp16 tensor -- the two steps the reference's block runs
+    as eager torch code before its INT8 MLP (``bench/bench_block.py:93-94`` then ``:59-63``).
+    Mean and biased variance in float64, so this is the exactly rounded value the fp32
+    implementations (torch's and the CUDA kernel's) approximate to within an fp16 ulp.
+    Returns ``(y_f16, q_int8, scales_f32)``."""
+    x = np.asarray(x_f16, dtype=np.float16).astype(np.float64)
+    mean = x.mean(axis=-1, keepdims=True)
+    var = ((x - mean) ** 2).mean(axis=-1, keepdims=True)
+    y = ((x - mean) / np.sqrt(var + eps)).astype(np.float32).astype(np.float16)
+    q, s = quantize_per_token(y)
+    return y, q, s

@@ -58,8 +58,27 @@ def quantiser_cases(gen):
     return cases
 
 
-def main(ref_root):
+def layernorm_quantize_cases(test_int8):
+    """LayerNorm as the reference's block applies it (bench/bench_block.py:93-94:
+    F.layer_norm(x, (d,)) on fp16) followed by the reference's per-token quantiser
+    (bench/bench_block.py:59-63 == tests/test_int8.py:47-63), on the CPU."""
+    gen = torch.Generator().manual_seed(777)
+    out = {}
+    for name, (rows, d, scale, shift) in {"d768": (9, 768, 1.0, 0.0), "d1024_shifted": (7, 1024, 3.0, 5.0),
+                                          "d64": (12, 64, 0.1, -0.3), "d4096": (3, 4096, 2.0, 0.5)}.items():
+        x = (torch.randn(rows, d, generator=gen) * scale + shift).half()
+        y = F.layer_norm(x, (d,))
+        q, sc = test_int8.quantize_per_token(y)
+        out[name + "__x"], out[name + "__y"] = x.numpy(), y.numpy()
+        out[name + "__q"], out[name + "__s"] = q.numpy(), sc.numpy()
+    np.savez_compressed(os.path.join(HERE, "layernorm_quantize.npz"), **out)
+
+
+def main(ref_root, only=None):
     test_int8, validate_int8 = _import_reference(ref_root)
+    if only == "layernorm":
+        layernorm_quantize_cases(test_int8)
+        return
     torch.manual_seed(0)
     gen = torch.Generator().manual_seed(20240607)
 
@@ -141,6 +160,8 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: make_golden.py <path to the reference checkout>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        sys.exit("usage: make_golden.py <path to the reference checkout> [layernorm]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)
+    if len(sys.argv) == 2:
+        main(sys.argv[1], "layernorm")

@@ -1,0 +1,105 @@
+"""Producer-side quantisation ops: LayerNorm fused with the per-token quantiser, and
+quantise-on-write of the new token's K/V rows into the INT8 cache."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import quant
+from helpers import ext, gold
+
+pytestmark = pytest.mark.gpu
+
+
+def _check_ln(x_np, q, s, y_ref, q_ref, s_ref):
+    dq = np.abs(q.astype(np.int32) - q_ref.astype(np.int32))
+    assert dq.max() <= 1, dq.max()
+    assert np.mean(dq != 0) < 2e-3, np.mean(dq != 0)
+    assert np.allclose(s, s_ref, rtol=1e-3, atol=0)
+
+
+def test_layernorm_quantize_golden_and_oracle():
+    g = gold("layernorm_quantize.npz")
+    names = sorted(k[:-3] for k in g.files if k.endswith("__x"))
+    assert len(names) == 4
+    for n in names:
+        x = g[n + "__x"]
+        q, s = ext().layernorm_quantize(torch.from_numpy(x).cuda())
+        q, s = q.cpu().numpy(), s.cpu().numpy()
+        _check_ln(x, q, s, g[n + "__y"], g[n + "__q"], g[n + "__s"])      # torch CPU + reference quantiser
+        y, q_o, s_o = quant.layernorm_quantize(x)
+        _check_ln(x, q, s, y, q_o, s_o)                                   # float64 oracle
+
+
+@pytest.mark.parametrize("shape", [(4, 128, 768), (1, 4096, 1024), (3, 5, 64), (2, 7, 4096), (1, 1, 8)])
+def test_layernorm_quantize_equals_the_two_step_path(shape):
+    torch.manual_seed(shape[-1])
+    x = (torch.randn(*shape, device="cuda") * 2.0 + 0.5).half()
+    q, s = ext().layernorm_quantize(x)
+    assert q.shape == x.shape and s.shape == x.shape[:-1] and q.dtype == torch.int8
+    q2, s2 = ext().quantize_per_token(F.layer_norm(x, (shape[-1],)))
+    dq = (q.int() - q2.int()).abs()
+    assert int(dq.max()) <= 1 and float((dq != 0).float().mean()) < 2e-3
+    assert torch.allclose(s, s2, rtol=1e-3, atol=0)
+
+
+def test_layernorm_quantize_edge_rows_and_errors():
+    e = ext()
+    x = torch.zeros(3, 256, device="cuda", dtype=torch.float16)
+    x[1] = 7.0                                    # constant row: variance 0, all codes 0
+    x[2, 0] = 100.0                               # one spike
+    q, s = e.layernorm_quantize(x)
+    assert torch.all(q[0] == 0) and torch.all(q[1] == 0)
+    assert int(q[2, 0]) == 127 and not torch.isnan(s).any()
+    q, s = e.layernorm_quantize(torch.zeros(0, 64, device="cuda", dtype=torch.float16))
+    assert q.numel() == 0 and s.numel() == 0
+    with pytest.raises(RuntimeError):
+        e.layernorm_quantize(torch.zeros(2, 60, device="cuda", dtype=torch.float16))
+    with pytest.raises(RuntimeError):
+        e.layernorm_quantize(torch.zeros(2, 64, device="cuda", dtype=torch.float32))
+
+
+@pytest.mark.parametrize("B,H,D,S_cap,pos", [(2, 3, 64, 40, 0), (1, 4, 128, 300, 299), (3, 2, 64, 129, 128)])
+def test_kv_append_is_quantise_on_write(B, H, D, S_cap, pos):
+    torch.manual_seed(pos + D)
+    e = ext()
+    K = torch.randint(-127, 128, (B, H, S_cap, D), dtype=torch.int8, device="cuda")
+    V = torch.randint(-127, 128, (B, H, S_cap, D), dtype=torch.int8, device="cuda")
+    sK = torch.rand(B * H * S_cap, device="cuda") + 0.5
+    sV = torch.rand(B * H * S_cap, device="cuda") + 0.5
+    K0, V0, sK0, sV0 = K.clone(), V.clone(), sK.clone(), sV.clone()
+    k_new = torch.randn(B, H, D, device="cuda", dtype=torch.float16)
+    v_new = torch.randn(B, H, D, device="cuda", dtype=torch.float16) * 3
+    e.kv_append_quantize(k_new, v_new, K, V, sK, sV, pos)
+    # bit-identical to the per-token quantiser (whose CPU arithmetic is the reference's)
+    for new, cache, sc, cache0, sc0 in ((k_new, K, sK, K0, sK0), (v_new, V, sV, V0, sV0)):
+        q_ref, s_ref = quant.quantize_per_token(new.cpu().numpy())
+        assert np.array_equal(cache[:, :, pos].cpu().numpy(), q_ref)
+        got_s = sc.view(B, H, S_cap)[:, :, pos].cpu().numpy()
+        assert np.array_equal(got_s.view(np.uint32), s_ref.view(np.uint32))
+        mask = torch.ones(S_cap, dtype=torch.bool, device="cuda")
+        mask[pos] = False
+        assert torch.equal(cache[:, :, mask], cache0[:, :, mask])          # nothing else touched
+        assert torch.equal(sc.view(B, H, S_cap)[:, :, mask], sc0.view(B, H, S_cap)[:, :, mask])
+    with pytest.raises(RuntimeError):
+        e.kv_append_quantize(k_new, v_new, K, V, sK, sV, S_cap)
+
+
+def test_decode_after_append_equals_decode_on_the_longer_cache():
+    torch.manual_seed(5)
+    e = ext()
+    B, H, D, S = 2, 4, 64, 200
+    Kf = torch.randn(B, H, S + 1, D, device="cuda", dtype=torch.float16)
+    Vf = torch.randn(B, H, S + 1, D, device="cuda", dtype=torch.float16)
+    Qi, sQ = e.quantize_per_token(torch.randn(B, H, D, device="cuda", dtype=torch.float16))
+    Ki_full, sK_full = e.quantize_per_token(Kf)
+    Vi_full, sV_full = e.quantize_per_token(Vf)
+    want = e.int8_decode_attention_forward(Qi, Ki_full, Vi_full, sQ.reshape(-1), sK_full.reshape(-1), sV_full.reshape(-1))
+    # cache holding the first S positions, room for one more; the last one arrives by append
+    Ki, Vi = Ki_full.clone(), Vi_full.clone()
+    sK, sV = sK_full.reshape(-1).clone(), sV_full.reshape(-1).clone()
+    Ki[:, :, S] = 0; Vi[:, :, S] = 0
+    sK.view(B, H, S + 1)[:, :, S] = 0; sV.view(B, H, S + 1)[:, :, S] = 0
+    e.kv_append_quantize(Kf[:, :, S].contiguous(), Vf[:, :, S].contiguous(), Ki, Vi, sK, sV, S)
+    got = e.int8_decode_attention_forward(Qi, Ki, Vi, sQ.reshape(-1), sK, sV)
+    assert torch.equal(got, want)

@@ -101,3 +101,18 @@ def test_kernel_mlp_close_to_simulation():
     # the reference requires its kernel within 0.05 of the simulation
     assert np.abs(out - ref).max() < 0.05
     assert _cos(out, ref) > 0.9999
+
+
+def test_layernorm_quantize_against_torch_cpu():
+    """The float64 LayerNorm of the oracle and torch's fp32 one can differ by one fp16 ulp on a
+    few elements (and then by one code): require near-identity, not bit-identity."""
+    g = _load("layernorm_quantize.npz")
+    names = _names(g)
+    assert len(names) == 4
+    for n in names:
+        y, q, s = quant.layernorm_quantize(g[n + "__x"])
+        ulp_off = np.mean(y.view(np.uint16) != g[n + "__y"].view(np.uint16))
+        assert ulp_off < 2e-3, (n, ulp_off)
+        dq = np.abs(q.astype(np.int32) - g[n + "__q"].astype(np.int32))
+        assert dq.max() <= 1 and np.mean(dq != 0) < 2e-3, (n, dq.max(), np.mean(dq != 0))
+        assert np.allclose(s, g[n + "__s"], rtol=1e-3, atol=0), n
