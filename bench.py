@@ -485,7 +485,35 @@ def sweep(torch, ext, cabi, world, rank, barrier, dist):
         res.extend(quantiser_and_prefill_sweep(torch, ext))
         res.extend(mlp_sweep(torch, ext, cabi))
         res.extend(block_sweep(torch))
+        res.extend(paged_sweep(torch, ext))
     return res
+
+
+def paged_sweep(torch, ext):
+    """The headline geometry (B32 H12 D64 ctx 32768) read through a paged INT8 KV cache with a
+    shuffled page table, all requests at full length: GB/s of K+V as in the headline metric."""
+    out = []
+    B, H, D, S = 32, 12, 64, 32768
+    g = torch.Generator(device="cuda").manual_seed(0)
+    Qi, sQ = ext.quantize_per_token(torch.randn(B, H, D, device="cuda", dtype=torch.float16, generator=g))
+    for page in (16, 64, 128):
+        npp = S // page
+        pages = B * npp
+        Kp = torch.randint(-127, 128, (pages, H, page, D), dtype=torch.int8, device="cuda", generator=g)
+        Vp = torch.randint(-127, 128, (pages, H, page, D), dtype=torch.int8, device="cuda", generator=g)
+        sKp = torch.rand(pages, H, page, device="cuda", generator=g) * 0.02 + 0.01
+        sVp = torch.rand(pages, H, page, device="cuda", generator=g) * 0.02 + 0.01
+        table = torch.randperm(pages, device="cuda", generator=g).to(torch.int32).view(B, npp).contiguous()
+        seq = torch.full((B,), S, dtype=torch.int32, device="cuda")
+        sq = sQ.reshape(-1).contiguous()
+        steps = 20
+        el = timed_steps(torch, lambda: ext.int8_decode_attention_paged(Qi, Kp, Vp, sq, sKp, sVp, table, seq, S), steps, 3)
+        gbps = kv_bytes(B, H, S, D) * steps / el / 1e9
+        out.append({"workload": f"paged decode B{B} H{H} D{D} ctx{S}, page {page}, shuffled page table",
+                    "us_per_step": el / steps * 1e6, "GBps": gbps, "pct_of_8TBps_per_gpu": gbps / 80.0})
+        del Kp, Vp, sKp, sVp
+        torch.cuda.empty_cache()
+    return out
 
 
 def block_sweep(torch):

@@ -152,6 +152,26 @@ int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_t* K, const
                                          const float* sQ, const float* sK, const float* sV,
                                          int BH, int S, int head_dim, i8tk_stream_t stream);
 
+/* Paged INT8 KV cache with a length per request: the layout a serving stack keeps (the
+ * reference's own kernel takes contiguous tensors only; its benchmark compares against a
+ * paged peer, bench/bench_decode_sota.py:44,65-90).
+ *   K_pool, V_pool  int8 [num_pages, heads, page_size, head_dim]
+ *   sK_pool, sV_pool fp32 [num_pages, heads, page_size]
+ *   page_table      int32 [batch, max_pages_per_seq] (device): request b holds, in sequence
+ *                   order, pages page_table[b][0 .. ceil(seq_lens[b] / page_size))
+ *   seq_lens        int32 [batch] (device), each in [1, max_seq_len]
+ *   Q int8 [batch*heads, head_dim], sQ fp32 [batch*heads], out fp16 [batch*heads, head_dim]
+ * max_seq_len is a host-side upper bound on seq_lens (it sizes the grid and the workspace:
+ * i8tk_decode_workspace_bytes(batch*heads, max_seq_len, head_dim)); tiles past a request's
+ * end move no bytes.  page_size 16, 32, 64 or 128; head_dim 64 or 128; pools 16-byte aligned. */
+int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool, const int8_t* V_pool,
+                                void* out_f16, const float* sQ,
+                                const float* sK_pool, const float* sV_pool,
+                                const int32_t* page_table, const int32_t* seq_lens,
+                                int batch, int heads, int max_seq_len, int page_size,
+                                int max_pages_per_seq, int head_dim,
+                                void* workspace, size_t workspace_bytes, i8tk_stream_t stream);
+
 /* Sequence-sharded form: the same scan over this caller's KV positions, but
  * the result is left as ONE unnormalised online-softmax partial per (b,h):
  *   part[bh] = { m (log2 units), l, 0, 0, acc[0..D) }   -- D+4 floats per row

@@ -70,6 +70,17 @@ struct DecodePlan {
     long long total;     // BH * tpb
 };
 
+// Paged KV cache (PAGED kernels): K, V and their scales live in pools of fixed-size pages,
+// laid out [page][head][position in page][D] (scales [page][head][position in page]); request
+// b owns pages page_table[b][0 .. ceil(seq_lens[b] / page)) in sequence order.
+struct PagedKV {
+    const int* page_table;   // [B][max_pages]
+    const int* seq_lens;     // [B] positions in use, >= 1
+    int H;                   // heads per request: b = bh / H, h = bh % H
+    int page;                // positions per page: 16, 32, 64 or 128
+    int max_pages;           // row length of page_table
+};
+
 __device__ __forceinline__ int dot16(const int4& q, const int4& k) {
     int d = __dp4a(q.x, k.x, 0);
     d = __dp4a(q.y, k.y, d);
@@ -157,14 +168,17 @@ __device__ __forceinline__ float warp_sum(float v) {
 // SCALES_BULK: the per-position scales ride the bulk copies (needs S % 4 == 0
 // and 16-byte aligned scale arrays); otherwise the owning lane loads them.
 // ---------------------------------------------------------------------------
-template <int D, bool SCALES_BULK>
+// PAGED: K, V, sK, sV are page pools addressed through `pg` and every request has its own
+// length (S is then the longest one: tiles past a request's end carry no bytes).
+template <int D, bool SCALES_BULK, bool PAGED>
 __global__ void __launch_bounds__(kThreads)
 decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K,
                       const int8_t* __restrict__ V, const float* __restrict__ sQ,
                       const float* __restrict__ sK, const float* __restrict__ sV,
                       float* __restrict__ rows,     // [nctas * maxseg * kConsumers, D+4]
                       int S, DecodePlan plan, float score_scale_log2,
-                      uint32_t* __restrict__ status) {
+                      uint32_t* __restrict__ status, PagedKV pg) {
+    static_assert(!PAGED || SCALES_BULK, "paged scales always ride the bulk copies");
     using T = DecodeTraits<D>;
     constexpr int LPR = T::LPR, RPP = T::RPP, STAGES = T::STAGES;
 
@@ -196,23 +210,46 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
 
     if (warp == kConsumers) {
         // ---- producer: one lane walks the tile list and keeps the ring full ----
-        if (lane != 0) return;
+        // contiguous cache: one lane issues the four copies of a tile; paged cache: lane q issues
+        // the copies of page q of the tile, so a tile of eight 16-position pages costs no more
+        // issue time than one page
+        if (!PAGED && lane != 0) return;
         const uint64_t stream_once = l2_policy_evict_first();   // K, V and their scales are read once
         int p_bh = bh0, p_tb = tb0;
         for (int i = 0; i < ntl; ++i) {
             const int st = i % STAGES;
             if (i >= STAGES) {
                 if (!mbar_wait_bounded(empty0 + 8 * st, ((i / STAGES) - 1) & 1)) {
-                    atomicExch(status, kDeviceTimeoutMagic);
+                    if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
                     return;
                 }
             }
             const int pos0 = p_tb * kTile;
+            const uint32_t bar = full0 + 8 * st;
+            const uint32_t dst = ring_s + st * T::STAGE_BYTES;
+            if constexpr (PAGED) {
+                // the tile is made of 128 / page pages; those past the request's end do not exist
+                const int b = p_bh / pg.H, h = p_bh - b * pg.H;
+                const int len = __ldg(pg.seq_lens + b);
+                const int ppt = kTile / pg.page;
+                int npg = (len - pos0 + pg.page - 1) / pg.page;
+                npg = npg < 0 ? 0 : (npg > ppt ? ppt : npg);
+                const uint32_t kv_bytes = (uint32_t)pg.page * D, sc_bytes = (uint32_t)pg.page * 4;
+                if (lane == 0) mbar_expect_tx(bar, (uint32_t)npg * 2 * (kv_bytes + sc_bytes));
+                const int* ids = pg.page_table + (size_t)b * pg.max_pages + pos0 / pg.page;
+                if (lane < npg) {
+                    const int q = lane;
+                    const size_t first = ((size_t)__ldg(ids + q) * pg.H + h) * pg.page;   // first position of the page
+                    bulk_g2s_hint(dst + 2 * T::TILE_BYTES + q * sc_bytes, sK + first, sc_bytes, bar, stream_once);
+                    bulk_g2s_hint(dst + 2 * T::TILE_BYTES + T::SCALE_BYTES + q * sc_bytes, sV + first, sc_bytes, bar,
+                                  stream_once);
+                    bulk_g2s_hint(dst + q * kv_bytes, K + first * D, kv_bytes, bar, stream_once);
+                    bulk_g2s_hint(dst + T::TILE_BYTES + q * kv_bytes, V + first * D, kv_bytes, bar, stream_once);
+                }
+            } else {
             const int nrow = min(kTile, S - pos0);
             const size_t row = (size_t)p_bh * S + pos0;
             const uint32_t kv_bytes = (uint32_t)nrow * D;
-            const uint32_t bar = full0 + 8 * st;
-            const uint32_t dst = ring_s + st * T::STAGE_BYTES;
             if constexpr (SCALES_BULK) {
                 const uint32_t sc_bytes = (uint32_t)nrow * 4;       // multiple of 16: S % 4 == 0
                 mbar_expect_tx(bar, 2 * kv_bytes + 2 * sc_bytes);
@@ -223,6 +260,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
             }
             bulk_g2s_hint(dst, K + row * D, kv_bytes, bar, stream_once);
             bulk_g2s_hint(dst + T::TILE_BYTES, V + row * D, kv_bytes, bar, stream_once);
+            }
             if (++p_tb == tpb) { p_tb = 0; ++p_bh; }
         }
         return;
@@ -243,6 +281,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         const float qs = sQ[c_bh] * score_scale_log2;
         const float* sKb = sK + (size_t)c_bh * S;
         const float* sVb = sV + (size_t)c_bh * S;
+        const int Sb = PAGED ? __ldg(pg.seq_lens + c_bh / pg.H) : S;    // positions of this (b,h) row
         float m = -INFINITY, l = 0.f;
         f32x2 acc[8];
 #pragma unroll
@@ -256,7 +295,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
 
         for (int t = 0; t < seg_tiles; ++t, ++i) {
             const int pos0 = (c_tb + t) * kTile;
-            const bool valid = (pos0 + own) < S;
+            const bool valid = (pos0 + own) < Sb;
 
             float sk0 = 0.f, sv0 = 0.f;
             if constexpr (!SCALES_BULK) {
@@ -275,7 +314,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
                 return;
             }
 
-            if (pos0 + warp * kSub < S) {           // this warp's sub-tile has rows (warp-uniform)
+            if (pos0 + warp * kSub < Sb) {          // this warp's sub-tile has rows (warp-uniform)
                 const unsigned char* stage = smem + st * T::STAGE_BYTES;
                 const int4* Kt = reinterpret_cast<const int4*>(stage + warp * kSub * D);
                 const int4* Vt = reinterpret_cast<const int4*>(stage + T::TILE_BYTES + warp * kSub * D);
@@ -632,23 +671,23 @@ size_t workspace_bytes(int BH, int S, int D) {
     return 256 + rows_bytes(make_plan(BH, S, D, sm_count()), D);
 }
 
-template <int D, bool SCALES_BULK>
+template <int D, bool SCALES_BULK, bool PAGED = false>
 int launch_partial(const int8_t* Q, const int8_t* K, const int8_t* V, const float* sQ,
                    const float* sK, const float* sV, float* rows, int S, const DecodePlan& p,
-                   uint32_t* status, cudaStream_t stream) {
+                   uint32_t* status, cudaStream_t stream, PagedKV pg = PagedKV{}) {
     using T = DecodeTraits<D>;
     static bool attr_done[64] = {false};   // per template instance
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(decode_partial_kernel<D, SCALES_BULK>,
+        I8TK_CUDA(cudaFuncSetAttribute(decode_partial_kernel<D, SCALES_BULK, PAGED>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
         attr_done[dev] = true;
     }
     const float score_scale_log2 = kLog2e / sqrtf((float)D);
     if (g_probe_start) I8TK_CUDA(cudaEventRecord(g_probe_start, stream));
-    decode_partial_kernel<D, SCALES_BULK><<<p.nctas, kThreads, T::SMEM_BYTES, stream>>>(
-        Q, K, V, sQ, sK, sV, rows, S, p, score_scale_log2, status);
+    decode_partial_kernel<D, SCALES_BULK, PAGED><<<p.nctas, kThreads, T::SMEM_BYTES, stream>>>(
+        Q, K, V, sQ, sK, sV, rows, S, p, score_scale_log2, status, pg);
     I8TK_CUDA(cudaGetLastError());
     if (g_probe_stop) I8TK_CUDA(cudaEventRecord(g_probe_stop, stream));
     return I8TK_OK;
@@ -836,6 +875,50 @@ extern "C" int i8tk_decode_attention_seq_sharded(const int8_t* Q, const int8_t* 
     else
         I8TK_CUDA(launch_after(decode_exchange_kernel<128>, dim3(grid), dim3(128), 0, st, (const float*)rows, BH, p,
                                empty, pp, pf, rank, world, epoch, static_cast<__half*>(out_f16), status));
+    return I8TK_OK;
+}
+
+extern "C" int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool, const int8_t* V_pool,
+                                           void* out_f16, const float* sQ, const float* sK_pool,
+                                           const float* sV_pool, const int32_t* page_table,
+                                           const int32_t* seq_lens, int batch, int heads, int max_seq_len,
+                                           int page_size, int max_pages_per_seq, int head_dim, void* workspace,
+                                           size_t workspace_bytes, i8tk_stream_t stream) {
+    I8TK_REQUIRE(Q && K_pool && V_pool && out_f16 && sQ && sK_pool && sV_pool && page_table && seq_lens,
+                 I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(batch > 0 && heads > 0 && max_seq_len > 0 && max_pages_per_seq > 0, I8TK_ERR_INVALID_ARGUMENT,
+                 "sizes must be positive");
+    I8TK_REQUIRE(head_dim == 64 || head_dim == 128, I8TK_ERR_UNSUPPORTED, "head_dim must be 64 or 128 (got %d)",
+                 head_dim);
+    I8TK_REQUIRE(page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128, I8TK_ERR_UNSUPPORTED,
+                 "page_size must be 16, 32, 64 or 128 (got %d)", page_size);
+    I8TK_REQUIRE((long long)max_pages_per_seq * page_size >= max_seq_len, I8TK_ERR_INVALID_ARGUMENT,
+                 "max_seq_len %d does not fit %d pages of %d", max_seq_len, max_pages_per_seq, page_size);
+    I8TK_REQUIRE(aligned_to(Q, 16) && aligned_to(K_pool, 16) && aligned_to(V_pool, 16) && aligned_to(sK_pool, 16) &&
+                     aligned_to(sV_pool, 16),
+                 I8TK_ERR_ALIGNMENT, "Q, the pools and their scales must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int BH = batch * heads;
+    const DecodePlan p = make_plan(BH, max_seq_len, head_dim, sm_count());
+    const size_t need = 256 + rows_bytes(p, head_dim);
+    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= need, I8TK_ERR_WORKSPACE,
+                 "decode workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
+    I8TK_REQUIRE(aligned_to(workspace, 256), I8TK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+    uint32_t* status = reinterpret_cast<uint32_t*>(workspace);
+    float* rows = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 256);
+    const PagedKV pg{page_table, seq_lens, heads, page_size, max_pages_per_seq};
+    int rc;
+    if (head_dim == 64) {
+        rc = launch_partial<64, true, true>(Q, K_pool, V_pool, sQ, sK_pool, sV_pool, rows, max_seq_len, p, status, st, pg);
+        if (rc != I8TK_OK) return rc;
+        I8TK_CUDA(launch_after(decode_combine_kernel<64, true>, dim3((BH + 3) / 4), dim3(128), 0, st,
+                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr));
+    } else {
+        rc = launch_partial<128, true, true>(Q, K_pool, V_pool, sQ, sK_pool, sV_pool, rows, max_seq_len, p, status, st, pg);
+        if (rc != I8TK_OK) return rc;
+        I8TK_CUDA(launch_after(decode_combine_kernel<128, true>, dim3((BH + 3) / 4), dim3(128), 0, st,
+                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr));
+    }
     return I8TK_OK;
 }
 

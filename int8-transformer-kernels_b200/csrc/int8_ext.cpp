@@ -91,6 +91,54 @@ torch::Tensor int8_decode_attention_forward_torch(torch::Tensor Q, torch::Tensor
     return out;
 }
 
+// Paged INT8 KV cache, one length per request.  Pools int8 [num_pages, H, page, D] and fp32
+// [num_pages, H, page]; page_table int32 [B, max_pages]; seq_lens int32 [B]; max_seq_len is the
+// caller's host-side bound on seq_lens.
+torch::Tensor int8_decode_attention_paged_torch(torch::Tensor Q, torch::Tensor K_pool, torch::Tensor V_pool,
+                                                torch::Tensor scale_Q, torch::Tensor sK_pool,
+                                                torch::Tensor sV_pool, torch::Tensor page_table,
+                                                torch::Tensor seq_lens, int64_t max_seq_len) {
+    TORCH_CHECK(Q.device().is_cuda() && Q.dtype() == torch::kInt8 && Q.dim() == 3 && Q.is_contiguous(),
+                "Q must be a contiguous int8 CUDA tensor (batch, heads, head_dim)");
+    TORCH_CHECK(K_pool.dtype() == torch::kInt8 && V_pool.dtype() == torch::kInt8 && K_pool.dim() == 4 &&
+                    K_pool.sizes() == V_pool.sizes() && K_pool.is_contiguous() && V_pool.is_contiguous(),
+                "K_pool, V_pool must be contiguous int8 (num_pages, heads, page_size, head_dim) of one shape");
+    const int64_t B = Q.size(0), H = Q.size(1), D = Q.size(2);
+    const int64_t pages = K_pool.size(0), page = K_pool.size(2);
+    TORCH_CHECK(K_pool.size(1) == H && K_pool.size(3) == D, "Q / pool head or head_dim mismatch");
+    TORCH_CHECK(D == 64 || D == 128, "decode kernel v1 supports head_dim 64 or 128");
+    TORCH_CHECK(page == 16 || page == 32 || page == 64 || page == 128, "page_size must be 16, 32, 64 or 128");
+    TORCH_CHECK(sK_pool.dtype() == torch::kFloat32 && sV_pool.dtype() == torch::kFloat32 &&
+                    sK_pool.is_contiguous() && sV_pool.is_contiguous() && sK_pool.numel() == pages * H * page &&
+                    sV_pool.numel() == pages * H * page,
+                "sK_pool, sV_pool must be contiguous float32 with num_pages*heads*page_size elements");
+    TORCH_CHECK(scale_Q.dtype() == torch::kFloat32 && scale_Q.numel() == B * H, "scale_Q must be float32, B*H elements");
+    TORCH_CHECK(page_table.dtype() == torch::kInt32 && page_table.dim() == 2 && page_table.size(0) == B &&
+                    page_table.is_contiguous(), "page_table must be contiguous int32 (batch, max_pages)");
+    TORCH_CHECK(seq_lens.dtype() == torch::kInt32 && seq_lens.numel() == B && seq_lens.is_contiguous(),
+                "seq_lens must be contiguous int32 with batch elements");
+    TORCH_CHECK(page_table.device() == Q.device() && seq_lens.device() == Q.device() &&
+                    K_pool.device() == Q.device() && V_pool.device() == Q.device() &&
+                    sK_pool.device() == Q.device() && sV_pool.device() == Q.device() && scale_Q.device() == Q.device(),
+                "all tensors must be on one CUDA device");
+    TORCH_CHECK(max_seq_len >= 1 && max_seq_len <= page_table.size(1) * page, "max_seq_len does not fit the page table");
+    c10::cuda::CUDAGuard guard(Q.device());
+    auto sq = scale_Q.contiguous();
+    auto out = torch::empty({B, H, D}, torch::TensorOptions().dtype(torch::kFloat16).device(Q.device()));
+    const size_t wbytes = i8tk_decode_workspace_bytes(static_cast<int>(B * H), static_cast<int>(max_seq_len),
+                                                      static_cast<int>(D));
+    auto ws = make_workspace(wbytes, Q.device());
+    check_status(i8tk_decode_attention_paged(
+                     Q.data_ptr<int8_t>(), K_pool.data_ptr<int8_t>(), V_pool.data_ptr<int8_t>(), out.data_ptr(),
+                     sq.data_ptr<float>(), sK_pool.data_ptr<float>(), sV_pool.data_ptr<float>(),
+                     page_table.data_ptr<int32_t>(), seq_lens.data_ptr<int32_t>(), static_cast<int>(B),
+                     static_cast<int>(H), static_cast<int>(max_seq_len), static_cast<int>(page),
+                     static_cast<int>(page_table.size(1)), static_cast<int>(D), ws.data_ptr(), wbytes,
+                     current_stream()),
+                 "int8_decode_attention_paged");
+    return out;
+}
+
 // Unnormalised (m, l, acc) rows for a KV shard: fp32 [B, H, D+4].
 torch::Tensor int8_decode_attention_partial_torch(torch::Tensor Q, torch::Tensor K, torch::Tensor V,
                                                   torch::Tensor scale_Q, torch::Tensor scale_K,
@@ -244,6 +292,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "INT8 attention with per-token quantization (CUDA) — returns FP16");
     m.def("int8_decode_attention_forward", &int8_decode_attention_forward_torch,
           "INT8 flash-decoding attention (seq_q==1, INT8 KV cache) — returns FP16");
+    m.def("int8_decode_attention_paged", &int8_decode_attention_paged_torch,
+          "INT8 flash-decoding attention over a paged INT8 KV cache with per-request lengths — returns FP16");
     m.def("int8_decode_attention_partial", &int8_decode_attention_partial_torch,
           "INT8 decode attention over a KV shard — returns unnormalised (m, l, 0, 0, acc[D]) rows");
     m.def("int8_decode_combine_partials", &int8_decode_combine_partials_torch,
