@@ -133,7 +133,7 @@ __device__ __forceinline__ int row_owner_lane(int r) {
 // group of G lanes (G a power of two <= 32); lane i of the group owns vectors
 // i, i+G, ... (at most NV of them).  Each group keeps R rows in flight.
 template <typename T, int G, int NV, int R>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
                          float* __restrict__ scales, long long rows, int cols) {
     constexpr int N = Vec16<T>::N;
