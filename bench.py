@@ -564,6 +564,19 @@ def quantiser_and_prefill_sweep(torch, ext):
                     "GBps": byts * steps / el / 1e9, "l2_resident": byts < 100e6})
         del x
         torch.cuda.empty_cache()
+    import torch.nn.functional as F
+    for rows, cols in ((16384, 1024), (131072, 1024)):
+        x = torch.randn(rows, cols, device="cuda", dtype=torch.float16)
+        steps = 20
+        el = timed_steps(torch, lambda: ext.layernorm_quantize(x), steps, 3)
+        el2 = timed_steps(torch, lambda: ext.quantize_per_token(F.layer_norm(x, (cols,))), steps, 3)
+        byts = rows * cols * 3 + rows * 4
+        out.append({"workload": f"layernorm_quantize [{rows}, {cols}] fp16 (LayerNorm + per-token quantiser, one pass)",
+                    "us_per_step": el / steps * 1e6, "GBps": byts * steps / el / 1e9,
+                    "us_per_step_torch_layer_norm_then_quantize_per_token": el2 / steps * 1e6,
+                    "l2_resident": byts < 100e6})
+        del x
+        torch.cuda.empty_cache()
     for (b, h, s, d) in ((8, 8, 4096, 64), (4, 8, 4096, 128)):
         g = torch.Generator(device="cuda").manual_seed(0)
         t = []

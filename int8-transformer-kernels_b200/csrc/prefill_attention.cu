@@ -287,16 +287,18 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             const float2 a = unpack2(y4[0]), b = unpack2(y4[1]), c = unpack2(y4[2]), d = unpack2(y4[3]);
             mx = max3(max3(mx, a.x, a.y), max3(b.x, b.y, c.x), fmaxf(c.y, fmaxf(d.x, d.y)));
         };
-        // the same for a partial last tile: columns from nv on (nv may be <= 0) do not exist
-        auto convert8_tail = [&](const uint32_t* sr8, const float* k8, f32x2* y4, float& mx, int nv) {
-            float dummy = -INFINITY;
-            convert8(sr8, k8, y4, dummy);
+        // partial last tile: its scores were converted like any other (the operand rows past the
+        // end hold the next head's data or TMA's zero fill, so they are finite); this pass, run once
+        // per CTA, then removes the columns that do not exist and recomputes the maximum
+        auto mask_tail = [&](f32x2* yy, float& mx) {
+            mx = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float2 v = unpack2(y4[e]);
-                if (2 * e >= nv) v.x = -INFINITY;
-                if (2 * e + 1 >= nv) v.y = -INFINITY;
-                y4[e] = pack2(v.x, v.y);
+            for (int e = 0; e < 32; ++e) {
+                float2 v = unpack2(yy[e]);
+                const int col = half * 64 + 2 * e;
+                if (col >= tail_valid) v.x = -INFINITY;
+                if (col + 1 >= tail_valid) v.y = -INFINITY;
+                yy[e] = pack2(v.x, v.y);
                 mx = fmaxf(mx, fmaxf(v.x, v.y));
             }
         };
@@ -333,14 +335,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 for (int cc = 0; cc < 4; ++cc) {
                     tmem_ld_wait(sr[cc & 1]);
                     if (cc < 3) tmem_ld16(s_addr + (cc + 1) * 16, sr[(cc + 1) & 1]);
-                    if (nt == 1 && tail_valid < kKT) {
-                        convert8_tail(&sr[cc & 1][0], wsc + cc * 16, &y[cc * 8], mx, tail_valid - half * 64 - cc * 16);
-                        convert8_tail(&sr[cc & 1][8], wsc + cc * 16 + 8, &y[cc * 8 + 4], mx, tail_valid - half * 64 - cc * 16 - 8);
-                    } else {
-                        convert8(&sr[cc & 1][0], wsc + cc * 16, &y[cc * 8], mx);
-                        convert8(&sr[cc & 1][8], wsc + cc * 16 + 8, &y[cc * 8 + 4], mx);
-                    }
+                    convert8(&sr[cc & 1][0], wsc + cc * 16, &y[cc * 8], mx);
+                    convert8(&sr[cc & 1][8], wsc + cc * 16 + 8, &y[cc * 8 + 4], mx);
                 }
+                if (nt == 1 && tail_valid < kKT) mask_tail(y, mx);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_SEMPTY));
@@ -414,12 +412,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                     for (int h = 0; h < 2; ++h) {
                         const int c = cc * 2 + h;        // 16-byte chunk of P / 8 columns
                         exp8(&y[c * 4], vsc + c * 8, nm2, prow + ((c ^ (r & 7)) << 4));
-                        if (j + 2 == nt && tail_valid < kKT)
-                            convert8_tail(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx, tail_valid - half * 64 - c * 8);
-                        else
-                            convert8(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx);
+                        convert8(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx);
                     }
                 }
+                if (j + 2 == nt && tail_valid < kKT) mask_tail(y, mx);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_SEMPTY + (st ^ 1)));
