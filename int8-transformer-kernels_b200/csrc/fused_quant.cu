@@ -42,7 +42,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
 }
 
-// One CTA per row; the row lives in registers between the three reductions.
+// Rows wider than 2048: one CTA per row; the row lives in registers between the three reductions.
 __global__ void __launch_bounds__(kLnThreads)
 layernorm_quantize_kernel(const __half* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scales,
                           int d, float eps) {
@@ -115,6 +115,113 @@ layernorm_quantize_kernel(const __half* __restrict__ x, int8_t* __restrict__ q, 
     }
 }
 
+// Four codes from four fp32 values with a row-wide reciprocal: x * rcp is within 1.6e-5 of the
+// exact quotient and the IEEE quotient within 0.8e-5, so only products within 1e-4 of a rounding
+// tie are redone with the IEEE division; rounding is the addition of 1.5 * 2^23 (code = low byte).
+__device__ __forceinline__ uint32_t quant4_rcp(float x0, float x1, float x2, float x3, float scale, float rcp) {
+    const f32x2 rcp2 = pack2(rcp, rcp);
+    const f32x2 magic2 = pack2(12582912.f, 12582912.f), nmagic2 = pack2(-12582912.f, -12582912.f);
+    const f32x2 mone2 = pack2(-1.f, -1.f);
+    const f32x2 qa = mul2(pack2(x0, x1), rcp2), qb = mul2(pack2(x2, x3), rcp2);
+    const f32x2 ra = add2(qa, magic2), rb = add2(qb, magic2);
+    const float2 da = unpack2(fma2(add2(ra, nmagic2), mone2, qa));
+    const float2 db = unpack2(fma2(add2(rb, nmagic2), mone2, qb));
+    const float2 fa = unpack2(ra), fb = unpack2(rb);
+    uint32_t w = prmt(prmt(__float_as_uint(fa.x), __float_as_uint(fa.y), 0x0040u),
+                      prmt(__float_as_uint(fb.x), __float_as_uint(fb.y), 0x0040u), 0x5410u);
+    if (fmaxf(fmaxf(fabsf(da.x), fabsf(da.y)), fmaxf(fabsf(db.x), fabsf(db.y))) > 0.4999f)
+        w = (uint32_t)(quant_exact(x0, scale) & 0xff) | ((uint32_t)(quant_exact(x1, scale) & 0xff) << 8) |
+            ((uint32_t)(quant_exact(x2, scale) & 0xff) << 16) | ((uint32_t)(quant_exact(x3, scale) & 0xff) << 24);
+    return w;
+}
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// One warp per row, the row in registers (NV 16-byte vectors per lane): d <= 256 * NV.  No
+// shared memory and no block-wide barrier; a block of eight warps walks rows grid-stride.
+template <int NV>
+__global__ void __launch_bounds__(256, (NV <= 4) ? 4 : 2)
+layernorm_quantize_warp_kernel(const __half* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scales,
+                               long long rows, int d, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int nvec = d / 8;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const float inv_d = 1.0f / (float)d;
+    for (long long row = warp; row < rows; row += nwarps) {
+        const __half* xr = x + row * d;
+        float v[NV][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int vi = lane + j * 32;
+            uint4 t = make_uint4(0u, 0u, 0u, 0u);
+            if (vi < nvec) t = *reinterpret_cast<const uint4*>(xr + vi * 8);
+            const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                v[j][2 * i] = f.x;
+                v[j][2 * i + 1] = f.y;
+                sum += f.x + f.y;
+            }
+        }
+        const float mean = warp_sum_f(sum) * inv_d;
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            if (lane + j * 32 < nvec) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float c = v[j][i] - mean;
+                    ss = fmaf(c, c, ss);
+                }
+            }
+        }
+        const float rstd = rsqrtf(warp_sum_f(ss) * inv_d + eps);
+        // normalised value as torch stores it (fp16); its maximum is exact in fp16
+        const f32x2 nmean2 = pack2(-mean, -mean), rstd2 = pack2(rstd, rstd);
+        __half2 hmax = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            if (lane + j * 32 < nvec) {
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const float2 n = unpack2(mul2(add2(pack2(v[j][i], v[j][i + 1]), nmean2), rstd2));
+                    const __half2 hy = __floats2half2_rn(n.x, n.y);
+                    hmax = __hmax2(hmax, __habs2(hy));
+                    const float2 back = __half22float2(hy);
+                    v[j][i] = back.x;
+                    v[j][i + 1] = back.y;
+                }
+            }
+        }
+        const float2 hm = __half22float2(hmax);
+        const float amax = warp_max_f(fmaxf(hm.x, hm.y));
+        const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+        const float rcp = __frcp_rn(scale);
+        if (lane == 0) scales[row] = scale;
+        int8_t* qr = q + row * d;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int vi = lane + j * 32;
+            if (vi < nvec)
+                *reinterpret_cast<uint2*>(qr + vi * 8) =
+                    make_uint2(quant4_rcp(v[j][0], v[j][1], v[j][2], v[j][3], scale, rcp),
+                               quant4_rcp(v[j][4], v[j][5], v[j][6], v[j][7], scale, rcp));
+        }
+    }
+}
+
 // One warp per (tensor, b*h) row of D fp16 values (D a multiple of 32, <= 256).
 __global__ void __launch_bounds__(128)
 kv_append_quantize_kernel(const __half* __restrict__ k_new, const __half* __restrict__ v_new,
@@ -163,8 +270,21 @@ extern "C" int i8tk_layernorm_quantize_f16(const void* x_f16, int8_t* q, float* 
     I8TK_REQUIRE(rows < (1ll << 31), I8TK_ERR_UNSUPPORTED, "too many rows");
     I8TK_REQUIRE(aligned_to(x_f16, 16) && aligned_to(q, 8), I8TK_ERR_ALIGNMENT,
                  "x must be 16-byte and q 8-byte aligned");
-    layernorm_quantize_kernel<<<(unsigned)rows, kLnThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(x_f16), q, scales, d_model, eps);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half* xh = static_cast<const __half*>(x_f16);
+    const int nvec = d_model / 8;
+    long long blocks = (rows + 7) / 8;                    // eight warps (rows) per block
+    if (blocks > 148ll * 16) blocks = 148ll * 16;
+    if (nvec <= 32)
+        layernorm_quantize_warp_kernel<1><<<(unsigned)blocks, 256, 0, st>>>(xh, q, scales, rows, d_model, eps);
+    else if (nvec <= 64)
+        layernorm_quantize_warp_kernel<2><<<(unsigned)blocks, 256, 0, st>>>(xh, q, scales, rows, d_model, eps);
+    else if (nvec <= 128)
+        layernorm_quantize_warp_kernel<4><<<(unsigned)blocks, 256, 0, st>>>(xh, q, scales, rows, d_model, eps);
+    else if (nvec <= 256)
+        layernorm_quantize_warp_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(xh, q, scales, rows, d_model, eps);
+    else                                                  // wider rows: one block per row
+        layernorm_quantize_kernel<<<(unsigned)rows, kLnThreads, 0, st>>>(xh, q, scales, d_model, eps);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }
