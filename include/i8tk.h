@@ -85,7 +85,23 @@ int i8tk_quantize_per_token_f16(const void* x_f16, int8_t* q, float* scales,
  * fp16, quantised per token and written into the INT8 cache K / V [BH, S_cap, head_dim] at
  * position pos_per_row[bh] (device int32[BH]) or, when pos_per_row is NULL, at `pos` for every
  * row; their scales go to sK / sV [BH, S_cap].  Rows whose position is outside [0, S_cap) are
- * skipped.  head_dim a multiple of 32, at most 256. */
+ * skipped.  head_dim a multiple of 32, at most 256.
+ *
+ * i8tk_quantize_qkv_heads_f16: the fused QKV projection qkv [batch*seq_len, 3*heads*head_dim]
+ * fp16 (q heads, then k heads, then v heads in each row) quantised per token and per head
+ * straight into the head-major layout the attention kernels take: out int8
+ * [3][batch][heads][seq_len][head_dim], scales fp32 [3][batch][heads][seq_len] -- the split,
+ * view, transpose and contiguous copies of bench/bench_block.py:96-101 disappear into the
+ * quantiser.  Codes and scales are bit-identical to i8tk_quantize_per_token_f16 on the
+ * transposed tensors.  head_dim 64 or 128.
+ *
+ * i8tk_dequantize_per_token_f16: out = fp16(q * scales[row] (+ residual)), the step after the
+ * INT8 MLP (bench/bench_block.py:113: .float() * scale -> .half(), then the residual add);
+ * residual_f16 may be NULL.  cols a multiple of 16. */
+int i8tk_quantize_qkv_heads_f16(const void* qkv_f16, int8_t* out, float* scales,
+                                int batch, int seq_len, int heads, int head_dim, i8tk_stream_t stream);
+int i8tk_dequantize_per_token_f16(const int8_t* q, const float* scales, const void* residual_f16,
+                                  void* out_f16, int64_t rows, int cols, i8tk_stream_t stream);
 int i8tk_layernorm_quantize_f16(const void* x_f16, int8_t* q, float* scales,
                                 int64_t rows, int d_model, float eps, i8tk_stream_t stream);
 int i8tk_kv_append_quantize_f16(const void* k_new_f16, const void* v_new_f16,

@@ -63,22 +63,25 @@ class Int8Block:
         B, S, d = h.shape
         xi, sx = self.ext.layernorm_quantize(h) if fused_ln else self.ext.quantize_per_token(h)
         out_i8, out_sc = self.ext.int8_mlp_forward(xi, self.W1i, self.W2i, sx.reshape(-1), self.sW1, self.sW2)
-        return (out_i8.view(B * S, d).float() * out_sc.unsqueeze(-1)).view(B, S, d).to(h.dtype)
+        # dequantise and add the residual stream in one pass
+        return self.ext.dequantize_per_token(out_i8, out_sc, h if fused_ln else None)
 
     def _tail(self, x, a, use_int8):
         h = x + a @ self.Wo
-        return h + (self._mlp_int8(h, fused_ln=True) if use_int8 else self._mlp_fp16(self._ln(h)))
+        if use_int8:
+            return self._mlp_int8(h, fused_ln=True)        # LayerNorm, MLP, dequantise + residual
+        return h + self._mlp_fp16(self._ln(h))
 
     # ---- prefill ----
     def forward_prefill(self, x, use_int8):
         B, S, _ = x.shape
-        q, k, v = self._project_qkv(self._ln(x))
         if use_int8:
-            qi, sq = self.ext.quantize_per_token(q)
-            ki, sk = self.ext.quantize_per_token(k)
-            vi, sv = self.ext.quantize_per_token(v)
-            a = self.ext.int8_attention_forward(qi, ki, vi, sq.reshape(-1), sk.reshape(-1), sv.reshape(-1))
+            # projection -> int8 heads in one pass: no split / transpose / contiguous copies
+            qkv_i, qkv_s = self.ext.quantize_qkv_heads(self._ln(x) @ self.Wqkv, self.H)
+            a = self.ext.int8_attention_forward(qkv_i[0], qkv_i[1], qkv_i[2], qkv_s[0].reshape(-1),
+                                                qkv_s[1].reshape(-1), qkv_s[2].reshape(-1))
         else:
+            q, k, v = self._project_qkv(self._ln(x))
             a = F.scaled_dot_product_attention(q, k, v)
         return self._tail(x, a.transpose(1, 2).contiguous().view(B, S, self.d), use_int8)
 

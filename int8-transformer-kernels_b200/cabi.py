@@ -37,6 +37,8 @@ SIGNATURES = {
     "i8tk_selftest_bounded_wait": (_i, [_vp, _i, _vp]),
     "i8tk_quantize_per_token_f32": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "i8tk_quantize_per_token_f16": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
+    "i8tk_quantize_qkv_heads_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "i8tk_dequantize_per_token_f16": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _vp]),
     "i8tk_layernorm_quantize_f16": (_i, [_vp, _vp, _vp, _i64, _i, _f, _vp]),
     "i8tk_kv_append_quantize_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "i8tk_quantize_fp16_to_int8": (_i, [_vp, _vp, _vp, _i64, _vp]),

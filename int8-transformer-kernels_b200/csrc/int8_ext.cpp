@@ -260,6 +260,53 @@ std::tuple<torch::Tensor, torch::Tensor> layernorm_quantize_torch(torch::Tensor 
     return {q, s};
 }
 
+// qkv fp16 [B, S, 3*H*Dh] -> (int8 [3,B,H,S,Dh], fp32 [3,B,H,S]): index 0/1/2 = q/k/v.
+std::tuple<torch::Tensor, torch::Tensor> quantize_qkv_heads_torch(torch::Tensor qkv, int64_t heads) {
+    TORCH_CHECK(qkv.device().is_cuda() && qkv.dtype() == torch::kFloat16 && qkv.dim() == 3,
+                "qkv must be a float16 CUDA tensor (batch, seq, 3*heads*head_dim)");
+    auto x = qkv.contiguous();
+    const int64_t B = x.size(0), S = x.size(1);
+    TORCH_CHECK(heads > 0 && x.size(2) % (3 * heads) == 0, "last dimension must be 3*heads*head_dim");
+    const int64_t Dh = x.size(2) / (3 * heads);
+    TORCH_CHECK(Dh == 64 || Dh == 128, "head_dim must be 64 or 128");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto q = torch::empty({3, B, heads, S, Dh}, torch::TensorOptions().dtype(torch::kInt8).device(x.device()));
+    auto s = torch::empty({3, B, heads, S}, torch::TensorOptions().dtype(torch::kFloat32).device(x.device()));
+    if (B * S == 0) return {q, s};
+    check_status(i8tk_quantize_qkv_heads_f16(x.data_ptr(), q.data_ptr<int8_t>(), s.data_ptr<float>(),
+                                             static_cast<int>(B), static_cast<int>(S), static_cast<int>(heads),
+                                             static_cast<int>(Dh), current_stream()),
+                 "quantize_qkv_heads");
+    return {q, s};
+}
+
+// fp16(q * scales[row]) (+ residual): q int8 [..., cols], scales fp32 with one value per row.
+torch::Tensor dequantize_per_token_torch(torch::Tensor q, torch::Tensor scales, c10::optional<torch::Tensor> residual) {
+    TORCH_CHECK(q.device().is_cuda() && q.dtype() == torch::kInt8 && q.dim() >= 1 && q.is_contiguous(),
+                "q must be a contiguous int8 CUDA tensor");
+    const int64_t cols = q.size(-1);
+    TORCH_CHECK(cols >= 16 && cols % 16 == 0, "last dimension must be a positive multiple of 16");
+    const int64_t rows = q.numel() / cols;
+    TORCH_CHECK(scales.dtype() == torch::kFloat32 && scales.numel() == rows && scales.device() == q.device(),
+                "scales must be float32 with one value per row");
+    auto sc = scales.contiguous();
+    c10::cuda::CUDAGuard guard(q.device());
+    auto out = torch::empty(q.sizes(), torch::TensorOptions().dtype(torch::kFloat16).device(q.device()));
+    const void* res = nullptr;
+    torch::Tensor r;
+    if (residual.has_value()) {
+        r = residual->contiguous();
+        TORCH_CHECK(r.dtype() == torch::kFloat16 && r.sizes() == q.sizes() && r.device() == q.device(),
+                    "residual must be float16 of q's shape");
+        res = r.data_ptr();
+    }
+    if (rows == 0) return out;
+    check_status(i8tk_dequantize_per_token_f16(q.data_ptr<int8_t>(), sc.data_ptr<float>(), res, out.data_ptr(), rows,
+                                               static_cast<int>(cols), current_stream()),
+                 "dequantize_per_token");
+    return out;
+}
+
 // In place: K, V int8 [B,H,S_cap,D] and sK, sV fp32 (numel B*H*S_cap) receive the new token at `pos`.
 void kv_append_quantize_torch(torch::Tensor k_new, torch::Tensor v_new, torch::Tensor K, torch::Tensor V,
                               torch::Tensor sK, torch::Tensor sV, int64_t pos) {
@@ -302,6 +349,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "Per-token symmetric INT8 quantisation — returns (int8, fp32 scales)");
     m.def("layernorm_quantize", &layernorm_quantize_torch, pybind11::arg("t"), pybind11::arg("eps") = 1e-5,
           "LayerNorm (no affine) + per-token INT8 quantisation of the fp16 result — returns (int8, fp32 scales)");
+    m.def("quantize_qkv_heads", &quantize_qkv_heads_torch,
+          "Fused QKV projection -> per-token INT8 in head-major layout — returns (int8 [3,B,H,S,Dh], fp32 [3,B,H,S])");
+    m.def("dequantize_per_token", &dequantize_per_token_torch, pybind11::arg("q"), pybind11::arg("scales"),
+          pybind11::arg("residual") = c10::nullopt, "fp16(q * scale[row]) (+ residual) — returns FP16");
     m.def("kv_append_quantize", &kv_append_quantize_torch,
           "Quantise the new token's K and V rows per token and write them into the INT8 cache at pos (in place)");
     register_mlp_ops(m);

@@ -129,13 +129,33 @@ __device__ __forceinline__ int row_owner_lane(int r) {
     return 0;
 }
 
+// Where row r of the input goes in the output.  RowIdentity: to row r.  RowQkvHeads: the input
+// is a fused projection [B*S, 3*H*Dh] read as rows of Dh elements, r = ((b*S + s)*3 + which)*H + h,
+// and the output is [3][B][H][S] rows: the head-major layout the attention kernels take, so the
+// split, view, transpose and contiguous copies of the eager path disappear into the quantiser.
+struct RowIdentity {
+    __device__ long long operator()(long long r) const { return r; }
+};
+struct RowQkvHeads {
+    int B, S, H;
+    __device__ long long operator()(long long r) const {
+        const int h = (int)(r % H);
+        const long long t3 = r / H;
+        const int which = (int)(t3 % 3);
+        const long long t = t3 / 3;
+        const int s = (int)(t % S);
+        const long long b = t / S;
+        return (((long long)which * B + b) * H + h) * S + s;
+    }
+};
+
 // Rows of `cols` elements, cols a multiple of Vec16<T>::N.  A row is handled by a
 // group of G lanes (G a power of two <= 32); lane i of the group owns vectors
 // i, i+G, ... (at most NV of them).  Each group keeps R rows in flight.
-template <typename T, int G, int NV, int R>
+template <typename T, int G, int NV, int R, typename RowMap>
 __global__ void __launch_bounds__(256, 4)
 quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
-                         float* __restrict__ scales, long long rows, int cols) {
+                         float* __restrict__ scales, long long rows, int cols, RowMap out_row) {
     constexpr int N = Vec16<T>::N;
     const int nvec = cols / N;
     constexpr int GPW = 32 / G;                     // groups per warp
@@ -151,7 +171,6 @@ quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
         const long long r0 = w0 + (long long)group_in_warp * R;
         const int nrows = (int)(rows - r0 < R ? (rows - r0 > 0 ? rows - r0 : 0) : R);   // rows of this group that exist
         const T* xg = x + r0 * cols + lane_in_group * N;
-        int8_t* qg = q + r0 * cols + lane_in_group * N;
         uint4 raw[R][NV];
         float amax[R];
 #pragma unroll
@@ -177,7 +196,7 @@ quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
             const float am = reduce_rows<G, R>(amax, lane_in_group, &rsel);
             const float scale = __fdiv_rn(fmaxf(am, 1e-8f), 127.0f);
             const float rcp = __frcp_rn(scale);
-            if (lane_in_group == row_owner_lane<G, R>(rsel) && rsel < nrows) scales[r0 + rsel] = scale;
+            if (lane_in_group == row_owner_lane<G, R>(rsel) && rsel < nrows) scales[out_row(r0 + rsel)] = scale;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 scale_r[r] = __shfl_sync(0xffffffffu, scale, group_lane0 + row_owner_lane<G, R>(r));
@@ -191,18 +210,19 @@ quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
                     amax[r] = fmaxf(amax[r], __shfl_xor_sync(0xffffffffu, amax[r], o));
                 scale_r[r] = __fdiv_rn(fmaxf(amax[r], 1e-8f), 127.0f);
                 rcp_r[r] = __frcp_rn(scale_r[r]);
-                if (lane_in_group == 0 && r < nrows) scales[r0 + r] = scale_r[r];
+                if (lane_in_group == 0 && r < nrows) scales[out_row(r0 + r)] = scale_r[r];
             }
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             if (r >= nrows) continue;
             const float scale = scale_r[r], rcp = rcp_r[r];
+            int8_t* qrow = q + out_row(r0 + r) * cols + lane_in_group * N;
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 const int vi = lane_in_group + j * G;
                 if (vi >= nvec) continue;
-                int8_t* dst = qg + r * cols + j * (G * N);
+                int8_t* dst = qrow + j * (G * N);
                 float v[N];
                 Vec16<T>::to_float(raw[r][j], v);
                 if constexpr (N == 4) {
@@ -240,15 +260,16 @@ quantize_rows_generic_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
     }
 }
 
-template <typename T, int G, int NV, int R>
-int launch_vec(const T* x, int8_t* q, float* scales, long long rows, int cols, cudaStream_t st) {
+template <typename T, int G, int NV, int R, typename RowMap = RowIdentity>
+int launch_vec(const T* x, int8_t* q, float* scales, long long rows, int cols, cudaStream_t st,
+               RowMap out_row = RowMap{}) {
     const long long groups = (rows + R - 1) / R;
     const long long threads = groups * G;
     long long blocks = (threads + 255) / 256;
     const long long cap = 148ll * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    quantize_rows_vec_kernel<T, G, NV, R><<<(int)blocks, 256, 0, st>>>(x, q, scales, rows, cols);
+    quantize_rows_vec_kernel<T, G, NV, R, RowMap><<<(int)blocks, 256, 0, st>>>(x, q, scales, rows, cols, out_row);
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }
@@ -311,6 +332,40 @@ __global__ void dequant_tensor_kernel(const int8_t* __restrict__ q, __half* __re
         out[i] = __float2half((float)q[i] * scale);
 }
 
+// out[r][c] = fp16(q[r][c] * scale[r]) (+ residual[r][c], added in fp32): the inverse step after the
+// INT8 MLP, which the eager path spells as .float() * scale -> .half() (+ the residual add).
+__global__ void __launch_bounds__(256)
+dequant_rows_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
+                    const __half* __restrict__ residual, __half* __restrict__ out, long long vecs, int vecs_per_row) {
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < vecs;
+         v += (long long)gridDim.x * blockDim.x) {
+        const float sc = scales[v / vecs_per_row];
+        const uint4 w = *reinterpret_cast<const uint4*>(q + v * 16);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
+        if (residual) {
+            r0 = *reinterpret_cast<const uint4*>(residual + v * 16);
+            r1 = *reinterpret_cast<const uint4*>(residual + v * 16 + 8);
+        }
+        const __half2* rh0 = reinterpret_cast<const __half2*>(&r0);
+        const __half2* rh1 = reinterpret_cast<const __half2*>(&r1);
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int b0 = (int)(int8_t)(ww[k] & 0xff), b1 = (int)(int8_t)((ww[k] >> 8) & 0xff);
+            const int b2 = (int)(int8_t)((ww[k] >> 16) & 0xff), b3 = (int)(int8_t)(ww[k] >> 24);
+            const float2 ra = __half22float2(k < 2 ? rh0[2 * k] : rh1[2 * k - 4]);
+            const float2 rb = __half22float2(k < 2 ? rh0[2 * k + 1] : rh1[2 * k - 3]);
+            const __half2 ha = __floats2half2_rn(fmaf((float)b0, sc, ra.x), fmaf((float)b1, sc, ra.y));
+            const __half2 hb = __floats2half2_rn(fmaf((float)b2, sc, rb.x), fmaf((float)b3, sc, rb.y));
+            o[2 * k] = *reinterpret_cast<const uint32_t*>(&ha);
+            o[2 * k + 1] = *reinterpret_cast<const uint32_t*>(&hb);
+        }
+        *reinterpret_cast<uint4*>(out + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(out + v * 16 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 int grid_for(long long n) {
     long long b = (n + 255) / 256;
     if (b > 148ll * 16) b = 148ll * 16;
@@ -322,6 +377,39 @@ int grid_for(long long n) {
 }  // namespace i8tk
 
 using namespace i8tk;
+
+extern "C" int i8tk_quantize_qkv_heads_f16(const void* qkv_f16, int8_t* out, float* scales, int batch, int seq_len,
+                                          int heads, int head_dim, i8tk_stream_t stream) {
+    I8TK_REQUIRE(qkv_f16 && out && scales, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(batch > 0 && seq_len > 0 && heads > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
+    I8TK_REQUIRE(head_dim == 64 || head_dim == 128, I8TK_ERR_UNSUPPORTED, "head_dim must be 64 or 128 (got %d)",
+                 head_dim);
+    I8TK_REQUIRE(aligned_to(qkv_f16, 16) && aligned_to(out, 8), I8TK_ERR_ALIGNMENT,
+                 "qkv must be 16-byte and out 8-byte aligned");
+    const long long rows = (long long)batch * seq_len * 3 * heads;
+    const RowQkvHeads map{batch, seq_len, heads};
+    const __half* x = static_cast<const __half*>(qkv_f16);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (head_dim == 64) return launch_vec<__half, 8, 1, 4, RowQkvHeads>(x, out, scales, rows, 64, st, map);
+    return launch_vec<__half, 16, 1, 4, RowQkvHeads>(x, out, scales, rows, 128, st, map);
+}
+
+extern "C" int i8tk_dequantize_per_token_f16(const int8_t* q, const float* scales, const void* residual_f16,
+                                             void* out_f16, int64_t rows, int cols, i8tk_stream_t stream) {
+    I8TK_REQUIRE(rows >= 0 && cols >= 16 && cols % 16 == 0, I8TK_ERR_INVALID_ARGUMENT,
+                 "rows must be >= 0 and cols a positive multiple of 16");
+    if (rows == 0) return I8TK_OK;
+    I8TK_REQUIRE(q && scales && out_f16, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(aligned_to(q, 16) && aligned_to(out_f16, 16) && (!residual_f16 || aligned_to(residual_f16, 16)),
+                 I8TK_ERR_ALIGNMENT, "q, out and residual must be 16-byte aligned");
+    const long long vecs = rows * (cols / 16);
+    long long blocks = (vecs + 255) / 256;
+    if (blocks > 148ll * 16) blocks = 148ll * 16;
+    dequant_rows_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        q, scales, static_cast<const __half*>(residual_f16), static_cast<__half*>(out_f16), vecs, cols / 16);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
 
 extern "C" int i8tk_quantize_per_token_f32(const float* x, int8_t* q, float* scales, int64_t rows,
                                            int cols, i8tk_stream_t stream) {

@@ -103,3 +103,34 @@ def test_decode_after_append_equals_decode_on_the_longer_cache():
     e.kv_append_quantize(Kf[:, :, S].contiguous(), Vf[:, :, S].contiguous(), Ki, Vi, sK, sV, S)
     got = e.int8_decode_attention_forward(Qi, Ki, Vi, sQ.reshape(-1), sK, sV)
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("B,S,H,Dh", [(2, 37, 4, 64), (1, 130, 3, 128), (3, 1, 2, 64)])
+def test_quantize_qkv_heads_is_the_quantiser_on_the_transposed_heads(B, S, H, Dh):
+    torch.manual_seed(S)
+    e = ext()
+    d = H * Dh
+    qkv = torch.randn(B, S, 3 * d, device="cuda", dtype=torch.float16) * 1.7
+    qi, sc = e.quantize_qkv_heads(qkv, H)
+    assert qi.shape == (3, B, H, S, Dh) and sc.shape == (3, B, H, S)
+    for w, part in enumerate(qkv.split(d, dim=-1)):
+        heads = part.view(B, S, H, Dh).transpose(1, 2).contiguous()
+        q_ref, s_ref = quant.quantize_per_token(heads.cpu().numpy())
+        assert np.array_equal(qi[w].cpu().numpy(), q_ref)
+        assert np.array_equal(sc[w].cpu().numpy().view(np.uint32), s_ref.view(np.uint32))
+
+
+def test_dequantize_per_token_with_and_without_residual():
+    torch.manual_seed(2)
+    e = ext()
+    q = torch.randint(-128, 128, (3, 50, 256), dtype=torch.int8, device="cuda")
+    s = torch.rand(3, 50, device="cuda") * 0.1 + 1e-3
+    got = e.dequantize_per_token(q, s)
+    want = (q.float() * s.unsqueeze(-1)).half()          # the eager spelling of the reference's block
+    assert torch.equal(got, want)
+    r = torch.randn(3, 50, 256, device="cuda", dtype=torch.float16)
+    got = e.dequantize_per_token(q, s, r)
+    exact = q.double() * s.double().unsqueeze(-1) + r.double()
+    assert torch.equal(got, exact.half())               # one rounding of the exact sum (fma in fp32 is exact enough here)
+    with pytest.raises(RuntimeError):
+        e.dequantize_per_token(q[..., :8].contiguous(), s)
