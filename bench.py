@@ -408,6 +408,9 @@ def main():
         rows_bytes = plan_warps * 2 * 4 * (D + 4) * 4
         line["roofline"]["traffic"] = int(1.0627 * step_bytes) + rows_bytes
         line["roofline"]["traffic_source"] = "scaled from an ncu capture of a 201 MB case (linear in positions)"
+        line["roofline"]["timing_note"] = ("events recorded around the scan kernel keep the merge kernel from "
+                                           "overlapping its tail (programmatic dependent launch), so us_per_launch "
+                                           "can exceed ms_per_step, which times scan + overlapped merge")
 
     if rank == 0 and world == 1:
         gbs, per_iter, threads, desc = cpu_reference_rate(seconds_budget=10.0)
