@@ -185,6 +185,10 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // Launched programmatically behind whatever precedes it in the stream: the wait keeps plain
+    // stream order (nothing is read before that work has completed), only the launch itself and
+    // this CTA's set-up may overlap its tail.
+    pdl_wait();
     pdl_launch_dependents();                    // the merge kernel may be scheduled as SMs drain
     const long long f0 = (long long)blockIdx.x * plan.tpc;
     if (f0 >= plan.total) return;
@@ -686,9 +690,8 @@ int launch_partial(const int8_t* Q, const int8_t* K, const int8_t* V, const floa
     }
     const float score_scale_log2 = kLog2e / sqrtf((float)D);
     if (g_probe_start) I8TK_CUDA(cudaEventRecord(g_probe_start, stream));
-    decode_partial_kernel<D, SCALES_BULK, PAGED><<<p.nctas, kThreads, T::SMEM_BYTES, stream>>>(
-        Q, K, V, sQ, sK, sV, rows, S, p, score_scale_log2, status, pg);
-    I8TK_CUDA(cudaGetLastError());
+    I8TK_CUDA(launch_after(decode_partial_kernel<D, SCALES_BULK, PAGED>, dim3(p.nctas), dim3(kThreads),
+                           T::SMEM_BYTES, stream, Q, K, V, sQ, sK, sV, rows, S, p, score_scale_log2, status, pg));
     if (g_probe_stop) I8TK_CUDA(cudaEventRecord(g_probe_stop, stream));
     return I8TK_OK;
 }

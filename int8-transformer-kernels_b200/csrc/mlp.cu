@@ -600,6 +600,7 @@ requant_tensor_kernel(const __half* __restrict__ H, const float* __restrict__ ab
 // Workspace presets of one forward: `words16` 16-byte words of all ones, one float of zero.
 __global__ void __launch_bounds__(256)
 preset_kernel(uint4* __restrict__ ones, size_t words16, float* __restrict__ zero) {
+    pdl_wait();                 // plain stream order towards whatever precedes the call
     pdl_launch_dependents();
     const uint4 v = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words16; i += (size_t)gridDim.x * blockDim.x)
@@ -867,8 +868,8 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
         int blocks = (int)((words + 255) / 256);
         if (blocks > 296) blocks = 296;
         if (blocks < 1) blocks = 1;
-        preset_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<uint4*>(w.parts1), words, w.tensor_absmax);
-        I8TK_CUDA(cudaGetLastError());
+        I8TK_CUDA(launch_after(preset_kernel, dim3(blocks), dim3(256), 0, st, reinterpret_cast<uint4*>(w.parts1),
+                               words, w.tensor_absmax));
     }
 
     // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token inside the
