@@ -152,6 +152,8 @@ template <int NV>
 __global__ void __launch_bounds__(256, (NV <= 4) ? 4 : 2)
 layernorm_quantize_warp_kernel(const __half* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scales,
                                long long rows, int d, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int nvec = d / 8;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -276,13 +278,17 @@ extern "C" int i8tk_layernorm_quantize_f16(const void* x_f16, int8_t* q, float* 
     long long blocks = (rows + 7) / 8;                    // eight warps (rows) per block
     if (blocks > 148ll * 16) blocks = 148ll * 16;
     if (nvec <= 32)
-        layernorm_quantize_warp_kernel<1><<<(unsigned)blocks, 256, 0, st>>>(xh, q, scales, rows, d_model, eps);
+        I8TK_CUDA(launch_after(layernorm_quantize_warp_kernel<1>, dim3((unsigned)blocks), dim3(256), 0, st, xh, q, scales,
+                               (long long)rows, d_model, eps));
     else if (nvec <= 64)
-        layernorm_quantize_warp_kernel<2><<<(unsigned)blocks, 256, 0, st>>>(xh, q, scales, rows, d_model, eps);
+        I8TK_CUDA(launch_after(layernorm_quantize_warp_kernel<2>, dim3((unsigned)blocks), dim3(256), 0, st, xh, q, scales,
+                               (long long)rows, d_model, eps));
     else if (nvec <= 128)
-        layernorm_quantize_warp_kernel<4><<<(unsigned)blocks, 256, 0, st>>>(xh, q, scales, rows, d_model, eps);
+        I8TK_CUDA(launch_after(layernorm_quantize_warp_kernel<4>, dim3((unsigned)blocks), dim3(256), 0, st, xh, q, scales,
+                               (long long)rows, d_model, eps));
     else if (nvec <= 256)
-        layernorm_quantize_warp_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(xh, q, scales, rows, d_model, eps);
+        I8TK_CUDA(launch_after(layernorm_quantize_warp_kernel<8>, dim3((unsigned)blocks), dim3(256), 0, st, xh, q, scales,
+                               (long long)rows, d_model, eps));
     else                                                  // wider rows: one block per row
         layernorm_quantize_kernel<<<(unsigned)rows, kLnThreads, 0, st>>>(xh, q, scales, d_model, eps);
     I8TK_CUDA(cudaGetLastError());

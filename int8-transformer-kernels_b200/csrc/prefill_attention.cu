@@ -131,6 +131,8 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     const uint32_t tmem_slot = bars + Cfg::NUM_BARS * 8;
     volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(base + Cfg::OFF_BARS + Cfg::NUM_BARS * 8);
 
+    pdl_wait();                 // stream order towards the producers of Q, K, V and the scales
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int bh = blockIdx.y;
@@ -539,9 +541,8 @@ int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* ou
     }
     const float score_scale_log2 = 1.4426950408889634f / sqrtf((float)D);
     dim3 grid((S + kQT - 1) / kQT, BH);
-    prefill_attention_kernel<D><<<grid, kPrefillThreads, Cfg::SMEM_BYTES, st>>>(tmQ, tmK, tmV, sQ, sK, sV, out, S,
-                                                                              score_scale_log2, status);
-    I8TK_CUDA(cudaGetLastError());
+    I8TK_CUDA(launch_after(prefill_attention_kernel<D>, grid, dim3(kPrefillThreads), Cfg::SMEM_BYTES, st, tmQ, tmK, tmV,
+                           sQ, sK, sV, out, S, score_scale_log2, status));
     return I8TK_OK;
 }
 

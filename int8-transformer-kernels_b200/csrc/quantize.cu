@@ -157,6 +157,8 @@ __global__ void __launch_bounds__(256, 4)
 quantize_rows_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
                          float* __restrict__ scales, long long rows, int cols, RowMap out_row) {
     constexpr int N = Vec16<T>::N;
+    pdl_wait();                                     // stream order towards the producer of x ...
+    pdl_launch_dependents();                        // ... while the consumer of q may set itself up
     const int nvec = cols / N;
     constexpr int GPW = 32 / G;                     // groups per warp
     const int lane_in_group = threadIdx.x % G;
@@ -269,8 +271,8 @@ int launch_vec(const T* x, int8_t* q, float* scales, long long rows, int cols, c
     const long long cap = 148ll * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    quantize_rows_vec_kernel<T, G, NV, R, RowMap><<<(int)blocks, 256, 0, st>>>(x, q, scales, rows, cols, out_row);
-    I8TK_CUDA(cudaGetLastError());
+    I8TK_CUDA(launch_after(quantize_rows_vec_kernel<T, G, NV, R, RowMap>, dim3((unsigned)blocks), dim3(256), 0, st, x, q,
+                           scales, rows, cols, out_row));
     return I8TK_OK;
 }
 
@@ -337,6 +339,8 @@ __global__ void dequant_tensor_kernel(const int8_t* __restrict__ q, __half* __re
 __global__ void __launch_bounds__(256)
 dequant_rows_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
                     const __half* __restrict__ residual, __half* __restrict__ out, long long vecs, int vecs_per_row) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < vecs;
          v += (long long)gridDim.x * blockDim.x) {
         const float sc = scales[v / vecs_per_row];
@@ -405,9 +409,9 @@ extern "C" int i8tk_dequantize_per_token_f16(const int8_t* q, const float* scale
     const long long vecs = rows * (cols / 16);
     long long blocks = (vecs + 255) / 256;
     if (blocks > 148ll * 16) blocks = 148ll * 16;
-    dequant_rows_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        q, scales, static_cast<const __half*>(residual_f16), static_cast<__half*>(out_f16), vecs, cols / 16);
-    I8TK_CUDA(cudaGetLastError());
+    I8TK_CUDA(launch_after(dequant_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                           q, scales, static_cast<const __half*>(residual_f16), static_cast<__half*>(out_f16), vecs,
+                           cols / 16));
     return I8TK_OK;
 }
 
