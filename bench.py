@@ -454,6 +454,21 @@ def sweep(torch, ext, cabi, world, rank, barrier, dist):
                     "pct_of_8TBps_per_gpu": 100.0 * gbs / world / NOMINAL_HBM_GBS,
                     "scaling": "strong" if strong else "weak",
                     "l2_resident": kv_bytes(b, h, s, d) < 100e6})
+        if name.startswith("cfg0") and world == 1:
+            # launch-bound: the same call captured 20 times into one CUDA graph and replayed
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    ext.int8_decode_attention_forward(*args)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(20):
+                    graph_out = ext.int8_decode_attention_forward(*args)
+            el_g = timed_steps(torch, graph.replay, 20, 3)
+            res[-1]["us_per_step_replayed_from_a_cuda_graph"] = el_g / 20 / 20 * 1e6
+            del graph, graph_out
         del args
         torch.cuda.empty_cache()
 
