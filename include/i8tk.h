@@ -256,10 +256,11 @@ int i8tk_decode_plan(int BH, int S, int head_dim, int* nctas, int* tiles_per_cta
  * into an fp32 accumulator, as in the reference.  Any seq_len >= 1 (a partial
  * last tile of 128 positions is masked; the reference takes a scalar fallback
  * when seq_len is not a multiple of 64).  head_dim 64 or 128: anything else
- * returns I8TK_ERR_UNSUPPORTED.  workspace: i8tk_attention_workspace_bytes() bytes,
- * 256-byte aligned (holds the status word).
+ * returns I8TK_ERR_UNSUPPORTED.  workspace: i8tk_attention_workspace_bytes(...) bytes,
+ * 256-byte aligned (the status word and an fp16 copy of V * sV, made once per call so
+ * that the query tiles of a head do not each convert V again).
  * ---------------------------------------------------------------------- */
-size_t i8tk_attention_workspace_bytes(void);
+size_t i8tk_attention_workspace_bytes(int batch, int heads, int seq_len, int head_dim);
 int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V, void* out_f16,
                            const float* sQ, const float* sK, const float* sV,
                            int batch, int heads, int seq_len, int head_dim,

@@ -56,7 +56,7 @@ SIGNATURES = {
     "i8tk_decode_partial_stride": (_i, [_i]),
     "i8tk_decode_set_probe_events": (_i, [_vp, _vp]),
     "i8tk_decode_plan": (_i, [_i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
-    "i8tk_attention_workspace_bytes": (_sz, []),
+    "i8tk_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "i8tk_attention_forward": (_i, [_vp] * 7 + [_i, _i, _i, _i, _vp, _sz, _vp]),
     "i8tk_mlp_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "i8tk_mlp_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,

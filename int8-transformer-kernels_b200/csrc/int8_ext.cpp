@@ -201,7 +201,8 @@ torch::Tensor int8_attention_forward_torch(torch::Tensor Q, torch::Tensor K, tor
     c10::cuda::CUDAGuard guard(Q.device());
     auto out = torch::empty({batch, heads, seq_len, head_dim},
                             torch::TensorOptions().dtype(torch::kFloat16).device(Q.device()));
-    const size_t wbytes = i8tk_attention_workspace_bytes();
+    const size_t wbytes = i8tk_attention_workspace_bytes(static_cast<int>(batch), static_cast<int>(heads),
+                                                         static_cast<int>(seq_len), static_cast<int>(head_dim));
     auto ws = make_workspace(wbytes, Q.device());
     check_status(i8tk_attention_forward(Q.data_ptr<int8_t>(), K.data_ptr<int8_t>(), V.data_ptr<int8_t>(),
                                         out.data_ptr(), sQ.data_ptr<float>(), sK.data_ptr<float>(),

@@ -10,9 +10,11 @@
 //   128x128 int32 accumulator in tensor memory (two buffers); PV is tcgen05.mma
 //   kind::f16 accumulating the 128xD fp32 output in tensor memory across all KV
 //   tiles.
-// * Q, K and raw V tiles arrive by TMA (swizzled K-major rows); two converter
-//   warps turn each int8 V tile into fp16 in the MN-major swizzled layout the
-//   PV instruction reads (int8 -> fp16 is exact).
+// * A pre-pass dequantises V once per call, V16 = fp16(V * sV), into the workspace: every
+//   128-row query tile of a head reads the same V, so converting it inside the attention
+//   kernel repeated the work S/128 times and took a fifth of its instructions.  Q and K
+//   tiles (int8) and V16 tiles (fp16) arrive by TMA; V16 lands directly in the MN-major
+//   128-byte-swizzled layout the PV instruction reads.
 // * Eight softmax warps, two per TMEM lane quarter, each thread owning 64 KV
 //   positions of one query row.  The scores are read from tensor memory once
 //   (tcgen05.ld), converted without the conversion unit (|q.k| < 2^22, so the
@@ -41,9 +43,7 @@ namespace {
 constexpr int kQT = 128;                 // query rows per CTA
 constexpr int kKT = 128;                 // KV positions per tile
 constexpr int kSoftmaxWarps = 8;         // two per TMEM lane quarter: each thread owns half of a score row
-constexpr int kConvWarp0 = 2 + kSoftmaxWarps;
-constexpr int kConvWarps = 2;            // each converter thread takes 128 / (32 * kConvWarps) rows of a V tile
-constexpr int kPrefillThreads = (kConvWarp0 + kConvWarps) * 32;   // TMA, MMA, 8 softmax, 2 converter warps
+constexpr int kPrefillThreads = (2 + kSoftmaxWarps) * 32;   // TMA, MMA, 8 softmax warps
 constexpr float kLazyStep = 8.0f;        // log2 units the true max may run ahead of the reference max
 
 template <int D>
@@ -54,11 +54,10 @@ struct PrefillCfg {
     static constexpr int SLAB_BYTES = kKT * 128;           // 128 rows of 128 bytes
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + TILE_BYTES;
-    static constexpr int OFF_VRAW = OFF_K + 2 * TILE_BYTES;
-    static constexpr int OFF_V16 = OFF_VRAW + 2 * TILE_BYTES;
+    static constexpr int OFF_V16 = OFF_K + 2 * TILE_BYTES;
     static constexpr int OFF_P = OFF_V16 + 2 * V16_BYTES;
-    static constexpr int OFF_SCALES = OFF_P + 2 * P_BYTES; // 8 warps x 2 tiles x (sK[64] | sV[64]) fp32
-    static constexpr int OFF_XCH = OFF_SCALES + kSoftmaxWarps * 2 * 128 * 4;   // [2][2 halves][128 rows] fp32
+    static constexpr int OFF_SCALES = OFF_P + 2 * P_BYTES; // 8 warps x 2 tiles x sK[64] fp32
+    static constexpr int OFF_XCH = OFF_SCALES + kSoftmaxWarps * 2 * 64 * 4;    // [2][2 halves][128 rows] fp32
     static constexpr int OFF_BARS = OFF_XCH + 2 * 2 * kQT * 4;
     static constexpr int NUM_BARS = 22;
     static constexpr int SMEM_BYTES = 1024 + OFF_BARS + NUM_BARS * 8 + 16;
@@ -70,8 +69,6 @@ enum Bar : int {
     B_QFULL = 0,
     B_KFULL = 1,      // [2]
     B_KEMPTY = 3,     // [2]
-    B_VRFULL = 5,     // [2]
-    B_VREMPTY = 7,    // [2]
     B_SFULL = 9,      // [2]
     B_SEMPTY = 11,    // [2]
     B_PFULL = 13,     // [2]
@@ -80,17 +77,30 @@ enum Bar : int {
     B_PVDONE = 19,    // [2]
 };
 
-// four int8 (biased by XOR 0x80 -> u = v + 128) to four fp16, exactly:
-// prmt builds the halves 0x64uu = 1024 + u, one HSUB2 removes 1024 + 128
-__device__ __forceinline__ void i8x4_to_h2x2(uint32_t raw, uint32_t& lo, uint32_t& hi) {
-    const uint32_t b = raw ^ 0x80808080u;
-    const uint32_t p0 = prmt(b, 0x64646464u, 0x4140u);
-    const uint32_t p1 = prmt(b, 0x64646464u, 0x4342u);
-    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
-    const __half2 h0 = __hsub2(*reinterpret_cast<const __half2*>(&p0), bias);
-    const __half2 h1 = __hsub2(*reinterpret_cast<const __half2*>(&p1), bias);
-    lo = *reinterpret_cast<const uint32_t*>(&h0);
-    hi = *reinterpret_cast<const uint32_t*>(&h1);
+// Pre-pass: V16[row][d] = fp16(V[row][d] * sV[row]) -- one rounding, from the fp32 product.
+// 16 elements per thread; rows of D int8.
+__global__ void __launch_bounds__(256)
+dequant_v_kernel(const int8_t* __restrict__ V, const float* __restrict__ sV, __half* __restrict__ V16,
+                 long long vecs, int vecs_per_row) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < vecs;
+         v += (long long)gridDim.x * blockDim.x) {
+        const float sc = sV[v / vecs_per_row];
+        const uint4 w = *reinterpret_cast<const uint4*>(V + v * 16);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float f0 = (float)(int)(int8_t)(ww[k] & 0xff) * sc, f1 = (float)(int)(int8_t)((ww[k] >> 8) & 0xff) * sc;
+            const float f2 = (float)(int)(int8_t)((ww[k] >> 16) & 0xff) * sc, f3 = (float)(int)(int8_t)(ww[k] >> 24) * sc;
+            const __half2 ha = __floats2half2_rn(f0, f1), hb = __floats2half2_rn(f2, f3);
+            o[2 * k] = *reinterpret_cast<const uint32_t*>(&ha);
+            o[2 * k + 1] = *reinterpret_cast<const uint32_t*>(&hb);
+        }
+        *reinterpret_cast<uint4*>(V16 + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(V16 + v * 16 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
 }
 
 // three-input maximum (one instruction on sm_100)
@@ -118,7 +128,7 @@ template <int D>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const float* __restrict__ sQ,
-                         const float* __restrict__ sK, const float* __restrict__ sV,
+                         const float* __restrict__ sK,
                          __half* __restrict__ out, int S, float score_scale_log2,
                          uint32_t* __restrict__ status) {
     using Cfg = PrefillCfg<D>;
@@ -147,11 +157,9 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar(B_KFULL + i), 1);
             mbar_init(bar(B_KEMPTY + i), 1);
-            mbar_init(bar(B_VRFULL + i), 1);
-            mbar_init(bar(B_VREMPTY + i), kConvWarps);
             mbar_init(bar(B_SFULL + i), 1);
             mbar_init(bar(B_SEMPTY + i), kSoftmaxWarps);
-            mbar_init(bar(B_V16FULL + i), kConvWarps);
+            mbar_init(bar(B_V16FULL + i), 1);
             mbar_init(bar(B_V16EMPTY + i), 1);
             mbar_init(bar(B_PFULL + i), kSoftmaxWarps);
             mbar_init(bar(B_PVDONE + i), 1);
@@ -165,24 +173,36 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     const uint32_t tmem_base = *tmem_slot_p;
 
     if (warp == 0) {
-        // ================= TMA producer =================
-        if (elect_one()) {
+        // ================= TMA producers =================
+        // Two lanes with independent loops: K tiles are freed by Q.K^T (which runs two tiles ahead),
+        // V16 tiles by P.V; one loop waiting for both would make Q.K^T of tile j wait for P.V of
+        // tile j-2, which is issued after it.
+        if (lane == 0) {
             mbar_expect_tx(bar(B_QFULL), Cfg::TILE_BYTES);
             tma_load_2d(base_s + Cfg::OFF_Q, &tmQ, 0, row_base + q0, bar(B_QFULL));
             for (int j = 0; j < nt; ++j) {
                 const int st = j & 1;
-                const uint32_t par = ((j >> 1) & 1) ^ 1;
-                if (!mbar_wait_spin_bounded(bar(B_KEMPTY + st), par) ||
-                    !mbar_wait_spin_bounded(bar(B_VREMPTY + st), par)) {
+                if (!mbar_wait_spin_bounded(bar(B_KEMPTY + st), ((j >> 1) & 1) ^ 1)) {
                     atomicExch(status, kDeviceTimeoutMagic);
                     break;
                 }
                 mbar_expect_tx(bar(B_KFULL + st), Cfg::TILE_BYTES);
                 tma_load_2d(base_s + Cfg::OFF_K + st * Cfg::TILE_BYTES, &tmK, 0, row_base + j * kKT,
                             bar(B_KFULL + st));
-                mbar_expect_tx(bar(B_VRFULL + st), Cfg::TILE_BYTES);
-                tma_load_2d(base_s + Cfg::OFF_VRAW + st * Cfg::TILE_BYTES, &tmV, 0, row_base + j * kKT,
-                            bar(B_VRFULL + st));
+            }
+        } else if (lane == 1) {
+            for (int j = 0; j < nt; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait_spin_bounded(bar(B_V16EMPTY + st), ((j >> 1) & 1) ^ 1)) {
+                    atomicExch(status, kDeviceTimeoutMagic);
+                    break;
+                }
+                // fp16 V: one box of 128 rows x 64 columns (128 bytes) per slab of the MN-major operand
+                mbar_expect_tx(bar(B_V16FULL + st), Cfg::V16_BYTES);
+#pragma unroll
+                for (int sl = 0; sl < D / 64; ++sl)
+                    tma_load_2d(base_s + Cfg::OFF_V16 + st * Cfg::V16_BYTES + sl * Cfg::SLAB_BYTES, &tmV, sl * 128,
+                                row_base + j * kKT, bar(B_V16FULL + st));
             }
         }
     } else if (warp == 1) {
@@ -235,13 +255,13 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             }
             if (!ok) atomicExch(status, kDeviceTimeoutMagic);
         }
-    } else if (warp < kConvWarp0) {
+    } else {
         // ================= softmax: half a query row (64 KV positions of every tile) per thread =================
         const int sw = warp - 2;                         // 0..7
         const int q = warp & 3;                          // TMEM lane quarter of this warp
         const int half = sw >> 2;                        // columns half*64 .. +63 of every score tile
         const int r = q * 32 + lane;                     // row inside the tile
-        float* wsc = reinterpret_cast<float*>(base + Cfg::OFF_SCALES) + sw * 256;   // [tile & 1][sK[64] | sV[64]] of these columns
+        float* wsc = reinterpret_cast<float*>(base + Cfg::OFF_SCALES) + sw * 128;   // [tile & 1][sK[64]] of these columns
         float* xch = reinterpret_cast<float*>(base + Cfg::OFF_XCH);                 // [2][half][row]
         // query rows past the end of a ragged sequence are computed on clamped operands and never stored
         const float qscale = sQ[min((long long)row_base + q0 + r, total_rows - 1)] * score_scale_log2;     // > 0
@@ -256,22 +276,18 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         f32x2 l2 = 0ull;
         bool ok = true;
         // this warp's per-position scales, fetched ahead of the tile that uses them
-        float pk0, pk1, pv0, pv1;
+        float pk0, pk1;
         auto prefetch = [&](int j) {
             // positions past the end of the arrays (ragged last tile of the last head) read the last element
             const long long o0 = (long long)row_base + j * kKT + half * 64 + lane;
             const size_t oa = (size_t)min(o0, total_rows - 1), ob = (size_t)min(o0 + 32, total_rows - 1);
             asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk0) : "l"(sK + oa));
             asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk1) : "l"(sK + ob));
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pv0) : "l"(sV + oa));
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pv1) : "l"(sV + ob));
         };
         auto commit_scales = [&](int j) {                // prefetched registers -> this warp's block for tile j
-            float* w = wsc + (j & 1) * 128;
+            float* w = wsc + (j & 1) * 64;
             w[lane] = pk0;
             w[32 + lane] = pk1;
-            w[64 + lane] = pv0;
-            w[96 + lane] = pv1;
             __syncwarp();
         };
         // y = (q.k) * sK for 8 columns of a score block held in registers, and their maximum
@@ -304,19 +320,14 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 mx = fmaxf(mx, fmaxf(v.x, v.y));
             }
         };
-        // p = 2^(y*qscale - m_ref) for 8 columns; P*sV as one 16-byte chunk of fp16
-        auto exp8 = [&](const f32x2* y4, const float* v8, f32x2 nm2, unsigned char* dst) {
-            const float4 va = *reinterpret_cast<const float4*>(v8);
-            const float4 vb = *reinterpret_cast<const float4*>(v8 + 4);
+        // p = 2^(y*qscale - m_ref) for 8 columns as one 16-byte chunk of fp16 (sV is already in V16)
+        auto exp8 = [&](const f32x2* y4, f32x2 nm2, unsigned char* dst) {
             const float2 a = unpack2(fma2(y4[0], qs2, nm2)), b = unpack2(fma2(y4[1], qs2, nm2));
             const float2 c = unpack2(fma2(y4[2], qs2, nm2)), d = unpack2(fma2(y4[3], qs2, nm2));
-            const f32x2 p01 = pack2(ex2_approx(a.x), ex2_approx(a.y)), p23 = pack2(ex2_approx(b.x), ex2_approx(b.y));
-            const f32x2 p45 = pack2(ex2_approx(c.x), ex2_approx(c.y)), p67 = pack2(ex2_approx(d.x), ex2_approx(d.y));
-            l2 = add2(l2, add2(add2(p01, p23), add2(p45, p67)));
-            const float2 w01 = unpack2(mul2(p01, pack2(va.x, va.y))), w23 = unpack2(mul2(p23, pack2(va.z, va.w)));
-            const float2 w45 = unpack2(mul2(p45, pack2(vb.x, vb.y))), w67 = unpack2(mul2(p67, pack2(vb.z, vb.w)));
-            *reinterpret_cast<uint4*>(dst) =
-                make_uint4(pack_h2(w01.x, w01.y), pack_h2(w23.x, w23.y), pack_h2(w45.x, w45.y), pack_h2(w67.x, w67.y));
+            const float p0 = ex2_approx(a.x), p1 = ex2_approx(a.y), p2 = ex2_approx(b.x), p3 = ex2_approx(b.y);
+            const float p4 = ex2_approx(c.x), p5 = ex2_approx(c.y), p6 = ex2_approx(d.x), p7 = ex2_approx(d.y);
+            l2 = add2(l2, add2(add2(pack2(p0, p1), pack2(p2, p3)), add2(pack2(p4, p5), pack2(p6, p7))));
+            *reinterpret_cast<uint4*>(dst) = make_uint4(pack_h2(p0, p1), pack_h2(p2, p3), pack_h2(p4, p5), pack_h2(p6, p7));
         };
 
         // ---- prologue: scores of tile 0 into registers ----
@@ -392,7 +403,6 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             // with the conversion of the NEXT tile's scores (integer and FMA pipes), which take over
             // the registers the exponentials have just released ----
             unsigned char* prow = prow0 + st * Cfg::P_BYTES;
-            const float* vsc = wsc + st * 128 + 64;
             const f32x2 nm2 = pack2(-m_ref, -m_ref);
             mx = -INFINITY;
             if (has_next) {
@@ -402,7 +412,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
                 tc_fence_after();
                 if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 2);
-                const float* ksc = wsc + (st ^ 1) * 128;
+                const float* ksc = wsc + (st ^ 1) * 64;
                 const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S0 : Cfg::TM_S1) + half * 64;
                 uint32_t sr[2][16];
                 tmem_ld16(s_addr, sr[0]);
@@ -413,7 +423,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int c = cc * 2 + h;        // 16-byte chunk of P / 8 columns
-                        exp8(&y[c * 4], vsc + c * 8, nm2, prow + ((c ^ (r & 7)) << 4));
+                        exp8(&y[c * 4], nm2, prow + ((c ^ (r & 7)) << 4));
                         convert8(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx);
                     }
                 }
@@ -423,7 +433,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 if (lane == 0) mbar_arrive(bar(B_SEMPTY + (st ^ 1)));
             } else {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) exp8(&y[c * 4], vsc + c * 8, nm2, prow + ((c ^ (r & 7)) << 4));
+                for (int c = 0; c < 8; ++c) exp8(&y[c * 4], nm2, prow + ((c ^ (r & 7)) << 4));
             }
             if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 3);
             tc_fence_before();
@@ -465,48 +475,6 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         } else if (lane == 0) {
             atomicExch(status, kDeviceTimeoutMagic);
         }
-    } else {
-        // ================= converter: raw int8 V tile -> fp16, MN-major swizzled =================
-        const int r0 = threadIdx.x - kConvWarp0 * 32;    // first KV row of the tile handled by this thread
-        for (int j = 0; j < nt; ++j) {
-            const int st = j & 1;
-            bool got = mbar_wait_spin_bounded(bar(B_VRFULL + st), (j >> 1) & 1);
-            if (got && j >= 2) got = mbar_wait_spin_bounded(bar(B_V16EMPTY + st), ((j >> 1) - 1) & 1);
-            if (!__all_sync(0xffffffffu, got)) {
-                if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
-                break;
-            }
-            if (r0 == 0) I8TK_PTRACE(384 + 2 * j);
-#pragma unroll
-            for (int rr = 0; rr < kKT / (32 * kConvWarps); ++rr) {
-            const int r = r0 + rr * (32 * kConvWarps);
-            const unsigned char* raw = base + Cfg::OFF_VRAW + st * Cfg::TILE_BYTES + r * D;
-            unsigned char* dst = base + Cfg::OFF_V16 + st * Cfg::V16_BYTES + r * 128;
-#pragma unroll
-            for (int i = 0; i < D / 16; ++i) {
-                // undo the TMA swizzle of the raw tile: 128-byte rows XOR by r%8, 64-byte rows by (r/2)%4
-                const int src_chunk = (D == 128) ? (i ^ (r & 7)) : (i ^ ((r >> 1) & 3));
-                const uint4 v = *reinterpret_cast<const uint4*>(raw + src_chunk * 16);
-                uint32_t h[8];
-                i8x4_to_h2x2(v.x, h[0], h[1]);
-                i8x4_to_h2x2(v.y, h[2], h[3]);
-                i8x4_to_h2x2(v.z, h[4], h[5]);
-                i8x4_to_h2x2(v.w, h[6], h[7]);
-                // dims i*16 .. i*16+15: slab (i*16)/64, 16-byte chunks 2*(i%4) and +1 of row r
-                unsigned char* drow = dst + (i >> 2) * Cfg::SLAB_BYTES;
-                const int c0 = 2 * (i & 3);
-                *reinterpret_cast<uint4*>(drow + ((c0 ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                *reinterpret_cast<uint4*>(drow + (((c0 + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
-            }
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (r0 == 0) I8TK_PTRACE(384 + 2 * j + 1);
-            if (lane == 0) {
-                mbar_arrive(bar(B_V16FULL + st));
-                mbar_arrive(bar(B_VREMPTY + st));
-            }
-        }
     }
 
     // common exit: every role ends here, then the allocating warp frees tensor memory
@@ -520,7 +488,8 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 
 template <int D>
 int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, const float* sQ,
-                   const float* sK, const float* sV, int BH, int S, uint32_t* status, cudaStream_t st) {
+                   const float* sK, const float* sV, int BH, int S, uint32_t* status, __half* V16,
+                   cudaStream_t st) {
     using Cfg = PrefillCfg<D>;
     static bool attr_done[64] = {false};
     int dev = 0;
@@ -530,21 +499,30 @@ int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* ou
                                        Cfg::SMEM_BYTES));
         attr_done[dev] = true;
     }
+    const unsigned long long rows = (unsigned long long)BH * S;
+    // V once through the dequantiser, then the attention kernel behind it
+    const long long vecs = (long long)rows * (D / 16);
+    long long blocks = (vecs + 255) / 256;
+    if (blocks > 148ll * 16) blocks = 148ll * 16;
+    I8TK_CUDA(launch_after(dequant_v_kernel, dim3((unsigned)blocks), dim3(256), 0, st, V, sV, V16, vecs, D / 16));
+
     const CUtensorMapSwizzle sw = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     CUtensorMap tmQ, tmK, tmV;
-    const unsigned long long rows = (unsigned long long)BH * S;
-    const void* ptrs[3] = {Q, K, V};
-    CUtensorMap* maps[3] = {&tmQ, &tmK, &tmV};
-    for (int i = 0; i < 3; ++i) {
-        const int rc = encode_map_2d_u8(maps[i], ptrs[i], rows, D, kKT, D, sw);
-        I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
-    }
+    int rc = encode_map_2d_u8(&tmQ, Q, rows, D, kKT, D, sw);
+    I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
+    rc = encode_map_2d_u8(&tmK, K, rows, D, kKT, D, sw);
+    I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
+    // fp16 V as a byte matrix [rows][2*D]: boxes of 128 rows x 128 bytes (64 columns), 128-byte swizzle
+    rc = encode_map_2d_u8(&tmV, V16, rows, 2ull * D, kKT, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
     const float score_scale_log2 = 1.4426950408889634f / sqrtf((float)D);
     dim3 grid((S + kQT - 1) / kQT, BH);
     I8TK_CUDA(launch_after(prefill_attention_kernel<D>, grid, dim3(kPrefillThreads), Cfg::SMEM_BYTES, st, tmQ, tmK, tmV,
-                           sQ, sK, sV, out, S, score_scale_log2, status));
+                           sQ, sK, out, S, score_scale_log2, status));
     return I8TK_OK;
 }
+
+size_t attention_workspace(long long rows, int D) { return 256 + round_up((size_t)rows * D * 2, 256); }
 
 }  // namespace
 }  // namespace i8tk
@@ -558,7 +536,10 @@ extern "C" int i8tk_debug_prefill_trace(long long* host_dst) {
 }
 #endif
 
-extern "C" size_t i8tk_attention_workspace_bytes(void) { return 256; }
+extern "C" size_t i8tk_attention_workspace_bytes(int batch, int heads, int seq_len, int head_dim) {
+    if (batch <= 0 || heads <= 0 || seq_len <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
+    return attention_workspace((long long)batch * heads * seq_len, head_dim);
+}
 
 extern "C" int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V, void* out_f16,
                                       const float* sQ, const float* sK, const float* sV, int batch,
@@ -572,12 +553,15 @@ extern "C" int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const in
     I8TK_REQUIRE((long long)batch * heads * seq_len < (1ll << 31), I8TK_ERR_UNSUPPORTED, "too many rows");
     I8TK_REQUIRE(aligned_to(Q, 16) && aligned_to(K, 16) && aligned_to(V, 16) && aligned_to(out_f16, 16),
                  I8TK_ERR_ALIGNMENT, "Q, K, V and out must be 16-byte aligned");
-    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= 256 && aligned_to(workspace, 256),
-                 I8TK_ERR_WORKSPACE, "workspace of 256 bytes, 256-byte aligned, is required");
+    const size_t need = attention_workspace((long long)batch * heads * seq_len, head_dim);
+    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= need, I8TK_ERR_WORKSPACE,
+                 "attention workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
+    I8TK_REQUIRE(aligned_to(workspace, 256), I8TK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint32_t* status = static_cast<uint32_t*>(workspace);
+    __half* V16 = reinterpret_cast<__half*>(static_cast<unsigned char*>(workspace) + 256);
     const int BH = batch * heads;
     if (head_dim == 64)
-        return launch_prefill<64>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, st);
-    return launch_prefill<128>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, st);
+        return launch_prefill<64>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
+    return launch_prefill<128>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
 }
