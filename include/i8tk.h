@@ -29,7 +29,7 @@ typedef void* i8tk_stream_t;
 enum i8tk_status {
     I8TK_OK = 0,
     I8TK_ERR_INVALID_ARGUMENT = 1,  /* null pointer, non-positive size, bad flag      */
-    I8TK_ERR_UNSUPPORTED = 2,       /* head_dim not in {64,128}, non-tile MLP shape   */
+    I8TK_ERR_UNSUPPORTED = 2,       /* head_dim not in {64,128}, MLP width not % 128  */
     I8TK_ERR_WORKSPACE = 3,         /* workspace null or smaller than *_workspace_bytes */
     I8TK_ERR_ALIGNMENT = 4,         /* pointer not aligned as documented              */
     I8TK_ERR_CUDA = 5,              /* a CUDA runtime/driver call or launch failed    */
@@ -284,8 +284,10 @@ int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V, vo
  *                   token and its scales written here.  NULL: legacy dynamic
  *                   per-tensor output scale, written to *out_tensor_scale.
  *   out_tensor_scale device fp32[1] or NULL (required when out_row_scales is NULL)
- * T, d_model, d_ff must be multiples of 128 (the reference's tile gate,
- * kernels/int8_mlp.cu:1023-1026); other shapes return I8TK_ERR_UNSUPPORTED.
+ * d_model and d_ff must be multiples of 128 (other widths return
+ * I8TK_ERR_UNSUPPORTED); T is any positive row count -- the reference gates all
+ * three on 128 and otherwise takes a static-scale fallback that leaves
+ * out_row_scales unwritten (kernels/int8_mlp.cu:1023-1026,1194-1225).
  * All pointers 16-byte aligned.
  * ---------------------------------------------------------------------- */
 enum i8tk_mlp_flags {

@@ -214,7 +214,8 @@ __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
 
 // ---------------------------------------------------------------------------
 // C[M,N] fp16 = epilogue( A[M,K] int8 . B[N,K]^T int8 ), persistent over tiles.
-// M % 128 == 0, N % BN == 0, K % 128 == 0.
+// N % BN == 0, K % 128 == 0; any M >= 1: the last row block may be partial (TMA fills the
+// missing rows of A with zeros; nothing is stored for rows >= M).
 // ---------------------------------------------------------------------------
 template <int BN, bool GELU, bool FUSED, bool DEFER>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -243,7 +244,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int tiles_n = N / BN;
-    const int num_tiles = (M / BM) * tiles_n;
+    const int num_tiles = ((M + BM - 1) / BM) * tiles_n;
     const int kblocks = K / BK;
 
     if (threadIdx.x == 0) {
@@ -363,7 +364,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 pf_s[j] = ld_nc_now(ep.b_per_col ? ep.scale_b + col : ep.scale_b);
                 pf_b[j] = ep.bias ? ld_nc_now(ep.bias + col) : 0.f;
             }
-            pf_sa = ld_nc_now(ep.a_per_row ? ep.scale_a + pm0 + q * 32 + lane : ep.scale_a);
+            pf_sa = ld_nc_now(ep.a_per_row ? ep.scale_a + min(pm0 + q * 32 + lane, M - 1) : ep.scale_a);
         };
         pdl_wait();     // row scales and the row-maxima flags come from the kernels before this one
         if ((int)blockIdx.x < num_tiles) prefetch(blockIdx.x);
@@ -386,7 +387,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * trace_lt + 6);
                 amax = fmaxf(amax, 1e-8f);
                 const float inv_l = 127.f / amax;
-                if (fn0 == 0 && slice == 0) ep.row_scale[fm0 + q * 32 + lane] = amax / 127.f;
+                if (fn0 == 0 && slice == 0 && fm0 + q * 32 + lane < M) ep.row_scale[fm0 + q * 32 + lane] = amax / 127.f;
                 constexpr int SEGS = HC / 16;              // 16-column segments per row
                 int8_t* c8blk = ep.C8 + (size_t)(fm0 + q * 32) * N + fn0 + c0;
                 auto body = [&](auto clamp_tag) {
@@ -402,7 +403,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const uint4 h1 = *reinterpret_cast<const uint4*>(rowp + (stash_swz<HC>(r, 2 * seg + 1) << 4));
                         const uint2 w0 = quant8_f16<kClamp>(h0, inv2);
                         const uint2 w1 = quant8_f16<kClamp>(h1, inv2);
-                        *reinterpret_cast<uint4*>(c8blk + (size_t)r * N + seg * 16) = make_uint4(w0.x, w0.y, w1.x, w1.y);
+                        if (fm0 + q * 32 + r < M)
+                            *reinterpret_cast<uint4*>(c8blk + (size_t)r * N + seg * 16) = make_uint4(w0.x, w0.y, w1.x, w1.y);
                     }
                 };
                 // values above the fp16 range were stored as inf: only then can a product
@@ -496,7 +498,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const int rr2 = it * 16 + (lane >> 1);
                         const int j = lane & 1;
                         const uint4 v = *reinterpret_cast<const uint4*>(cst + rr2 * 32 + ((j ^ ((rr2 >> 2) & 1)) << 4));
-                        *reinterpret_cast<uint4*>(cblk + (size_t)rr2 * N + cc * 16 + j * 8) = v;
+                        if (m0 + q * 32 + rr2 < M) *reinterpret_cast<uint4*>(cblk + (size_t)rr2 * N + cc * 16 + j * 8) = v;
                     }
                 }
             }
@@ -692,7 +694,7 @@ int sm_count_mlp() {
 int gemm_grid(int M, int N, int bn, bool fused) {
     const int sms = sm_count_mlp();
     const int tiles_n = N / bn;
-    const long long tiles = (long long)(M / BM) * tiles_n;
+    const long long tiles = (long long)((M + BM - 1) / BM) * tiles_n;
     int grid = tiles < sms ? (int)tiles : sms;
     if (fused && grid > tiles_n) grid = (grid / tiles_n) * tiles_n;
     return grid > 0 ? grid : 1;
@@ -708,7 +710,7 @@ int pick_bn(int M, int N, bool b_mn, bool fused) {
         const int bn = widths[i];
         if (N % bn) continue;
         if (b_mn && bn % 128) continue;          // [K][N] weights come in 128-wide slabs
-        const long long tiles = (long long)(M / BM) * (N / bn);
+        const long long tiles = (long long)((M + BM - 1) / BM) * (N / bn);
         const int grid = gemm_grid(M, N, bn, fused);
         const long long cost = ((tiles + grid - 1) / grid) * bn;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
@@ -779,8 +781,9 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
     const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
     const size_t o_status = take(256);
     const size_t o_tabs = take(256);
-    const size_t o_p1 = take((size_t)T * (d_ff / pick_bn(T, d_ff, b_mn, true)) * 4);
-    const size_t o_p2 = take((size_t)T * (d_model / pick_bn(T, d_model, b_mn, true)) * 4);
+    const size_t Tp = (size_t)((T + 127) / 128) * 128;       // rows of the flag arrays: whole row blocks
+    const size_t o_p1 = take(Tp * (d_ff / pick_bn(T, d_ff, b_mn, true)) * 4);
+    const size_t o_p2 = take(Tp * (d_model / pick_bn(T, d_model, b_mn, true)) * 4);
     const size_t ones_end = off;
     const size_t o_hsc = take((size_t)T * 4);
     const size_t o_hi8 = take((size_t)T * d_ff);
@@ -844,8 +847,8 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
                  "one of out_row_scales / out_tensor_scale must be given");
     I8TK_REQUIRE(T > 0 && d_model > 0 && d_ff > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
     I8TK_REQUIRE((flags & ~7) == 0, I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
-    I8TK_REQUIRE(T % 128 == 0 && d_model % 128 == 0 && d_ff % 128 == 0, I8TK_ERR_UNSUPPORTED,
-                 "T, d_model and d_ff must be multiples of 128 (got %d, %d, %d)", T, d_model, d_ff);
+    I8TK_REQUIRE(d_model % 128 == 0 && d_ff % 128 == 0, I8TK_ERR_UNSUPPORTED,
+                 "d_model and d_ff must be multiples of 128 (got %d, %d)", d_model, d_ff);
     I8TK_REQUIRE(aligned_to(x, 16) && aligned_to(W1, 16) && aligned_to(W2, 16) && aligned_to(out, 16),
                  I8TK_ERR_ALIGNMENT, "x, W1, W2 and out must be 16-byte aligned");
     const MlpWorkspace w = carve(workspace, T, d_model, d_ff, flags);

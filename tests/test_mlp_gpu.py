@@ -172,8 +172,10 @@ def test_argument_errors():
         e.int8_mlp_forward_per_channel_bias(x, W1, W2, s(128), s(256), s(128), s(3))
     with pytest.raises(RuntimeError, match="must be int8"):
         e.int8_mlp_forward(x.float(), W1, W2, s(128), s(256), s(128))
-    with pytest.raises(RuntimeError, match="multiples of 128"):
-        e.int8_mlp_forward(torch.zeros(1, 4, 128, dtype=torch.int8, device="cuda"), W1, W2, s(4), s(256), s(128))
+    with pytest.raises(RuntimeError, match="multiples of 128"):       # d_model / d_ff must fill tiles; T need not
+        e.int8_mlp_forward(torch.zeros(1, 128, 64, dtype=torch.int8, device="cuda"),
+                           torch.zeros(64, 256, dtype=torch.int8, device="cuda"),
+                           torch.zeros(256, 64, dtype=torch.int8, device="cuda"), s(128), s(256), s(64))
     with pytest.raises(RuntimeError, match="tile multiples"):
         e.int8_mlp_forward_prepacked(torch.zeros(1, 4, 128, dtype=torch.int8, device="cuda"),
                                      W1.t().contiguous(), W2.t().contiguous(), 1.0, 1.0, 1.0)
@@ -187,6 +189,31 @@ def test_argument_errors():
                               sc.data_ptr(), sc.data_ptr(), None, sc.data_ptr(), None, 128, 128, 256, 3,
                               ws.data_ptr(), 256, None)
     assert rc == cabi().ERR_WORKSPACE
+
+
+@pytest.mark.parametrize("T", [1, 7, 100, 129, 300, 1000])
+def test_any_number_of_rows(T):
+    """Row counts that are not multiples of the 128-row tile (the reference takes its static-scale
+    fallback there, kernels/int8_mlp.cu:1023-1026): same results as the rows inside a padded batch."""
+    torch.manual_seed(T)
+    e = ext()
+    dm, dff = 256, 512
+    Tp = ((T + 127) // 128) * 128
+    x = torch.randn(1, Tp, dm, device="cuda", dtype=torch.float16)
+    xi, sx = e.quantize_per_token(x)
+    w1i, s1 = quant.quantize_per_channel_w((torch.randn(dm, dff) * 0.05).numpy())
+    w2i, s2 = quant.quantize_per_channel_w((torch.randn(dff, dm) * 0.05).numpy())
+    w1_t, s1_t, w2_t, s2_t = _cuda(w1i, s1, w2i, s2)
+    b1 = torch.randn(dff, device="cuda") * 0.01
+    sxf = sx.reshape(-1).contiguous()
+    full, full_sc = e.int8_mlp_forward_per_channel_bias(xi, w1_t, w2_t, sxf, s1_t, s2_t, b1)
+    part, part_sc = e.int8_mlp_forward_per_channel_bias(xi[:, :T].contiguous(), w1_t, w2_t, sxf[:T].contiguous(),
+                                                        s1_t, s2_t, b1)
+    assert part.shape == (1, T, dm) and part_sc.shape == (T,)
+    assert torch.equal(part[0], full[0, :T]) and torch.equal(part_sc, full_sc[:T])
+    # legacy per-tensor surface on the same rows
+    o, sc = e.int8_mlp_forward(xi[:, :T].contiguous(), w1_t, w2_t, 0.02, 0.001, 0.001)
+    assert o.shape == (1, T, dm) and sc > 0
 
 
 @pytest.mark.parametrize("M,dm,dff", [(4096, 768, 3072),     # benchmark geometry: 3 tiles per CTA in GEMM1
