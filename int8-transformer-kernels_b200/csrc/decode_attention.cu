@@ -239,16 +239,37 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
                 int npg = (len - pos0 + pg.page - 1) / pg.page;
                 npg = npg < 0 ? 0 : (npg > ppt ? ppt : npg);
                 const uint32_t kv_bytes = (uint32_t)pg.page * D, sc_bytes = (uint32_t)pg.page * 4;
-                if (lane == 0) mbar_expect_tx(bar, (uint32_t)npg * 2 * (kv_bytes + sc_bytes));
                 const int* ids = pg.page_table + (size_t)b * pg.max_pages + pos0 / pg.page;
-                if (lane < npg) {
-                    const int q = lane;
-                    const size_t first = ((size_t)__ldg(ids + q) * pg.H + h) * pg.page;   // first position of the page
-                    bulk_g2s_hint(dst + 2 * T::TILE_BYTES + q * sc_bytes, sK + first, sc_bytes, bar, stream_once);
-                    bulk_g2s_hint(dst + 2 * T::TILE_BYTES + T::SCALE_BYTES + q * sc_bytes, sV + first, sc_bytes, bar,
-                                  stream_once);
-                    bulk_g2s_hint(dst + q * kv_bytes, K + first * D, kv_bytes, bar, stream_once);
-                    bulk_g2s_hint(dst + T::TILE_BYTES + q * kv_bytes, V + first * D, kv_bytes, bar, stream_once);
+                if (pg.page > 32) {
+                    // large pages: the scales ride bulk copies of their own (256-512 B each)
+                    if (lane == 0) mbar_expect_tx(bar, (uint32_t)npg * 2 * (kv_bytes + sc_bytes));
+                    if (lane < npg) {
+                        const int q = lane;
+                        const size_t first = ((size_t)__ldg(ids + q) * pg.H + h) * pg.page;   // first position of the page
+                        bulk_g2s_hint(dst + 2 * T::TILE_BYTES + q * sc_bytes, sK + first, sc_bytes, bar, stream_once);
+                        bulk_g2s_hint(dst + 2 * T::TILE_BYTES + T::SCALE_BYTES + q * sc_bytes, sV + first, sc_bytes, bar,
+                                      stream_once);
+                        bulk_g2s_hint(dst + q * kv_bytes, K + first * D, kv_bytes, bar, stream_once);
+                        bulk_g2s_hint(dst + T::TILE_BYTES + q * kv_bytes, V + first * D, kv_bytes, bar, stream_once);
+                    }
+                } else {
+                    // small pages (16 or 32 positions): a tile is 4-8 pages and four bulk copies per
+                    // page would be bound by copy issue, so only K and V travel as bulk copies; the
+                    // 64-128 bytes of scales per page go as 16-byte asynchronous copies of the page's
+                    // lane, which the stage's barrier is told to wait for before lane 0 arrives
+                    if (lane < npg) {
+                        const size_t first = ((size_t)__ldg(ids + lane) * pg.H + h) * pg.page;
+                        bulk_g2s_hint(dst + lane * kv_bytes, K + first * D, kv_bytes, bar, stream_once);
+                        bulk_g2s_hint(dst + T::TILE_BYTES + lane * kv_bytes, V + first * D, kv_bytes, bar, stream_once);
+                        const uint32_t dk = dst + 2 * T::TILE_BYTES + lane * sc_bytes;
+                        for (uint32_t o = 0; o < sc_bytes; o += 16) {
+                            cp_async16(dk + o, reinterpret_cast<const unsigned char*>(sK + first) + o);
+                            cp_async16(dk + T::SCALE_BYTES + o, reinterpret_cast<const unsigned char*>(sV + first) + o);
+                        }
+                        cp_async_mbar_arrive(bar);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_expect_tx(bar, (uint32_t)npg * 2 * kv_bytes);
                 }
             } else {
             const int nrow = min(kTile, S - pos0);
