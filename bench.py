@@ -509,11 +509,17 @@ def sweep(torch, ext, cabi, world, rank, barrier, dist):
 
 def paged_sweep(torch, ext):
     """The headline geometry (B32 H12 D64 ctx 32768) read through a paged INT8 KV cache with a
-    shuffled page table, all requests at full length: GB/s of K+V as in the headline metric."""
+    shuffled page table: all requests at full length, and two batches of mixed lengths (drawn
+    uniformly from 256..32768; one request at 32768 among 31 at 2048).  GB/s of the K+V bytes
+    the lengths really cover, as in the headline metric."""
     out = []
     B, H, D, S = 32, 12, 64, 32768
     g = torch.Generator(device="cuda").manual_seed(0)
     Qi, sQ = ext.quantize_per_token(torch.randn(B, H, D, device="cuda", dtype=torch.float16, generator=g))
+    sq = sQ.reshape(-1).contiguous()
+    mixes = (("all requests at full length", torch.full((B,), S, dtype=torch.int32)),
+             ("lengths uniform in 256..32768", torch.randint(256, S + 1, (B,), generator=torch.Generator().manual_seed(1)).to(torch.int32)),
+             ("one request at 32768, 31 at 2048", torch.tensor([S] + [2048] * (B - 1), dtype=torch.int32)))
     for page in (16, 64, 128):
         npp = S // page
         pages = B * npp
@@ -522,13 +528,13 @@ def paged_sweep(torch, ext):
         sKp = torch.rand(pages, H, page, device="cuda", generator=g) * 0.02 + 0.01
         sVp = torch.rand(pages, H, page, device="cuda", generator=g) * 0.02 + 0.01
         table = torch.randperm(pages, device="cuda", generator=g).to(torch.int32).view(B, npp).contiguous()
-        seq = torch.full((B,), S, dtype=torch.int32, device="cuda")
-        sq = sQ.reshape(-1).contiguous()
-        steps = 20
-        el = timed_steps(torch, lambda: ext.int8_decode_attention_paged(Qi, Kp, Vp, sq, sKp, sVp, table, seq, S), steps, 3)
-        gbps = kv_bytes(B, H, S, D) * steps / el / 1e9
-        out.append({"workload": f"paged decode B{B} H{H} D{D} ctx{S}, page {page}, shuffled page table",
-                    "us_per_step": el / steps * 1e6, "GBps": gbps, "pct_of_8TBps_per_gpu": gbps / 80.0})
+        for name, lens in mixes if page != 64 else mixes[:1]:
+            seq = lens.cuda()
+            steps = 20
+            el = timed_steps(torch, lambda: ext.int8_decode_attention_paged(Qi, Kp, Vp, sq, sKp, sVp, table, seq, S), steps, 3)
+            gbps = 2 * H * D * int(lens.sum()) * steps / el / 1e9
+            out.append({"workload": f"paged decode B{B} H{H} D{D} ctx{S}, page {page}, shuffled page table, {name}",
+                        "us_per_step": el / steps * 1e6, "GBps": gbps, "pct_of_8TBps_per_gpu": gbps / 80.0})
         del Kp, Vp, sKp, sVp
         torch.cuda.empty_cache()
     return out

@@ -175,11 +175,15 @@ int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_t* K, const
  *   sK_pool, sV_pool fp32 [num_pages, heads, page_size]
  *   page_table      int32 [batch, max_pages_per_seq] (device): request b holds, in sequence
  *                   order, pages page_table[b][0 .. ceil(seq_lens[b] / page_size))
- *   seq_lens        int32 [batch] (device), each in [1, max_seq_len]
+ *   seq_lens        int32 [batch] (device), each in [0, max_seq_len]; a request of length 0
+ *                   gets a zero output row
  *   Q int8 [batch*heads, head_dim], sQ fp32 [batch*heads], out fp16 [batch*heads, head_dim]
  * max_seq_len is a host-side upper bound on seq_lens (it sizes the grid and the workspace:
- * i8tk_decode_workspace_bytes(batch*heads, max_seq_len, head_dim)); tiles past a request's
- * end move no bytes.  page_size 16, 32, 64 or 128; head_dim 64 or 128; pools 16-byte aligned. */
+ * i8tk_decode_workspace_bytes(batch*heads, max_seq_len, head_dim)).  The lengths themselves
+ * are read on the device only: a one-CTA kernel counts the 128-position tiles each request
+ * really has and cuts their sequence into equal runs for the CTAs of the scan, so a batch of
+ * mixed lengths takes the time of the bytes it reads, not of batch x the longest request.
+ * page_size 16, 32, 64 or 128; head_dim 64 or 128; pools 16-byte aligned. */
 int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool, const int8_t* V_pool,
                                 void* out_f16, const float* sQ,
                                 const float* sK_pool, const float* sV_pool,

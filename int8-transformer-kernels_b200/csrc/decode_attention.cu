@@ -73,13 +73,116 @@ struct DecodePlan {
 // Paged KV cache (PAGED kernels): K, V and their scales live in pools of fixed-size pages,
 // laid out [page][head][position in page][D] (scales [page][head][position in page]); request
 // b owns pages page_table[b][0 .. ceil(seq_lens[b] / page)) in sequence order.
+//
+// Requests differ in length, and the lengths are known on the device only, so the division of
+// the work is made there: decode_ragged_plan_kernel counts the tiles every request really has
+// (ceil(seq_lens[b] / kTile) per head, none for an empty request), lays the tiles of all (b,h)
+// rows end to end, cuts that sequence into equal runs, one per CTA, and leaves for CTA c the row
+// and tile its run starts at.  A short request therefore costs what it reads, not what the
+// longest one does.
 struct PagedKV {
     const int* page_table;   // [B][max_pages]
-    const int* seq_lens;     // [B] positions in use, >= 1
+    const int* seq_lens;     // [B] positions in use
     int H;                   // heads per request: b = bh / H, h = bh % H
     int page;                // positions per page: 16, 32, 64 or 128
     int max_pages;           // row length of page_table
+    int B;                   // requests
+    const int* hdr;          // plan: [0] tiles per CTA, [1] tiles in all
+    const int* prefix;       // plan: [B+1] tiles per head of the requests before b
+    const int4* starts;      // plan: [nctas] {first (b,h) row, first tile in it, tiles of the run, 0}
 };
+
+__device__ __forceinline__ int tiles_of(int len) { return len > 0 ? (len + kTile - 1) / kTile : 0; }
+
+// First (b,h) row at or after `bh` that has tiles, and its tile count.  Called only while tiles
+// of the CTA's run remain, so such a row exists; the bound keeps a damaged plan inside the arrays.
+__device__ __forceinline__ int row_with_tiles(const PagedKV& pg, int bh, int& tpb) {
+    const int BH = pg.B * pg.H;
+    while (bh < BH) {
+        tpb = tiles_of(pg.seq_lens[bh / pg.H]);
+        if (tpb > 0) return bh;
+        bh = (bh / pg.H + 1) * pg.H;
+    }
+    tpb = 1 << 30;
+    return BH - 1;
+}
+
+// One CTA of 1024 threads: tiles per request, their exclusive prefix sum, how many of the
+// launched CTAs take a run (about kTargetTiles tiles each, at least one resident wave, at most
+// the grid), the run length, and the starting point of every CTA of the scan.
+constexpr int kPlanSmemRequests = 4096;      // prefix sums of up to this many requests are searched in shared memory
+
+__global__ void __launch_bounds__(1024)
+decode_ragged_plan_kernel(const int* __restrict__ seq_lens, int B, int H, int nctas, int resident, int target_tiles,
+                          int* __restrict__ hdr, int* __restrict__ prefix, int4* __restrict__ starts) {
+    __shared__ int warp_tot[32];
+    __shared__ int s_prefix[kPlanSmemRequests + 1];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const bool in_smem = B <= kPlanSmemRequests;
+    const int per = (B + 1023) / 1024;
+    const int lo = min(B, t * per), hi = min(B, lo + per);
+    int sum = 0;
+    for (int b = lo; b < hi; ++b) sum += tiles_of(seq_lens[b]);
+    int inc = sum;                                   // inclusive scan over the threads
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_tot[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += v;
+        }
+        warp_tot[lane] = w;
+    }
+    __syncthreads();
+    int base = inc - sum + (warp > 0 ? warp_tot[warp - 1] : 0);
+    for (int b = lo; b < hi; ++b) {
+        prefix[b] = base;
+        if (in_smem) s_prefix[b] = base;
+        base += tiles_of(seq_lens[b]);
+    }
+    if (t == 1023) {
+        prefix[B] = warp_tot[31];
+        if (in_smem) s_prefix[B] = warp_tot[31];
+    }
+    __syncthreads();                                 // the prefix sums are read back below by other threads
+    const int* pre = in_smem ? s_prefix : prefix;
+
+    const long long total = (long long)warp_tot[31] * H;
+    long long use = total / target_tiles;            // CTAs that take a run
+    if (use < resident) use = resident;
+    if (use > nctas) use = nctas;
+    long long tpc = (total + use - 1) / use;
+    if (tpc < 1) tpc = 1;
+    if (t == 0) {
+        hdr[0] = (int)tpc;
+        hdr[1] = (int)total;
+    }
+    for (int c = t; c < nctas; c += 1024) {
+        const long long f0 = (long long)c * tpc;
+        int4 st = make_int4(0, 0, 0, 0);
+        if (f0 < total) {
+            int a = 0, z = B - 1;                    // largest b with prefix[b] * H <= f0
+            while (a < z) {
+                const int mid = (a + z + 1) >> 1;
+                if ((long long)pre[mid] * H <= f0) a = mid; else z = mid - 1;
+            }
+            const int tb = pre[a + 1] - pre[a];                  // > 0: f0 lies inside request a
+            const long long rem = f0 - (long long)pre[a] * H;
+            const int h = (int)(rem / tb);
+            st = make_int4(a * H + h, (int)(rem - (long long)h * tb), (int)min(tpc, total - f0), 0);
+        }
+        starts[c] = st;
+    }
+}
 
 __device__ __forceinline__ int dot16(const int4& q, const int4& k) {
     int d = __dp4a(q.x, k.x, 0);
@@ -190,10 +293,21 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
     // this CTA's set-up may overlap its tail.
     pdl_wait();
     pdl_launch_dependents();                    // the merge kernel may be scheduled as SMs drain
-    const long long f0 = (long long)blockIdx.x * plan.tpc;
-    if (f0 >= plan.total) return;
-    const int ntl = (int)min((long long)plan.tpc, plan.total - f0);   // tiles of this CTA
+    int ntl, bh0, tb0;                          // tiles of this CTA, row and tile it starts at
     const int tpb = plan.tpb;
+    if constexpr (PAGED) {
+        const int4 st = pg.starts[blockIdx.x];
+        bh0 = st.x;
+        tb0 = st.y;
+        ntl = st.z;
+        if (ntl <= 0) return;
+    } else {
+        const long long f0 = (long long)blockIdx.x * plan.tpc;
+        if (f0 >= plan.total) return;
+        ntl = (int)min((long long)plan.tpc, plan.total - f0);
+        bh0 = (int)(f0 / tpb);
+        tb0 = (int)(f0 - (long long)bh0 * tpb);
+    }
 
     const uint32_t ring_s = smem_u32(smem);
     const uint32_t full0 = ring_s + T::RING_BYTES;
@@ -209,9 +323,6 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
     }
     __syncthreads();
 
-    const int bh0 = (int)(f0 / tpb);
-    const int tb0 = (int)(f0 - (long long)bh0 * tpb);
-
     if (warp == kConsumers) {
         // ---- producer: one lane walks the tile list and keeps the ring full ----
         // contiguous cache: one lane issues the four copies of a tile; paged cache: lane q issues
@@ -220,6 +331,8 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         if (!PAGED && lane != 0) return;
         const uint64_t stream_once = l2_policy_evict_first();   // K, V and their scales are read once
         int p_bh = bh0, p_tb = tb0;
+        int p_tpb = tpb;                            // tiles of row p_bh
+        if constexpr (PAGED) p_tpb = tiles_of(pg.seq_lens[bh0 / pg.H]);
         for (int i = 0; i < ntl; ++i) {
             const int st = i % STAGES;
             if (i >= STAGES) {
@@ -286,7 +399,13 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
             bulk_g2s_hint(dst, K + row * D, kv_bytes, bar, stream_once);
             bulk_g2s_hint(dst + T::TILE_BYTES, V + row * D, kv_bytes, bar, stream_once);
             }
-            if (++p_tb == tpb) { p_tb = 0; ++p_bh; }
+            if (++p_tb == p_tpb) {
+                p_tb = 0;
+                ++p_bh;
+                if constexpr (PAGED) {
+                    if (i + 1 < ntl) p_bh = row_with_tiles(pg, p_bh, p_tpb);
+                }
+            }
         }
         return;
     }
@@ -298,10 +417,12 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
     const f32x2 neg_magic2 = pack2(-8388736.0f, -8388736.0f);   // -(2^23 + 128)
 
     int c_bh = bh0, c_tb = tb0;
+    int c_tpb = tpb;                                // tiles of row c_bh
+    if constexpr (PAGED) c_tpb = tiles_of(pg.seq_lens[bh0 / pg.H]);
     int i = 0;                                      // tiles of this CTA consumed so far
     for (int seg = 0; i < ntl; ++seg) {
         // ---- one (b,h) segment: tiles [c_tb, c_tb + seg_tiles) of row c_bh ----
-        const int seg_tiles = min(ntl - i, tpb - c_tb);
+        const int seg_tiles = min(ntl - i, c_tpb - c_tb);
         const int4 q4 = *reinterpret_cast<const int4*>(Q + (size_t)c_bh * D + c * 16);
         const float qs = sQ[c_bh] * score_scale_log2;
         const float* sKb = sK + (size_t)c_bh * S;
@@ -405,7 +526,9 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
             for (int k = 0; k < 16; ++k) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
         }
         const float lsum = warp_sum(l);
-        float* row = rows + (((size_t)blockIdx.x * plan.maxseg + seg) * kConsumers + warp) * T::ROW_FLOATS;
+        // paged: slot (row + CTA) is unique because the CTAs' runs are ordered by row
+        float* row = PAGED ? rows + ((size_t)(c_bh + blockIdx.x) * kConsumers + warp) * T::ROW_FLOATS
+                           : rows + (((size_t)blockIdx.x * plan.maxseg + seg) * kConsumers + warp) * T::ROW_FLOATS;
         if (lane == 0) *reinterpret_cast<float4*>(row) = make_float4(m, lsum, 0.f, 0.f);
         if (g == 0) {
             float4* dst = reinterpret_cast<float4*>(row + 4 + c * 16);
@@ -414,7 +537,13 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
                 dst[k] = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
         }
         c_tb += seg_tiles;
-        if (c_tb == tpb) { c_tb = 0; ++c_bh; }
+        if (c_tb == c_tpb) {
+            c_tb = 0;
+            ++c_bh;
+            if constexpr (PAGED) {
+                if (i < ntl) c_bh = row_with_tiles(pg, c_bh, c_tpb);
+            }
+        }
     }
 }
 
@@ -424,10 +553,12 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
 // the plan).  Otherwise: row (s, bh) of a gathered [nparts, BH, D+4] array.
 // Writes either the normalised fp16 output or one merged row.
 // ---------------------------------------------------------------------------
-template <int D, bool FLAT>
+// RAGGED (with FLAT): the rows were written under the device-side plan of a paged cache; a
+// request without positions gets a zero output row.
+template <int D, bool FLAT, bool RAGGED = false>
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, DecodePlan plan,
-                      __half* __restrict__ out, float* __restrict__ row_out) {
+                      __half* __restrict__ out, float* __restrict__ row_out, PagedKV pg) {
     constexpr int ROW = D + 4;
     constexpr int DPL = D / 32;
     pdl_wait();                                 // rows of the scan launched just before this kernel
@@ -436,13 +567,22 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, Decode
     const int lane = threadIdx.x & 31;
 
     int c_first = 0, n = nparts;
-    if constexpr (FLAT) {
+    if constexpr (RAGGED) {
+        const int b = bh / pg.H, h = bh - b * pg.H;
+        const int p0 = pg.prefix[b], tb = pg.prefix[b + 1] - p0, tpc = pg.hdr[0];
+        const long long fb = (long long)p0 * pg.H + (long long)h * tb;    // first flat tile of the row
+        c_first = (int)(fb / tpc);
+        n = tb > 0 ? ((int)((fb + tb - 1) / tpc) - c_first + 1) * kConsumers : 0;
+    } else if constexpr (FLAT) {
         const long long fb = (long long)bh * plan.tpb;
         c_first = (int)(fb / plan.tpc);
         n = ((int)((fb + plan.tpb - 1) / plan.tpc) - c_first + 1) * kConsumers;
     }
     auto row_ptr = [&](int i) -> const float* {
-        if constexpr (FLAT) {
+        if constexpr (RAGGED) {
+            const int cta = c_first + i / kConsumers;
+            return rows + ((size_t)(bh + cta) * kConsumers + i % kConsumers) * ROW;
+        } else if constexpr (FLAT) {
             const int cta = c_first + i / kConsumers;
             const int seg = bh - (int)(((long long)cta * plan.tpc) / plan.tpb);
             return rows + (((size_t)cta * plan.maxseg + seg) * kConsumers + i % kConsumers) * ROW;
@@ -480,7 +620,7 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, Decode
     }
 
     if (out != nullptr) {
-        const float inv = 1.0f / L;
+        const float inv = L > 0.f ? 1.0f / L : 0.f;     // no positions at all: zeros
         __half* o = out + (size_t)bh * D + lane * DPL;
         if constexpr (DPL == 4) {
             __half2 h0 = __floats2half2_rn(a[0] * inv, a[1] * inv);
@@ -665,9 +805,13 @@ int env_int(const char* name, int dflt) {
 // the cost of filling a ring negligible while leaving the hardware scheduler
 // room to even out SM-to-SM speed differences; tiny problems get at least
 // kMinTiles tiles per CTA.  I8TK_DECODE_CTAS overrides the count (tuning only).
+constexpr int kTargetTiles = 64;
+// Paged cache: longer runs measured faster (fewer ring fills against page-sized copies);
+// I8TK_DECODE_TARGET_TILES overrides it (tuning only).
+constexpr int kPagedTargetTiles = 128;
+
 DecodePlan make_plan(int BH, int S, int D, int sms) {
     constexpr int kMinTiles = 2;
-    constexpr int kTargetTiles = 64;
     const int ctas_per_sm = (D == 64) ? DecodeTraits<64>::CTAS_PER_SM : DecodeTraits<128>::CTAS_PER_SM;
     DecodePlan p;
     p.tpb = (S + kTile - 1) / kTile;
@@ -692,8 +836,29 @@ size_t rows_bytes(const DecodePlan& p, int D) {
     return (size_t)p.nctas * p.maxseg * kConsumers * (D + 4) * sizeof(float);
 }
 
+// Workspace of the paged entry point behind the 256-byte status block: one row slot per
+// (row + CTA) pair, the plan header, the CTAs' starting points and the tile prefix sums.
+struct RaggedLayout {
+    size_t rows_off, hdr_off, starts_off, prefix_off, total;
+};
+
+RaggedLayout ragged_layout(int BH, int B, int nctas, int D) {
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    RaggedLayout l;
+    l.rows_off = 256;
+    l.hdr_off = l.rows_off + up((size_t)(BH + nctas) * kConsumers * (D + 4) * sizeof(float));
+    l.starts_off = l.hdr_off + 256;
+    l.prefix_off = l.starts_off + up((size_t)nctas * sizeof(int4));
+    l.total = l.prefix_off + up((size_t)(B + 1) * sizeof(int));
+    return l;
+}
+
+// Large enough for the contiguous and for the paged entry points (a batch has at most BH requests).
 size_t workspace_bytes(int BH, int S, int D) {
-    return 256 + rows_bytes(make_plan(BH, S, D, sm_count()), D);
+    const DecodePlan p = make_plan(BH, S, D, sm_count());
+    const size_t flat = 256 + rows_bytes(p, D);
+    const size_t ragged = ragged_layout(BH, BH, p.nctas, D).total;
+    return flat > ragged ? flat : ragged;
 }
 
 template <int D, bool SCALES_BULK, bool PAGED = false>
@@ -740,7 +905,7 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
     if (rc != I8TK_OK) return rc;
     // the merge may be scheduled while the scan drains: it waits (pdl_wait) for the scan's rows
     I8TK_CUDA(launch_after(decode_combine_kernel<D, true>, dim3((BH + 3) / 4), dim3(128), 0, stream,
-                           (const float*)rows, BH, 0, p, out, part));
+                           (const float*)rows, BH, 0, p, out, part, PagedKV{}));
     return I8TK_OK;
 }
 
@@ -923,25 +1088,34 @@ extern "C" int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool
                  I8TK_ERR_ALIGNMENT, "Q, the pools and their scales must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int BH = batch * heads;
+    // the longest request only sizes the grid; the runs are cut on the device from the real lengths
     const DecodePlan p = make_plan(BH, max_seq_len, head_dim, sm_count());
-    const size_t need = 256 + rows_bytes(p, head_dim);
-    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= need, I8TK_ERR_WORKSPACE,
-                 "decode workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
+    const RaggedLayout lay = ragged_layout(BH, batch, p.nctas, head_dim);
+    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= lay.total, I8TK_ERR_WORKSPACE,
+                 "decode workspace too small: need %zu bytes, got %zu", lay.total, workspace_bytes);
     I8TK_REQUIRE(aligned_to(workspace, 256), I8TK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
-    uint32_t* status = reinterpret_cast<uint32_t*>(workspace);
-    float* rows = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 256);
-    const PagedKV pg{page_table, seq_lens, heads, page_size, max_pages_per_seq};
+    unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+    uint32_t* status = reinterpret_cast<uint32_t*>(ws);
+    float* rows = reinterpret_cast<float*>(ws + lay.rows_off);
+    int* hdr = reinterpret_cast<int*>(ws + lay.hdr_off);
+    int4* starts = reinterpret_cast<int4*>(ws + lay.starts_off);
+    int* prefix = reinterpret_cast<int*>(ws + lay.prefix_off);
+    const PagedKV pg{page_table, seq_lens, heads, page_size, max_pages_per_seq, batch, hdr, prefix, starts};
+    const int resident = sm_count() * (head_dim == 64 ? DecodeTraits<64>::CTAS_PER_SM : DecodeTraits<128>::CTAS_PER_SM);
+    I8TK_CUDA(launch_after(decode_ragged_plan_kernel, dim3(1), dim3(1024), 0, st, seq_lens, batch, heads, p.nctas,
+                           resident < p.nctas ? resident : p.nctas, env_int("I8TK_DECODE_TARGET_TILES", kPagedTargetTiles), hdr, prefix,
+                           starts));
     int rc;
     if (head_dim == 64) {
         rc = launch_partial<64, true, true>(Q, K_pool, V_pool, sQ, sK_pool, sV_pool, rows, max_seq_len, p, status, st, pg);
         if (rc != I8TK_OK) return rc;
-        I8TK_CUDA(launch_after(decode_combine_kernel<64, true>, dim3((BH + 3) / 4), dim3(128), 0, st,
-                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr));
+        I8TK_CUDA(launch_after(decode_combine_kernel<64, true, true>, dim3((BH + 3) / 4), dim3(128), 0, st,
+                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr, pg));
     } else {
         rc = launch_partial<128, true, true>(Q, K_pool, V_pool, sQ, sK_pool, sV_pool, rows, max_seq_len, p, status, st, pg);
         if (rc != I8TK_OK) return rc;
-        I8TK_CUDA(launch_after(decode_combine_kernel<128, true>, dim3((BH + 3) / 4), dim3(128), 0, st,
-                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr));
+        I8TK_CUDA(launch_after(decode_combine_kernel<128, true, true>, dim3((BH + 3) / 4), dim3(128), 0, st,
+                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr, pg));
     }
     return I8TK_OK;
 }
@@ -973,10 +1147,10 @@ extern "C" int i8tk_decode_combine_partials(const float* parts, int nparts, int 
     const DecodePlan none{};
     if (head_dim == 64)
         decode_combine_kernel<64, false><<<grid, 128, 0, st>>>(parts, BH, nparts, none,
-                                                               static_cast<__half*>(out_f16), nullptr);
+                                                               static_cast<__half*>(out_f16), nullptr, PagedKV{});
     else
         decode_combine_kernel<128, false><<<grid, 128, 0, st>>>(parts, BH, nparts, none,
-                                                                static_cast<__half*>(out_f16), nullptr);
+                                                                static_cast<__half*>(out_f16), nullptr, PagedKV{});
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }

@@ -80,3 +80,43 @@ def test_paged_is_deterministic_and_rejects_bad_arguments():
     with pytest.raises(RuntimeError):
         e.int8_decode_attention_paged(Qi, Kp[:, :, :8].contiguous(), Vp[:, :, :8].contiguous(), sQ.reshape(-1),
                                       sKp[:, :, :8].contiguous(), sVp[:, :, :8].contiguous(), table, seq, 300)
+
+
+@pytest.mark.parametrize("B,H,D,page,seed", [(48, 3, 64, 16, 1), (40, 2, 128, 64, 2), (300, 1, 64, 128, 3)])
+def test_paged_ragged_batch(B, H, D, page, seed):
+    """One long request among many short ones, and more requests than the scan has CTAs per row:
+    the runs of the CTAs are cut from the real lengths, every request must still come out as
+    the contiguous op gives it."""
+    e = ext()
+    rng = np.random.default_rng(seed)
+    lens = [int(v) for v in rng.integers(1, 700, size=B)]
+    lens[B // 3] = 6000
+    lens[0] = 1
+    lens[-1] = 129
+    Qi, sQ, Kp, Vp, sKp, sVp, table, seq, contig = _paged_case(B, H, D, lens, page, seed=seed)
+    out = e.int8_decode_attention_paged(Qi, Kp, Vp, sQ.reshape(-1), sKp, sVp, table, seq, max(lens))
+    assert not torch.isnan(out).any()
+    for b, (Ki, Vi, sK, sV) in enumerate(contig):
+        same = e.int8_decode_attention_forward(Qi[b:b + 1].contiguous(), Ki[None].contiguous(), Vi[None].contiguous(),
+                                               sQ[b:b + 1].reshape(-1), sK.reshape(-1), sV.reshape(-1))
+        tol = 2e-3 * max(1.0, float(same.float().abs().max()))
+        assert (out[b:b + 1].float() - same.float()).abs().max().item() < tol, (b, lens[b])
+    for b in (0, B // 3, B - 1):                  # and against the float64 oracle for the extremes
+        Ki, Vi, sK, sV = contig[b]
+        ref = odec.decode_attention(Qi[b:b + 1].cpu().numpy(), Ki[None].cpu().numpy(), Vi[None].cpu().numpy(),
+                                    sQ[b:b + 1].cpu().numpy(), sK[None].cpu().numpy(), sV[None].cpu().numpy())
+        assert cosine(out[b:b + 1].float().cpu().numpy(), ref) > 0.9999
+
+
+def test_paged_request_without_positions_gives_zeros():
+    e = ext()
+    lens = [200, 5, 300, 140]
+    Qi, sQ, Kp, Vp, sKp, sVp, table, seq, _ = _paged_case(4, 2, 64, lens, 32, seed=11)
+    full = e.int8_decode_attention_paged(Qi, Kp, Vp, sQ.reshape(-1), sKp, sVp, table, seq, 300)
+    for gone in (1, 3, 0):
+        seq2 = seq.clone()
+        seq2[gone] = 0
+        out = e.int8_decode_attention_paged(Qi, Kp, Vp, sQ.reshape(-1), sKp, sVp, table, seq2, 300)
+        assert torch.count_nonzero(out[gone]).item() == 0
+        keep = [b for b in range(4) if b != gone]
+        assert (out[keep].float() - full[keep].float()).abs().max().item() < 2e-3   # other runs, other merge order
