@@ -265,6 +265,30 @@ def timed_steps(torch, fn, steps, warmup, barrier=None):
     return e0.elapsed_time(e1) / 1e3      # seconds
 
 
+def timed_settled(torch, fn, steps, warmup, barrier=None, min_seconds=0.03):
+    """timed_steps for the sweep's short kernels.  A fixed 10-20 calls of a kernel of tens of
+    microseconds is a window of a few milliseconds, and the first milliseconds after a different
+    workload were measured up to 20 % slow (the same call on the same buffers, repeated, settles).
+    So: run the call for 20 ms first, then time at least `steps` calls and at least `min_seconds`
+    of them.  Returns seconds scaled back to `steps` calls, like timed_steps."""
+    if barrier is not None:
+        return timed_steps(torch, fn, steps, warmup, barrier)
+    fn()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        for _ in range(5):
+            fn()
+        n += 5
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if dt >= 0.02:
+            break
+    actual = max(steps, min(5000, int(min_seconds / (dt / n)) + 1))
+    return timed_steps(torch, fn, actual, warmup) * steps / actual
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -447,7 +471,7 @@ def sweep(torch, ext, cabi, world, rank, barrier, dist):
                       8192, True, 20))
     for name, b, h, d, s, outl, steps in cases:
         args = make_inputs(torch, ext, b, h, s, d, outliers=outl, seed=rank)
-        el = reduce_max(timed_steps(torch, lambda: ext.int8_decode_attention_forward(*args), steps, 5, barrier))
+        el = reduce_max(timed_settled(torch, lambda: ext.int8_decode_attention_forward(*args), steps, 5, barrier))
         strong = name.startswith("cfg2") and world > 1
         gbs = world * kv_bytes(b, h, s, d) * steps / el / 1e9
         res.append({"workload": name, "us_per_step": el / steps * 1e6, "GBps": gbs,
@@ -466,7 +490,7 @@ def sweep(torch, ext, cabi, world, rank, barrier, dist):
             with torch.cuda.graph(graph):
                 for _ in range(20):
                     graph_out = ext.int8_decode_attention_forward(*args)
-            el_g = timed_steps(torch, graph.replay, 20, 3)
+            el_g = timed_settled(torch, graph.replay, 20, 3)
             res[-1]["us_per_step_replayed_from_a_cuda_graph"] = el_g / 20 / 20 * 1e6
             del graph, graph_out
         del args
@@ -531,7 +555,7 @@ def paged_sweep(torch, ext):
         for name, lens in mixes if page != 64 else mixes[:1]:
             seq = lens.cuda()
             steps = 20
-            el = timed_steps(torch, lambda: ext.int8_decode_attention_paged(Qi, Kp, Vp, sq, sKp, sVp, table, seq, S), steps, 3)
+            el = timed_settled(torch, lambda: ext.int8_decode_attention_paged(Qi, Kp, Vp, sq, sKp, sVp, table, seq, S), steps, 3)
             gbps = 2 * H * D * int(lens.sum()) * steps / el / 1e9
             out.append({"workload": f"paged decode B{B} H{H} D{D} ctx{S}, page {page}, shuffled page table, {name}",
                         "us_per_step": el / steps * 1e6, "GBps": gbps, "pct_of_8TBps_per_gpu": gbps / 80.0})
@@ -554,8 +578,8 @@ def block_sweep(torch):
     for S in (512, 2048):
         x = torch.randn(8, S, 1024, device="cuda", dtype=torch.float16, generator=g)
         c = cos(blk.forward_prefill(x, True), blk.forward_prefill(x, False))
-        t8 = timed_steps(torch, lambda: blk.forward_prefill(x, True), 10, 3) / 10
-        t16 = timed_steps(torch, lambda: blk.forward_prefill(x, False), 10, 3) / 10
+        t8 = timed_settled(torch, lambda: blk.forward_prefill(x, True), 10, 3) / 10
+        t16 = timed_settled(torch, lambda: blk.forward_prefill(x, False), 10, 3) / 10
         out.append({"workload": f"block prefill B8 H16 Dh64 d_ff4096 S{S}", "int8_ms": t8 * 1e3, "fp16_ms": t16 * 1e3,
                     "speedup_vs_fp16": t16 / t8, "cos_vs_fp16": c})
     for Skv in (8192, 32768):
@@ -564,8 +588,8 @@ def block_sweep(torch):
         V = torch.randn(128, 16, Skv, 64, device="cuda", dtype=torch.float16, generator=g)
         kv8 = blk.quantize_kv(K, V)
         c = cos(blk.forward_decode(x, kv8, True), blk.forward_decode(x, (K, V), False))
-        t8 = timed_steps(torch, lambda: blk.forward_decode(x, kv8, True), 10, 3) / 10
-        t16 = timed_steps(torch, lambda: blk.forward_decode(x, (K, V), False), 10, 3) / 10
+        t8 = timed_settled(torch, lambda: blk.forward_decode(x, kv8, True), 10, 3) / 10
+        t16 = timed_settled(torch, lambda: blk.forward_decode(x, (K, V), False), 10, 3) / 10
         out.append({"workload": f"block decode B128 H16 Dh64 d_ff4096 Skv{Skv}", "int8_ms": t8 * 1e3,
                     "fp16_ms": t16 * 1e3, "speedup_vs_fp16": t16 / t8, "cos_vs_fp16": c})
         del K, V, kv8
@@ -582,7 +606,7 @@ def quantiser_and_prefill_sweep(torch, ext):
                                 (torch.float16, 65536, 1024, "MLP activations, fp16 in")):
         x = torch.randn(rows, cols, device="cuda", dtype=dt)
         steps = 20
-        el = timed_steps(torch, lambda: ext.quantize_per_token(x), steps, 3)
+        el = timed_settled(torch, lambda: ext.quantize_per_token(x), steps, 3)
         byts = rows * cols * (x.element_size() + 1) + rows * 4
         out.append({"workload": f"quantize_per_token [{rows}, {cols}] ({tag})", "us_per_step": el / steps * 1e6,
                     "GBps": byts * steps / el / 1e9, "l2_resident": byts < 100e6})
@@ -592,8 +616,8 @@ def quantiser_and_prefill_sweep(torch, ext):
     for rows, cols in ((16384, 1024), (131072, 1024)):
         x = torch.randn(rows, cols, device="cuda", dtype=torch.float16)
         steps = 20
-        el = timed_steps(torch, lambda: ext.layernorm_quantize(x), steps, 3)
-        el2 = timed_steps(torch, lambda: ext.quantize_per_token(F.layer_norm(x, (cols,))), steps, 3)
+        el = timed_settled(torch, lambda: ext.layernorm_quantize(x), steps, 3)
+        el2 = timed_settled(torch, lambda: ext.quantize_per_token(F.layer_norm(x, (cols,))), steps, 3)
         byts = rows * cols * 3 + rows * 4
         out.append({"workload": f"layernorm_quantize [{rows}, {cols}] fp16 (LayerNorm + per-token quantiser, one pass)",
                     "us_per_step": el / steps * 1e6, "GBps": byts * steps / el / 1e9,
@@ -608,7 +632,7 @@ def quantiser_and_prefill_sweep(torch, ext):
             xi, sx = ext.quantize_per_token(torch.randn(b, h, s, d, device="cuda", dtype=torch.float16, generator=g))
             t.extend([xi, sx.reshape(-1).contiguous()])
         steps = 10
-        el = timed_steps(torch, lambda: ext.int8_attention_forward(t[0], t[2], t[4], t[1], t[3], t[5]), steps, 3)
+        el = timed_settled(torch, lambda: ext.int8_attention_forward(t[0], t[2], t[4], t[1], t[3], t[5]), steps, 3)
         ops = 4.0 * b * h * s * s * d
         out.append({"workload": f"prefill int8 attention B{b} H{h} S{s} D{d}", "us_per_step": el / steps * 1e6,
                     "TOPS": ops * steps / el / 1e12})
@@ -649,8 +673,8 @@ def mlp_sweep(torch, ext, cabi):
                                                 osc.data_ptr(), None, M, dm, dff, flags, ws.data_ptr(), wb, st))
 
             steps = 50
-            el = timed_steps(torch, prepacked, steps, 5)
-            el2 = timed_steps(torch, lambda: ext.int8_mlp_forward_per_channel_bias(xi, w1i, w2i, sxf, s1, s2, b1),
+            el = timed_settled(torch, prepacked, steps, 5)
+            el2 = timed_settled(torch, lambda: ext.int8_mlp_forward_per_channel_bias(xi, w1i, w2i, sxf, s1, s2, b1),
                               steps, 5)
             ops = 4.0 * M * dm * dff
             out.append({"workload": f"cfg4 fused INT8 MLP M={M} {dm}->{dff}->{dm}",
