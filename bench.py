@@ -177,6 +177,8 @@ PROFILE_CASES = {
     "quantize_f32_64": (3145728, 64),      # rows, cols: 1.0 GB through the per-token quantiser
     "prefill_d64": (2, 8, 4096, 64),       # B, H, S, D: 512 CTAs of 128 query rows
     "prefill_d128": (2, 8, 4096, 128),
+    "paged_d64_p64": (8, 12, 64, 16384, 64),   # B, H, D, longest request, page: lengths 2048..16384, shuffled table
+    "lnquant_f16_1024": (131072, 1024),    # rows, cols: 268 MB in, 134 MB of codes out
 }
 
 
@@ -192,6 +194,34 @@ def run_profile_case(name):
         torch.cuda.synchronize()
         print(f"profile case {name}: [{rows}, {cols}] fp32, bytes per launch {rows * cols * 5 + rows * 4}, "
               f"checksum {float(sc.sum()):.4f}")
+        return
+    if name.startswith("lnquant"):
+        rows, cols = PROFILE_CASES[name]
+        x = torch.randn(rows, cols, device="cuda", dtype=torch.float16)
+        for _ in range(3):
+            qi, sc = ext.layernorm_quantize(x)
+        torch.cuda.synchronize()
+        print(f"profile case {name}: [{rows}, {cols}] fp16, bytes per launch {rows * cols * 3 + rows * 4}, "
+              f"checksum {float(sc.sum()):.4f}")
+        return
+    if name.startswith("paged"):
+        b, h, d, s, page = PROFILE_CASES[name]
+        g = torch.Generator(device="cuda").manual_seed(0)
+        Qi, sQ = ext.quantize_per_token(torch.randn(b, h, d, device="cuda", dtype=torch.float16, generator=g))
+        npp = s // page
+        pages = b * npp
+        Kp = torch.randint(-127, 128, (pages, h, page, d), dtype=torch.int8, device="cuda", generator=g)
+        Vp = torch.randint(-127, 128, (pages, h, page, d), dtype=torch.int8, device="cuda", generator=g)
+        sKp = torch.rand(pages, h, page, device="cuda", generator=g) * 0.02 + 0.01
+        sVp = torch.rand(pages, h, page, device="cuda", generator=g) * 0.02 + 0.01
+        table = torch.randperm(pages, device="cuda", generator=g).to(torch.int32).view(b, npp).contiguous()
+        lens = torch.linspace(2048, s, b).to(torch.int32)
+        seq = lens.cuda()
+        for _ in range(5):
+            out = ext.int8_decode_attention_paged(Qi, Kp, Vp, sQ.reshape(-1).contiguous(), sKp, sVp, table, seq, s)
+        torch.cuda.synchronize()
+        print(f"profile case {name}: B{b} H{h} D{d} page {page}, lengths {lens.tolist()}, "
+              f"K+V bytes per launch {2 * h * d * int(lens.sum())}, checksum {float(out.float().sum()):.4f}")
         return
     if name.startswith("prefill"):
         b, h, sq, d = PROFILE_CASES[name]

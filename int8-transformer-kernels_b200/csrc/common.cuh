@@ -173,6 +173,13 @@ __device__ __forceinline__ f32x2 pack2(float a, float b) {
     return *reinterpret_cast<f32x2*>(&t);
 }
 __device__ __forceinline__ float2 unpack2(f32x2 v) { return *reinterpret_cast<float2*>(&v); }
+
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     f32x2 d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));

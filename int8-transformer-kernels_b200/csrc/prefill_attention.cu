@@ -103,13 +103,6 @@ dequant_v_kernel(const int8_t* __restrict__ V, const float* __restrict__ sV, __h
     }
 }
 
-// three-input maximum (one instruction on sm_100)
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
