@@ -61,8 +61,9 @@ struct PrefillCfg {
     static constexpr int OFF_BARS = OFF_XCH + 2 * 2 * kQT * 4;
     static constexpr int NUM_BARS = 22;
     static constexpr int SMEM_BYTES = 1024 + OFF_BARS + NUM_BARS * 8 + 16;
-    static constexpr int TMEM_COLS = 512;                  // S0 | S1 | O (D columns)
+    static constexpr int TMEM_COLS = 512;                  // S0 | S1 | O (D columns) | P0 | P1
     static constexpr int TM_S0 = 0, TM_S1 = 128, TM_O = 256;
+    static constexpr int TM_P = 384;                       // two fp16 P tiles, 64 columns each (two values per column)
 };
 
 enum Bar : int {
@@ -213,11 +214,11 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 const uint64_t db0 = smem_desc_sw128_mn(v16, Cfg::SLAB_BYTES);
 #pragma unroll
                 for (int i = 0; i < kKT / 16; ++i) {
-                    // A: K-major fp16, 64-wide blocks 16 KB apart, 32 bytes per step inside a block
-                    const uint64_t da = smem_desc_sw128(base_s + Cfg::OFF_P + (t & 1) * Cfg::P_BYTES + (i >> 2) * Cfg::SLAB_BYTES) + 2 * (i & 3);
+                    // A: P in tensor memory, 8 columns (16 KV positions as fp16 pairs) per step
+                    const uint32_t ta = tmem_base + Cfg::TM_P + (t & 1) * 64 + i * 8;
                     // B: MN-major fp16, 16 rows of 128 bytes per step
                     const uint64_t db = db0 + (uint64_t)(128 * i);
-                    mma_f16(tmem_base + Cfg::TM_O, da, db, idesc_pv, (t | i) != 0);
+                    mma_f16_ta(tmem_base + Cfg::TM_O, ta, db, idesc_pv, (t | i) != 0);
                 }
                 tc_commit(bar(B_V16EMPTY + (t & 1)));
                 tc_commit(bar(B_PVDONE + (t & 1)));
@@ -260,7 +261,6 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         const float qscale = sQ[min((long long)row_base + q0 + r, total_rows - 1)] * score_scale_log2;     // > 0
         const f32x2 qs2 = pack2(qscale, qscale);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        unsigned char* prow0 = base + Cfg::OFF_P + half * Cfg::SLAB_BYTES + r * 128;  // this row in this half's 64-wide K block
         // int32 -> fp32 without the conversion unit: |q.k| <= 127*127*128 < 2^22, so adding the
         // score to the bit pattern of 1.5*2^23 and subtracting 1.5*2^23 as a float is exact
         constexpr uint32_t kMagicI = 0x4B400000u;
@@ -313,14 +313,15 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 mx = fmaxf(mx, fmaxf(v.x, v.y));
             }
         };
-        // p = 2^(y*qscale - m_ref) for 8 columns as one 16-byte chunk of fp16 (sV is already in V16)
-        auto exp8 = [&](const f32x2* y4, f32x2 nm2, unsigned char* dst) {
+        // p = 2^(y*qscale - m_ref) for 8 columns, stored as four fp16 pairs into this row's lane of the
+        // P tile in tensor memory (sV is already in V16)
+        auto exp8 = [&](const f32x2* y4, f32x2 nm2, uint32_t dst) {
             const float2 a = unpack2(fma2(y4[0], qs2, nm2)), b = unpack2(fma2(y4[1], qs2, nm2));
             const float2 c = unpack2(fma2(y4[2], qs2, nm2)), d = unpack2(fma2(y4[3], qs2, nm2));
             const float p0 = ex2_approx(a.x), p1 = ex2_approx(a.y), p2 = ex2_approx(b.x), p3 = ex2_approx(b.y);
             const float p4 = ex2_approx(c.x), p5 = ex2_approx(c.y), p6 = ex2_approx(d.x), p7 = ex2_approx(d.y);
             l2 = add2(l2, add2(add2(pack2(p0, p1), pack2(p2, p3)), add2(pack2(p4, p5), pack2(p6, p7))));
-            *reinterpret_cast<uint4*>(dst) = make_uint4(pack_h2(p0, p1), pack_h2(p2, p3), pack_h2(p4, p5), pack_h2(p6, p7));
+            tmem_st4(dst, pack_h2(p0, p1), pack_h2(p2, p3), pack_h2(p4, p5), pack_h2(p6, p7));
         };
 
         // ---- prologue: scores of tile 0 into registers ----
@@ -395,7 +396,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             // ---- exponentials of this tile (special-function unit) interleaved, 8 columns at a time,
             // with the conversion of the NEXT tile's scores (integer and FMA pipes), which take over
             // the registers the exponentials have just released ----
-            unsigned char* prow = prow0 + st * Cfg::P_BYTES;
+            const uint32_t prow = lane_addr + Cfg::TM_P + st * 64 + half * 32;   // this thread's 32 columns of P
             const f32x2 nm2 = pack2(-m_ref, -m_ref);
             mx = -INFINITY;
             if (has_next) {
@@ -416,7 +417,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int c = cc * 2 + h;        // 16-byte chunk of P / 8 columns
-                        exp8(&y[c * 4], nm2, prow + ((c ^ (r & 7)) << 4));
+                        exp8(&y[c * 4], nm2, prow + c * 4);
                         convert8(&sr[cc & 1][h * 8], ksc + c * 8, &y[c * 4], mx);
                     }
                 }
@@ -426,11 +427,11 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 if (lane == 0) mbar_arrive(bar(B_SEMPTY + (st ^ 1)));
             } else {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) exp8(&y[c * 4], nm2, prow + ((c ^ (r & 7)) << 4));
+                for (int c = 0; c < 8; ++c) exp8(&y[c * 4], nm2, prow + c * 4);
             }
             if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 3);
+            tmem_st_wait();                              // P is in tensor memory before the MMA thread is told
             tc_fence_before();
-            fence_proxy_async();                         // generic-proxy writes of P visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_PFULL + st));
             if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 4);

@@ -157,6 +157,18 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64
         : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem], fp16 x fp16 -> fp32: A is read from tensor memory, row i of the
+// M = 128 rows in lane i, two consecutive K elements per 32-bit column (8 columns per K = 16 step).
+__device__ __forceinline__ void mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Instruction descriptor for kind::f16: D = f32 (1 @ bit 4), A = B = fp16 (0 @ bits 7, 10),
 // A K-major, B optionally MN-major (bit 16), N/8 @ bit 17, M/16 @ bit 24.
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool b_mn_major) {
@@ -185,6 +197,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
           "r"(r[15])
         : "memory");
+}
+// 4 registers per thread -> 32 lanes x 4 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
