@@ -26,8 +26,12 @@
 //   tcgen05.st) rare.  The exponentials of tile j (special-function unit) are
 //   interleaved, eight columns at a time, with the conversion of tile j+1's scores
 //   (integer and FMA pipes), which take over the registers just released; Q.K^T
-//   therefore runs two tiles ahead of P.V.  P*sV goes as fp16 into one of two
-//   swizzled K-major operand buffers.  Packed fp32x2 arithmetic throughout.
+//   therefore runs two tiles ahead of P.V.  P goes as fp16 pairs into one of two
+//   64-column blocks of tensor memory (tcgen05.st), from where the P.V instruction reads
+//   its A operand: no shared-memory round trip, no swizzle arithmetic, no proxy fence.
+//   Packed fp32x2 arithmetic throughout.
+// * K and V16 tiles move through rings of kRing stages, so a late tile does not hold up the
+//   single thread that issues both products in turn.
 // * Every mbarrier wait is bounded; on expiry a status word is set and all
 //   roles fall through to the common exit, which frees tensor memory.
 //
@@ -44,22 +48,21 @@ constexpr int kQT = 128;                 // query rows per CTA
 constexpr int kKT = 128;                 // KV positions per tile
 constexpr int kSoftmaxWarps = 8;         // two per TMEM lane quarter: each thread owns half of a score row
 constexpr int kPrefillThreads = (2 + kSoftmaxWarps) * 32;   // TMA, MMA, 8 softmax warps
+constexpr int kRing = 3;                 // stages of the K ring and of the V16 ring
 constexpr float kLazyStep = 8.0f;        // log2 units the true max may run ahead of the reference max
 
 template <int D>
 struct PrefillCfg {
     static constexpr int TILE_BYTES = kKT * D;             // one int8 tile (Q, K or raw V)
     static constexpr int V16_BYTES = kKT * D * 2;          // fp16 V tile
-    static constexpr int P_BYTES = kQT * kKT * 2;          // fp16 P tile: two 64-wide K blocks
     static constexpr int SLAB_BYTES = kKT * 128;           // 128 rows of 128 bytes
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + TILE_BYTES;
-    static constexpr int OFF_V16 = OFF_K + 2 * TILE_BYTES;
-    static constexpr int OFF_P = OFF_V16 + 2 * V16_BYTES;
-    static constexpr int OFF_SCALES = OFF_P + 2 * P_BYTES; // 8 warps x 2 tiles x sK[64] fp32
+    static constexpr int OFF_V16 = OFF_K + kRing * TILE_BYTES;
+    static constexpr int OFF_SCALES = OFF_V16 + kRing * V16_BYTES; // 8 warps x 2 tiles x sK[64] fp32
     static constexpr int OFF_XCH = OFF_SCALES + kSoftmaxWarps * 2 * 64 * 4;    // [2][2 halves][128 rows] fp32
     static constexpr int OFF_BARS = OFF_XCH + 2 * 2 * kQT * 4;
-    static constexpr int NUM_BARS = 22;
+    static constexpr int NUM_BARS = 24;
     static constexpr int SMEM_BYTES = 1024 + OFF_BARS + NUM_BARS * 8 + 16;
     static constexpr int TMEM_COLS = 512;                  // S0 | S1 | O (D columns) | P0 | P1
     static constexpr int TM_S0 = 0, TM_S1 = 128, TM_O = 256;
@@ -68,13 +71,13 @@ struct PrefillCfg {
 
 enum Bar : int {
     B_QFULL = 0,
-    B_KFULL = 1,      // [2]
-    B_KEMPTY = 3,     // [2]
-    B_SFULL = 9,      // [2]
-    B_SEMPTY = 11,    // [2]
-    B_PFULL = 13,     // [2]
-    B_V16FULL = 15,   // [2]
-    B_V16EMPTY = 17,  // [2]
+    B_KFULL = 1,      // [kRing]
+    B_KEMPTY = 4,     // [kRing]
+    B_SFULL = 7,      // [2]
+    B_SEMPTY = 9,     // [2]
+    B_PFULL = 11,     // [2]
+    B_V16FULL = 13,   // [kRing]
+    B_V16EMPTY = 16,  // [kRing]
     B_PVDONE = 19,    // [2]
 };
 
@@ -148,13 +151,15 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 
     if (threadIdx.x == 0) {
         mbar_init(bar(B_QFULL), 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kRing; ++i) {
             mbar_init(bar(B_KFULL + i), 1);
             mbar_init(bar(B_KEMPTY + i), 1);
-            mbar_init(bar(B_SFULL + i), 1);
-            mbar_init(bar(B_SEMPTY + i), kSoftmaxWarps);
             mbar_init(bar(B_V16FULL + i), 1);
             mbar_init(bar(B_V16EMPTY + i), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(B_SFULL + i), 1);
+            mbar_init(bar(B_SEMPTY + i), kSoftmaxWarps);
             mbar_init(bar(B_PFULL + i), kSoftmaxWarps);
             mbar_init(bar(B_PVDONE + i), 1);
         }
@@ -175,8 +180,8 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             mbar_expect_tx(bar(B_QFULL), Cfg::TILE_BYTES);
             tma_load_2d(base_s + Cfg::OFF_Q, &tmQ, 0, row_base + q0, bar(B_QFULL));
             for (int j = 0; j < nt; ++j) {
-                const int st = j & 1;
-                if (!mbar_wait_spin_bounded(bar(B_KEMPTY + st), ((j >> 1) & 1) ^ 1)) {
+                const int st = j % kRing;
+                if (!mbar_wait_spin_bounded(bar(B_KEMPTY + st), ((j / kRing) & 1) ^ 1)) {
                     atomicExch(status, kDeviceTimeoutMagic);
                     break;
                 }
@@ -186,8 +191,8 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             }
         } else if (lane == 1) {
             for (int j = 0; j < nt; ++j) {
-                const int st = j & 1;
-                if (!mbar_wait_spin_bounded(bar(B_V16EMPTY + st), ((j >> 1) & 1) ^ 1)) {
+                const int st = j % kRing;
+                if (!mbar_wait_spin_bounded(bar(B_V16EMPTY + st), ((j / kRing) & 1) ^ 1)) {
                     atomicExch(status, kDeviceTimeoutMagic);
                     break;
                 }
@@ -208,9 +213,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             auto issue_pv = [&](int t) -> bool {
                 // O (+)= P_t . V_t : 8 steps of 16 KV positions
                 if (!mbar_wait_spin_bounded(bar(B_PFULL + (t & 1)), (t >> 1) & 1)) return false;
-                if (!mbar_wait_spin_bounded(bar(B_V16FULL + (t & 1)), (t >> 1) & 1)) return false;
+                const int vs = t % kRing;                // stage of the V16 ring
+                if (!mbar_wait_spin_bounded(bar(B_V16FULL + vs), (t / kRing) & 1)) return false;
                 tc_fence_after();
-                const uint32_t v16 = base_s + Cfg::OFF_V16 + (t & 1) * Cfg::V16_BYTES;
+                const uint32_t v16 = base_s + Cfg::OFF_V16 + vs * Cfg::V16_BYTES;
                 const uint64_t db0 = smem_desc_sw128_mn(v16, Cfg::SLAB_BYTES);
 #pragma unroll
                 for (int i = 0; i < kKT / 16; ++i) {
@@ -220,7 +226,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                     const uint64_t db = db0 + (uint64_t)(128 * i);
                     mma_f16_ta(tmem_base + Cfg::TM_O, ta, db, idesc_pv, (t | i) != 0);
                 }
-                tc_commit(bar(B_V16EMPTY + (t & 1)));
+                tc_commit(bar(B_V16EMPTY + vs));
                 tc_commit(bar(B_PVDONE + (t & 1)));
                 return true;
             };
@@ -228,20 +234,21 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             // while they exponentiate tile j, so S(j+1) has to be on its way before P(j-1) is complete.
             for (int j = 0; j < nt + 2 && ok; ++j) {
                 if (j < nt) {
-                    const int st = j & 1;
-                    if (!mbar_wait_spin_bounded(bar(B_KFULL + st), (j >> 1) & 1) ||
+                    const int st = j & 1;                // score buffer
+                    const int kst = j % kRing;           // stage of the K ring
+                    if (!mbar_wait_spin_bounded(bar(B_KFULL + kst), (j / kRing) & 1) ||
                         !mbar_wait_spin_bounded(bar(B_SEMPTY + st), ((j >> 1) & 1) ^ 1)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t ks = base_s + Cfg::OFF_K + st * Cfg::TILE_BYTES;
+                    const uint32_t ks = base_s + Cfg::OFF_K + kst * Cfg::TILE_BYTES;
                     const uint64_t da = (D == 128) ? smem_desc_sw128(base_s + Cfg::OFF_Q) : smem_desc_sw64(base_s + Cfg::OFF_Q);
                     const uint64_t db = (D == 128) ? smem_desc_sw128(ks) : smem_desc_sw64(ks);
 #pragma unroll
                     for (int k = 0; k < D / 32; ++k)
                         mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * k, db + 2 * k, idesc_qk, k != 0);
-                    tc_commit(bar(B_KEMPTY + st));
+                    tc_commit(bar(B_KEMPTY + kst));
                     tc_commit(bar(B_SFULL + st));
                     I8TK_PTRACE(256 + 4 * j);
                 }
