@@ -120,3 +120,39 @@ def test_paged_request_without_positions_gives_zeros():
         assert torch.count_nonzero(out[gone]).item() == 0
         keep = [b for b in range(4) if b != gone]
         assert (out[keep].float() - full[keep].float()).abs().max().item() < 2e-3   # other runs, other merge order
+
+
+def test_paged_more_requests_than_the_plan_keeps_in_shared_memory():
+    """5000 requests: the plan kernel searches its prefix sums in global memory (it keeps up to
+    4096 in shared memory).  Pages are shared between requests (the cache is only read), the
+    result must match the same requests run in two batches of 2500 and, for a few of them, the
+    contiguous op on the gathered pages."""
+    e = ext()
+    B, H, D, page, num_pages, max_pages = 5000, 2, 64, 16, 256, 20
+    g = torch.Generator(device="cuda").manual_seed(5)
+    Kp = torch.randint(-127, 128, (num_pages, H, page, D), dtype=torch.int8, device="cuda", generator=g)
+    Vp = torch.randint(-127, 128, (num_pages, H, page, D), dtype=torch.int8, device="cuda", generator=g)
+    sKp = torch.rand(num_pages, H, page, device="cuda", generator=g) * 0.02 + 0.005
+    sVp = torch.rand(num_pages, H, page, device="cuda", generator=g) * 0.02 + 0.005
+    table = torch.randint(0, num_pages, (B, max_pages), device="cuda", generator=g).to(torch.int32)
+    seq = torch.randint(1, max_pages * page + 1, (B,), device="cuda", generator=g).to(torch.int32)
+    Qi, sQ = e.quantize_per_token(torch.randn(B, H, D, device="cuda", generator=g))
+    sq = sQ.reshape(-1).contiguous()
+    S = max_pages * page
+    out = e.int8_decode_attention_paged(Qi, Kp, Vp, sq, sKp, sVp, table, seq, S)
+    assert not torch.isnan(out).any()
+    for lo in (0, 2500):
+        part = e.int8_decode_attention_paged(Qi[lo:lo + 2500].contiguous(), Kp, Vp, sq[lo * H:(lo + 2500) * H].contiguous(),
+                                             sKp, sVp, table[lo:lo + 2500].contiguous(), seq[lo:lo + 2500].contiguous(), S)
+        assert (out[lo:lo + 2500].float() - part.float()).abs().max().item() < 2e-3
+    for b in (0, 1234, 4097, 4999):
+        L = int(seq[b])
+        n = (L + page - 1) // page
+        ids = table[b, :n].long()
+        Kc = Kp[ids].permute(1, 0, 2, 3).reshape(H, n * page, D)[:, :L].contiguous()
+        Vc = Vp[ids].permute(1, 0, 2, 3).reshape(H, n * page, D)[:, :L].contiguous()
+        sKc = sKp[ids].permute(1, 0, 2).reshape(H, n * page)[:, :L].contiguous()
+        sVc = sVp[ids].permute(1, 0, 2).reshape(H, n * page)[:, :L].contiguous()
+        same = e.int8_decode_attention_forward(Qi[b:b + 1].contiguous(), Kc[None], Vc[None], sQ[b:b + 1].reshape(-1),
+                                               sKc.reshape(-1), sVc.reshape(-1))
+        assert (out[b:b + 1].float() - same.float()).abs().max().item() < 2e-3
