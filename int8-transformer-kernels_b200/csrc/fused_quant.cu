@@ -5,7 +5,8 @@
 // * layernorm_quantize: LayerNorm (no affine, eps 1e-5, as F.layer_norm(x, (d,)) in
 //   bench/bench_block.py:93-94) of an fp16 row, rounded to fp16 as torch stores it, then the
 //   per-token quantiser's arithmetic (tests/test_int8.py:47-63) on that value -- one pass over
-//   the row instead of LayerNorm + abs/amax/div/round/clamp/cast kernels.
+//   the row instead of LayerNorm + abs/amax/div/round/clamp/cast kernels.  Rows up to 2048 wide
+//   take the code as round(x * (1/scale)) in one FMA (see quant4_fma2); wider rows divide.
 // * kv_append_quantize: the new token's K and V rows ([B*H, D], fp16) quantised per token and
 //   written straight into the INT8 cache at their position, with their scales -- quantise on
 //   write, no intermediate tensors.
@@ -115,26 +116,6 @@ layernorm_quantize_kernel(const __half* __restrict__ x, int8_t* __restrict__ q, 
     }
 }
 
-// Four codes from four fp32 values with a row-wide reciprocal: x * rcp is within 1.6e-5 of the
-// exact quotient and the IEEE quotient within 0.8e-5, so only products within 1e-4 of a rounding
-// tie are redone with the IEEE division; rounding is the addition of 1.5 * 2^23 (code = low byte).
-__device__ __forceinline__ uint32_t quant4_rcp(float x0, float x1, float x2, float x3, float scale, float rcp) {
-    const f32x2 rcp2 = pack2(rcp, rcp);
-    const f32x2 magic2 = pack2(12582912.f, 12582912.f), nmagic2 = pack2(-12582912.f, -12582912.f);
-    const f32x2 mone2 = pack2(-1.f, -1.f);
-    const f32x2 qa = mul2(pack2(x0, x1), rcp2), qb = mul2(pack2(x2, x3), rcp2);
-    const f32x2 ra = add2(qa, magic2), rb = add2(qb, magic2);
-    const float2 da = unpack2(fma2(add2(ra, nmagic2), mone2, qa));
-    const float2 db = unpack2(fma2(add2(rb, nmagic2), mone2, qb));
-    const float2 fa = unpack2(ra), fb = unpack2(rb);
-    uint32_t w = prmt(prmt(__float_as_uint(fa.x), __float_as_uint(fa.y), 0x0040u),
-                      prmt(__float_as_uint(fb.x), __float_as_uint(fb.y), 0x0040u), 0x5410u);
-    if (fmaxf(fmaxf(fabsf(da.x), fabsf(da.y)), fmaxf(fabsf(db.x), fabsf(db.y))) > 0.4999f)
-        w = (uint32_t)(quant_exact(x0, scale) & 0xff) | ((uint32_t)(quant_exact(x1, scale) & 0xff) << 8) |
-            ((uint32_t)(quant_exact(x2, scale) & 0xff) << 16) | ((uint32_t)(quant_exact(x3, scale) & 0xff) << 24);
-    return w;
-}
-
 __device__ __forceinline__ float warp_sum_f(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -146,24 +127,16 @@ __device__ __forceinline__ float warp_max_f(float v) {
     return v;
 }
 
-// quant4_rcp on two packed pairs; the tie test takes the largest of the four distances with two
-// three-input maxima.
-__device__ __forceinline__ uint32_t quant4_rcp2(f32x2 a, f32x2 b, float scale, f32x2 rcp2) {
-    const f32x2 magic2 = pack2(12582912.f, 12582912.f), nmagic2 = pack2(-12582912.f, -12582912.f);
-    const f32x2 mone2 = pack2(-1.f, -1.f);
-    const f32x2 qa = mul2(a, rcp2), qb = mul2(b, rcp2);
-    const f32x2 ra = add2(qa, magic2), rb = add2(qb, magic2);
-    const float2 da = unpack2(fma2(add2(ra, nmagic2), mone2, qa));
-    const float2 db = unpack2(fma2(add2(rb, nmagic2), mone2, qb));
-    const float2 fa = unpack2(ra), fb = unpack2(rb);
-    uint32_t w = prmt(prmt(__float_as_uint(fa.x), __float_as_uint(fa.y), 0x0040u),
-                      prmt(__float_as_uint(fb.x), __float_as_uint(fb.y), 0x0040u), 0x5410u);
-    if (max3(max3(fabsf(da.x), fabsf(da.y), fabsf(db.x)), fabsf(db.y), 0.f) > 0.4999f) {
-        const float2 xa = unpack2(a), xb = unpack2(b);
-        w = (uint32_t)(quant_exact(xa.x, scale) & 0xff) | ((uint32_t)(quant_exact(xa.y, scale) & 0xff) << 8) |
-            ((uint32_t)(quant_exact(xb.x, scale) & 0xff) << 16) | ((uint32_t)(quant_exact(xb.y, scale) & 0xff) << 24);
-    }
-    return w;
+// Four codes from two packed pairs: code = low byte of fma(x, 1/scale, 1.5 * 2^23), one rounding.
+// No tie test here (the plain quantiser has one and is bit-exact): x * (1/scale) is within 1.6e-5
+// of the exact quotient, so a code can differ from the divide-then-round result only for
+// quotients that close to k + 0.5, about 3e-5 of all elements, while the normalised value itself
+// differs from torch's in its last bit far more often than that.
+__device__ __forceinline__ uint32_t quant4_fma2(f32x2 a, f32x2 b, f32x2 rcp2) {
+    const f32x2 magic2 = pack2(12582912.f, 12582912.f);
+    const float2 fa = unpack2(fma2(a, rcp2, magic2)), fb = unpack2(fma2(b, rcp2, magic2));
+    return prmt(prmt(__float_as_uint(fa.x), __float_as_uint(fa.y), 0x0040u),
+                prmt(__float_as_uint(fb.x), __float_as_uint(fb.y), 0x0040u), 0x5410u);
 }
 
 // One warp per row, the row in registers (NV 16-byte vectors per lane) as packed fp32 pairs, so
@@ -253,8 +226,8 @@ layernorm_quantize_warp_kernel(const __half* __restrict__ x, int8_t* __restrict_
         for (int j = 0; j < NV; ++j) {
             const int vi = lane + j * 32;
             if (vi < nvec)
-                *reinterpret_cast<uint2*>(qr + vi * 8) = make_uint2(quant4_rcp2(v[j][0], v[j][1], scale, rcp2),
-                                                                    quant4_rcp2(v[j][2], v[j][3], scale, rcp2));
+                *reinterpret_cast<uint2*>(qr + vi * 8) = make_uint2(quant4_fma2(v[j][0], v[j][1], rcp2),
+                                                                    quant4_fma2(v[j][2], v[j][3], rcp2));
         }
     }
 }
