@@ -63,22 +63,25 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 // 0.8e-5: the two can only round to different codes when x * rcp lies within 2.4e-5 of a
 // rounding tie.  Quotients within 1e-4 of a tie (about 0.02 % of elements) are therefore redone
 // with the IEEE division and the rest need nothing more than the multiply.  Rounding to nearest
-// even is the addition of 1.5 * 2^23, which leaves the code in the low byte of the sum;
+// even is the addition of 1.5 * 2^23, which leaves the code in the low byte of the sum (product
+// and addition are one FMA; the distance from a tie is a second FMA of the same product with
+// minus the code);
 // |x / scale| <= 127 by construction of the scale, so no clamp is needed.  Packed fp32x2
 // arithmetic throughout: no conversion or rounding instruction (those run at a quarter of the
 // FMA rate).
 __device__ __forceinline__ uint32_t quant4(float x0, float x1, float x2, float x3, float scale, float rcp) {
     const f32x2 rcp2 = pack2(rcp, rcp);
-    const f32x2 magic2 = pack2(12582912.f, 12582912.f), nmagic2 = pack2(-12582912.f, -12582912.f);
+    const f32x2 magic2 = pack2(12582912.f, 12582912.f);
     const f32x2 mone2 = pack2(-1.f, -1.f);
-    const f32x2 qa = mul2(pack2(x0, x1), rcp2), qb = mul2(pack2(x2, x3), rcp2);
-    const f32x2 ra = add2(qa, magic2), rb = add2(qb, magic2);          // low byte = code
-    const float2 da = unpack2(fma2(add2(ra, nmagic2), mone2, qa));     // q - rne(q)
-    const float2 db = unpack2(fma2(add2(rb, nmagic2), mone2, qb));
+    const f32x2 xa = pack2(x0, x1), xb = pack2(x2, x3);
+    const f32x2 ra = fma2(xa, rcp2, magic2), rb = fma2(xb, rcp2, magic2);     // low byte = code n
+    // distance of the quotient from that code: x * rcp - n, with -n = magic - r (exact)
+    const float2 da = unpack2(fma2(xa, rcp2, fma2(ra, mone2, magic2)));
+    const float2 db = unpack2(fma2(xb, rcp2, fma2(rb, mone2, magic2)));
     const float2 fa = unpack2(ra), fb = unpack2(rb);
     uint32_t w = prmt(prmt(__float_as_uint(fa.x), __float_as_uint(fa.y), 0x0040u),
                       prmt(__float_as_uint(fb.x), __float_as_uint(fb.y), 0x0040u), 0x5410u);
-    if (fmaxf(fmaxf(fabsf(da.x), fabsf(da.y)), fmaxf(fabsf(db.x), fabsf(db.y))) > 0.4999f)
+    if (max3(max3(fabsf(da.x), fabsf(da.y), fabsf(db.x)), fabsf(db.y), 0.f) > 0.4999f)
         w = pack4(quant1(x0, scale), quant1(x1, scale), quant1(x2, scale), quant1(x3, scale));
     return w;
 }
