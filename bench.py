@@ -601,6 +601,24 @@ def paged_sweep(torch, ext):
                         "us_per_step": el / steps * 1e6, "GBps": gbps, "pct_of_8TBps_per_gpu": gbps / 80.0})
         del Kp, Vp, sKp, sVp
         torch.cuda.empty_cache()
+    # config 2's geometry (D = 128) through 64-position pages, all requests at full length
+    B, H, D, S, page = 64, 32, 128, 8192, 64
+    Qi, sQ = ext.quantize_per_token(torch.randn(B, H, D, device="cuda", dtype=torch.float16, generator=g))
+    npp = S // page
+    pages = B * npp
+    Kp = torch.randint(-127, 128, (pages, H, page, D), dtype=torch.int8, device="cuda", generator=g)
+    Vp = torch.randint(-127, 128, (pages, H, page, D), dtype=torch.int8, device="cuda", generator=g)
+    sKp = torch.rand(pages, H, page, device="cuda", generator=g) * 0.02 + 0.01
+    sVp = torch.rand(pages, H, page, device="cuda", generator=g) * 0.02 + 0.01
+    table = torch.randperm(pages, device="cuda", generator=g).to(torch.int32).view(B, npp).contiguous()
+    seq = torch.full((B,), S, dtype=torch.int32, device="cuda")
+    sq = sQ.reshape(-1).contiguous()
+    el = timed_settled(torch, lambda: ext.int8_decode_attention_paged(Qi, Kp, Vp, sq, sKp, sVp, table, seq, S), 20, 3)
+    gbps = kv_bytes(B, H, S, D) * 20 / el / 1e9
+    out.append({"workload": f"paged decode B{B} H{H} D{D} ctx{S}, page {page}, shuffled page table, all requests at full length",
+                "us_per_step": el / 20 * 1e6, "GBps": gbps, "pct_of_8TBps_per_gpu": gbps / 80.0})
+    del Kp, Vp, sKp, sVp
+    torch.cuda.empty_cache()
     return out
 
 
