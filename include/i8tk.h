@@ -44,13 +44,21 @@ const char* i8tk_last_error(void);
 int i8tk_version(void);
 
 /* Every device-side wait in this library is bounded.  A kernel that gives up
- * stores a marker in the first 4 bytes of the workspace it was given and
- * returns normally (the context stays usable).  i8tk_check_status_word copies
- * that word back (it synchronises `stream`) and returns
+ * returns normally (the context stays usable) after recording the fact in the
+ * status block, the first 8 bytes of the workspace it was given:
+ *   word 0  a marker for "a wait of the LAST call on this workspace gave up"; the first
+ *           kernel of every call clears it, so it needs no initialisation
+ *   word 1  a count of such give-ups that no kernel ever clears: zero it once after
+ *           allocating the workspace and it tells, however rarely it is read, whether
+ *           any call since then failed
+ * The outputs of a call that gave up are not valid (the fused MLP also turns the row
+ * scales it could not finish into NaN, so the failure travels with the data).
+ * i8tk_check_status_word copies word 0 back (it synchronises `stream`) and returns
  * I8TK_ERR_DEVICE_TIMEOUT if the marker is there.  i8tk_selftest_bounded_wait
  * launches a probe kernel that waits `polls` times (about a microsecond each)
- * on a barrier nothing signals and then records the marker in *status_word.
- * Neither has a counterpart in the reference, which checks no CUDA error at all. */
+ * on a barrier nothing signals and then records the give-up in the 8-byte block at
+ * status_word.  Neither has a counterpart in the reference, which checks no CUDA
+ * error at all. */
 int i8tk_check_status_word(const void* status_word, i8tk_stream_t stream);
 int i8tk_selftest_bounded_wait(void* status_word, int polls, i8tk_stream_t stream);
 
@@ -62,7 +70,9 @@ int i8tk_selftest_bounded_wait(void* status_word, int polls, i8tk_stream_t strea
  *   x       [rows, cols] fp32 (or fp16 for the _f16 form), row-major
  *   q       [rows, cols] int8
  *   scales  [rows]       fp32:  max(absmax,1e-8)/127, codes = clamp(rne(x/scale),-128,127)
- * Results are bit-identical to the torch code.  cols >= 1.
+ * Results are bit-identical to the torch code for finite inputs.  A NaN in a row is ignored by
+ * the row maximum here (fmaxf drops it) where torch's amax propagates it into the scale; the
+ * NaN element itself becomes an unspecified code in both.  cols >= 1.
  * ---------------------------------------------------------------------- */
 int i8tk_quantize_per_token_f32(const float* x, int8_t* q, float* scales,
                                 int64_t rows, int cols, i8tk_stream_t stream);
@@ -154,8 +164,8 @@ int i8tk_decode_attention_forward(const int8_t* Q, const int8_t* K, const int8_t
  * The scratch is a fixed 8 MiB block that is part of the library image
  * (i8tk_decode_static_scratch_bytes()); every GPU that loads the library
  * carries it until the process exits.  The call itself allocates nothing and
- * frees nothing.  Shapes whose scratch need (i8tk_decode_workspace_bytes)
- * exceeds the block are refused with I8TK_ERR_WORKSPACE -- on a 148-SM part the
+ * frees nothing.  Shapes whose partial rows (plus the 256-byte status block) do
+ * not fit the block are refused with I8TK_ERR_WORKSPACE -- on a 148-SM part the
  * serving shapes need well under 4 MiB; only very many (b,h) rows with a very
  * short context go over.
  *
@@ -165,8 +175,16 @@ int i8tk_decode_attention_forward(const int8_t* Q, const int8_t* K, const int8_t
  * call left there; the kernels overwrite every row they later read, so nothing
  * has to be cleared.  Two calls that may run on the GPU at the same time
  * (different streams) would race on it: serialise them, or use the
- * workspace form above for one of them. */
+ * workspace form above for one of them.  Two host threads that make their
+ * first call on the same device at the same moment both look the address up
+ * and store the same value: harmless.
+ *
+ * The caller cannot reach the block, so its status block is read through
+ * i8tk_decode_static_check_status: it synchronises `stream`, returns
+ * I8TK_ERR_DEVICE_TIMEOUT if a kernel of the last static call on the current
+ * device gave up a bounded wait, and clears the record. */
 size_t i8tk_decode_static_scratch_bytes(void);
+int i8tk_decode_static_check_status(i8tk_stream_t stream);
 int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_t* K, const int8_t* V,
                                          void* out_f16,
                                          const float* sQ, const float* sK, const float* sV,
@@ -183,7 +201,9 @@ int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_t* K, const
  *                   gets a zero output row
  *   Q int8 [batch*heads, head_dim], sQ fp32 [batch*heads], out fp16 [batch*heads, head_dim]
  * max_seq_len is a host-side upper bound on seq_lens (it sizes the grid and the workspace:
- * i8tk_decode_workspace_bytes(batch*heads, max_seq_len, head_dim)).  The lengths themselves
+ * i8tk_decode_workspace_bytes(batch*heads, max_seq_len, head_dim)); an entry of seq_lens outside
+ * [0, max_seq_len] is read as the nearer end of that range, so a damaged length cannot send the
+ * kernels past a page-table row.  Page ids are trusted.  The lengths themselves
  * are read on the device only: a one-CTA kernel counts the 128-position tiles each request
  * really has and cuts their sequence into equal runs for the CTAs of the scan, so a batch of
  * mixed lengths takes the time of the bytes it reads, not of batch x the longest request.
@@ -231,6 +251,10 @@ int i8tk_decode_combine_partials(const float* parts, int nparts, int BH, int hea
  * kernels/int8_decode_attention.cu:389-426 across GPUs; no counterpart in the
  * reference, which is single-GPU. */
 int i8tk_decode_exchange_ctas(int BH);
+/* How many times the exchange kernel polls another rank's flag before it gives up (each poll is
+ * a load of memory a peer writes, about a microsecond; default 2^21, i.e. seconds).  0 restores
+ * the default.  Process-wide; a supervisor that prefers a fast error to a long wait lowers it. */
+int i8tk_decode_set_exchange_spin_limit(unsigned int polls);
 int i8tk_decode_attention_seq_sharded(const int8_t* Q, const int8_t* K, const int8_t* V,
                                       void* out_f16,
                                       const float* sQ, const float* sK, const float* sV,

@@ -2,7 +2,10 @@
 
 Produces, beside this file:
   libi8tk.so  -- the C-ABI CUDA library (include/i8tk.h), nvcc, sm_100a only
+  libi8tk_compat.so -- the reference's C++-linkage launchers over it (include/i8tk_compat.h)
   int8_ext*.so -- the PyTorch binding over it (pybind11, no kernels)
+  build/compat_driver -- torch-free program that links the compat launchers by their C++ names
+                         (source: tests/compat_driver.cpp; built only when that file is present)
 
 ``python build.py`` builds what is out of date; ``build_all(force=True)``
 rebuilds everything.  nvcc cross-compiles without a GPU.
@@ -16,6 +19,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libi8tk.so")
+COMPAT_LIB = os.path.join(HERE, "libi8tk_compat.so")
+COMPAT_DRIVER = os.path.join(HERE, "build", "compat_driver")
+COMPAT_DRIVER_SRC = os.path.join(ROOT, "tests", "compat_driver.cpp")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
               "-std=c++17", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
@@ -85,8 +92,26 @@ def build_ext(force=False):
     return target
 
 
+def build_compat(force=False):
+    """The reference's native launchers (C++ linkage) as a thin library over libi8tk.so."""
+    src = os.path.join(CSRC, "compat_launchers.cpp")
+    hdr = os.path.join(ROOT, "include", "i8tk_compat.h")
+    if force or _stale(COMPAT_LIB, [src, hdr, LIB, os.path.join(ROOT, "include", "i8tk.h")]):
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I" + os.path.join(CUDA_HOME, "include"), src,
+              "-o", COMPAT_LIB, "-L" + HERE, "-li8tk", "-L" + os.path.join(CUDA_HOME, "lib64"), "-lcudart",
+              "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(CUDA_HOME, "lib64")])
+    if os.path.exists(COMPAT_DRIVER_SRC) and (force or _stale(COMPAT_DRIVER, [COMPAT_DRIVER_SRC, COMPAT_LIB, hdr])):
+        os.makedirs(os.path.dirname(COMPAT_DRIVER), exist_ok=True)
+        _run(["g++", "-O2", "-std=c++17", "-I" + os.path.join(CUDA_HOME, "include"), COMPAT_DRIVER_SRC,
+              "-o", COMPAT_DRIVER, "-L" + HERE, "-li8tk_compat", "-li8tk",
+              "-L" + os.path.join(CUDA_HOME, "lib64"), "-lcudart",
+              "-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath," + os.path.join(CUDA_HOME, "lib64")])
+    return COMPAT_LIB
+
+
 def build_all(force=False):
     build_lib(force)
+    build_compat(force)
     build_ext(force)
 
 

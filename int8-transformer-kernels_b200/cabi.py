@@ -47,10 +47,12 @@ SIGNATURES = {
     "i8tk_decode_attention_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "i8tk_decode_static_scratch_bytes": (_sz, []),
     "i8tk_decode_attention_forward_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "i8tk_decode_static_check_status": (_i, [_vp]),
     "i8tk_decode_attention_paged": (_i, [_vp] * 9 + [_i] * 6 + [_vp, _sz, _vp]),
     "i8tk_decode_attention_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "i8tk_decode_combine_partials": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "i8tk_decode_exchange_ctas": (_i, [_i]),
+    "i8tk_decode_set_exchange_spin_limit": (_i, [ctypes.c_uint]),
     "i8tk_decode_attention_seq_sharded": (_i, [_vp] * 7 + [_i, _i, _i, _vp, _sz, _vp, _vp, _i, _i,
                                                ctypes.c_uint, _vp]),
     "i8tk_decode_partial_stride": (_i, [_i]),

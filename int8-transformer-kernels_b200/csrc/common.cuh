@@ -37,12 +37,23 @@ inline bool aligned_to(const void* p, size_t a) {
 
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Magic value a kernel stores in the workspace status word when a bounded
-// wait runs out (an arbitrary fresh workspace will not contain it).
+// Status block at the start of every workspace (two 32-bit words):
+//   word 0  receives this magic value when a bounded wait of the CURRENT call runs out; the
+//           first kernel of every call clears it, so what it shows belongs to the last call
+//   word 1  counts such give-ups and is never cleared by a kernel: a caller that zeroes it
+//           once can look at it as rarely as it likes and still learn that some call failed
 constexpr uint32_t kDeviceTimeoutMagic = 0xD1E7E0u;
 
 // ---- device helpers -----------------------------------------------------
 #ifdef __CUDACC__
+
+// A bounded wait gave up: mark the call and bump the sticky count (see kDeviceTimeoutMagic).
+__device__ __forceinline__ void note_timeout(uint32_t* status) {
+    atomicExch(status, kDeviceTimeoutMagic);
+    atomicAdd(status + 1, 1u);
+}
+// Run by one thread of the first kernel of a call, before anything of that call can give up.
+__device__ __forceinline__ void clear_call_status(uint32_t* status) { *status = 0u; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -87,19 +87,26 @@ struct PagedKV {
     int page;                // positions per page: 16, 32, 64 or 128
     int max_pages;           // row length of page_table
     int B;                   // requests
+    int max_len;             // host-side bound on seq_lens: longer entries are read as this
     const int* hdr;          // plan: [0] tiles per CTA, [1] tiles in all
     const int* prefix;       // plan: [B+1] tiles per head of the requests before b
     const int4* starts;      // plan: [nctas] {first (b,h) row, first tile in it, tiles of the run, 0}
 };
 
 __device__ __forceinline__ int tiles_of(int len) { return len > 0 ? (len + kTile - 1) / kTile : 0; }
+// A request's length as the kernels use it: inside [0, max_len], so that a damaged entry can
+// neither walk off its page-table row nor leave the workspace sized from max_len.
+__device__ __forceinline__ int request_len(const int* seq_lens, int b, int max_len) {
+    const int len = __ldg(seq_lens + b);
+    return len < 0 ? 0 : (len > max_len ? max_len : len);
+}
 
 // First (b,h) row at or after `bh` that has tiles, and its tile count.  Called only while tiles
 // of the CTA's run remain, so such a row exists; the bound keeps a damaged plan inside the arrays.
 __device__ __forceinline__ int row_with_tiles(const PagedKV& pg, int bh, int& tpb) {
     const int BH = pg.B * pg.H;
     while (bh < BH) {
-        tpb = tiles_of(pg.seq_lens[bh / pg.H]);
+        tpb = tiles_of(request_len(pg.seq_lens, bh / pg.H, pg.max_len));
         if (tpb > 0) return bh;
         bh = (bh / pg.H + 1) * pg.H;
     }
@@ -113,18 +120,20 @@ __device__ __forceinline__ int row_with_tiles(const PagedKV& pg, int bh, int& tp
 constexpr int kPlanSmemRequests = 4096;      // prefix sums of up to this many requests are searched in shared memory
 
 __global__ void __launch_bounds__(1024)
-decode_ragged_plan_kernel(const int* __restrict__ seq_lens, int B, int H, int nctas, int resident, int target_tiles,
-                          int* __restrict__ hdr, int* __restrict__ prefix, int4* __restrict__ starts) {
+decode_ragged_plan_kernel(const int* __restrict__ seq_lens, int B, int H, int max_len, int nctas, int resident,
+                          int target_tiles, int* __restrict__ hdr, int* __restrict__ prefix, int4* __restrict__ starts,
+                          uint32_t* __restrict__ status) {
     __shared__ int warp_tot[32];
     __shared__ int s_prefix[kPlanSmemRequests + 1];
     pdl_wait();
     pdl_launch_dependents();
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    if (t == 0) clear_call_status(status);
     const bool in_smem = B <= kPlanSmemRequests;
     const int per = (B + 1023) / 1024;
     const int lo = min(B, t * per), hi = min(B, lo + per);
     int sum = 0;
-    for (int b = lo; b < hi; ++b) sum += tiles_of(seq_lens[b]);
+    for (int b = lo; b < hi; ++b) sum += tiles_of(request_len(seq_lens, b, max_len));
     int inc = sum;                                   // inclusive scan over the threads
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -147,7 +156,7 @@ decode_ragged_plan_kernel(const int* __restrict__ seq_lens, int B, int H, int nc
     for (int b = lo; b < hi; ++b) {
         prefix[b] = base;
         if (in_smem) s_prefix[b] = base;
-        base += tiles_of(seq_lens[b]);
+        base += tiles_of(request_len(seq_lens, b, max_len));
     }
     if (t == 1023) {
         prefix[B] = warp_tot[31];
@@ -293,6 +302,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
     // this CTA's set-up may overlap its tail.
     pdl_wait();
     pdl_launch_dependents();                    // the merge kernel may be scheduled as SMs drain
+    if (blockIdx.x == 0 && threadIdx.x == 0) clear_call_status(status);
     int ntl, bh0, tb0;                          // tiles of this CTA, row and tile it starts at
     const int tpb = plan.tpb;
     if constexpr (PAGED) {
@@ -332,12 +342,12 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         const uint64_t stream_once = l2_policy_evict_first();   // K, V and their scales are read once
         int p_bh = bh0, p_tb = tb0;
         int p_tpb = tpb;                            // tiles of row p_bh
-        if constexpr (PAGED) p_tpb = tiles_of(pg.seq_lens[bh0 / pg.H]);
+        if constexpr (PAGED) p_tpb = tiles_of(request_len(pg.seq_lens, bh0 / pg.H, pg.max_len));
         for (int i = 0; i < ntl; ++i) {
             const int st = i % STAGES;
             if (i >= STAGES) {
                 if (!mbar_wait_bounded(empty0 + 8 * st, ((i / STAGES) - 1) & 1)) {
-                    if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
+                    if (lane == 0) note_timeout(status);
                     return;
                 }
             }
@@ -347,7 +357,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
             if constexpr (PAGED) {
                 // the tile is made of 128 / page pages; those past the request's end do not exist
                 const int b = p_bh / pg.H, h = p_bh - b * pg.H;
-                const int len = __ldg(pg.seq_lens + b);
+                const int len = request_len(pg.seq_lens, b, pg.max_len);
                 const int ppt = kTile / pg.page;
                 int npg = (len - pos0 + pg.page - 1) / pg.page;
                 npg = npg < 0 ? 0 : (npg > ppt ? ppt : npg);
@@ -418,7 +428,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
 
     int c_bh = bh0, c_tb = tb0;
     int c_tpb = tpb;                                // tiles of row c_bh
-    if constexpr (PAGED) c_tpb = tiles_of(pg.seq_lens[bh0 / pg.H]);
+    if constexpr (PAGED) c_tpb = tiles_of(request_len(pg.seq_lens, bh0 / pg.H, pg.max_len));
     int i = 0;                                      // tiles of this CTA consumed so far
     for (int seg = 0; i < ntl; ++seg) {
         // ---- one (b,h) segment: tiles [c_tb, c_tb + seg_tiles) of row c_bh ----
@@ -427,7 +437,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         const float qs = sQ[c_bh] * score_scale_log2;
         const float* sKb = sK + (size_t)c_bh * S;
         const float* sVb = sV + (size_t)c_bh * S;
-        const int Sb = PAGED ? __ldg(pg.seq_lens + c_bh / pg.H) : S;    // positions of this (b,h) row
+        const int Sb = PAGED ? request_len(pg.seq_lens, c_bh / pg.H, pg.max_len) : S;    // positions of this (b,h) row
         float m = -INFINITY, l = 0.f;
         f32x2 acc[8];
 #pragma unroll
@@ -456,7 +466,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
             const int st = i % STAGES;
             const bool got = mbar_wait_bounded(full0 + 8 * st, (i / STAGES) & 1);
             if (!__all_sync(0xffffffffu, got)) {
-                if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
+                if (lane == 0) note_timeout(status);
                 return;
             }
 
@@ -662,7 +672,7 @@ template <int D>
 __global__ void __launch_bounds__(128)
 decode_exchange_kernel(const float* __restrict__ rows, int BH, DecodePlan plan, int empty,
                        float* const* __restrict__ peer_parts, uint32_t* const* __restrict__ peer_flags,
-                       int rank, int world, uint32_t epoch, __half* __restrict__ out,
+                       int rank, int world, uint32_t epoch, uint32_t spin_limit, __half* __restrict__ out,
                        uint32_t* __restrict__ status) {
     constexpr int ROW = D + 4;
     constexpr int DPL = D / 32;
@@ -671,6 +681,7 @@ decode_exchange_kernel(const float* __restrict__ rows, int BH, DecodePlan plan, 
     const int bh = blockIdx.x * 4 + warp;
     const bool active = bh < BH;
     pdl_wait();                                 // rows of the scan launched just before this kernel
+    if (empty && blockIdx.x == 0 && threadIdx.x == 0) clear_call_status(status);   // no scan ran to do it
 
     // ---- 1. local merge ------------------------------------------------------
     float gm = -INFINITY, L = 0.f;
@@ -726,12 +737,12 @@ decode_exchange_kernel(const float* __restrict__ rows, int BH, DecodePlan plan, 
     if (threadIdx.x < world) {
         const uint32_t* f = peer_flags[rank] + (size_t)threadIdx.x * gridDim.x + slot;
         bool seen = false;
-        for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
+        for (uint32_t spin = 0; spin < spin_limit; ++spin) {
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
             if ((int32_t)(v - epoch) >= 0) { seen = true; break; }
         }
-        if (!seen) atomicExch(status, kDeviceTimeoutMagic);
+        if (!seen) note_timeout(status);
     }
     __syncthreads();
     if (!active) return;
@@ -782,6 +793,11 @@ decode_exchange_kernel(const float* __restrict__ rows, int BH, DecodePlan plan, 
 thread_local cudaEvent_t g_probe_start = nullptr;
 thread_local cudaEvent_t g_probe_stop = nullptr;
 
+// Polls the exchange kernel spends on another rank's flag before it gives up (each is a load
+// that travels to memory another GPU writes: about a microsecond, so the default is seconds).
+constexpr unsigned int kExchangeSpinDefault = 1u << 21;
+unsigned int g_exchange_spin_limit = kExchangeSpinDefault;
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;
@@ -799,6 +815,10 @@ int env_int(const char* name, int dflt) {
     const char* e = getenv(name);
     return e ? atoi(e) : dflt;
 }
+// Tuning overrides, read from the environment once per process.
+int forced_ctas() { static const int v = env_int("I8TK_DECODE_CTAS", 0); return v; }
+int scales_by_ldg() { static const int v = env_int("I8TK_DECODE_SCALES_LDG", 0); return v; }
+int paged_target_tiles(int dflt) { static const int v = env_int("I8TK_DECODE_TARGET_TILES", 0); return v > 0 ? v : dflt; }
 
 // CTAs are persistent over contiguous runs of the flat tile sequence.  The
 // count is between one and four resident waves: about 64 tiles per CTA keeps
@@ -822,7 +842,7 @@ DecodePlan make_plan(int BH, int S, int D, int sms) {
     if (want > 4 * slots) want = 4 * slots;
     const long long cap = (p.total + kMinTiles - 1) / kMinTiles;
     if (want > cap) want = cap;
-    const int forced = env_int("I8TK_DECODE_CTAS", 0);
+    const int forced = forced_ctas();
     if (forced > 0) want = forced;
     if (want > p.total) want = p.total;
     if (want < 1) want = 1;
@@ -896,7 +916,7 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
     uint32_t* status = reinterpret_cast<uint32_t*>(workspace);
     float* rows = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 256);
     const bool bulk_scales = (S % 4 == 0) && aligned_to(sK, 16) && aligned_to(sV, 16) &&
-                             env_int("I8TK_DECODE_SCALES_LDG", 0) == 0;
+                             scales_by_ldg() == 0;
     int rc;
     if (bulk_scales)
         rc = launch_partial<D, true>(Q, K, V, sQ, sK, sV, rows, S, p, status, stream);
@@ -998,7 +1018,8 @@ extern "C" int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_
                                                     i8tk_stream_t stream) {
     int rc = check_decode_args(Q, K, V, out_f16, sQ, sK, sV, BH, S, head_dim);
     if (rc != I8TK_OK) return rc;
-    const size_t need = workspace_bytes(BH, S, head_dim);
+    // what the contiguous forward really uses: the status block and the partial rows of its plan
+    const size_t need = 256 + rows_bytes(make_plan(BH, S, head_dim, sm_count()), head_dim);
     I8TK_REQUIRE(need <= kStaticScratchBytes, I8TK_ERR_WORKSPACE,
                  "this shape needs %zu bytes of scratch; the built-in block holds %zu -- use "
                  "i8tk_decode_attention_forward with a caller-provided workspace",
@@ -1014,7 +1035,28 @@ extern "C" int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_
                               scratch, kStaticScratchBytes, st);
 }
 
+extern "C" int i8tk_decode_static_check_status(i8tk_stream_t stream) {
+    void* scratch = nullptr;
+    const int rc = static_scratch_ptr(&scratch);
+    if (rc != I8TK_OK) return rc;
+    uint32_t words[2] = {0u, 0u};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    I8TK_CUDA(cudaMemcpyAsync(words, scratch, sizeof(words), cudaMemcpyDeviceToHost, st));
+    I8TK_CUDA(cudaStreamSynchronize(st));
+    if (words[0] == kDeviceTimeoutMagic) {
+        I8TK_CUDA(cudaMemsetAsync(scratch, 0, sizeof(words), st));
+        set_error("a kernel of i8tk_decode_attention_forward_static gave up a bounded wait");
+        return I8TK_ERR_DEVICE_TIMEOUT;
+    }
+    return I8TK_OK;
+}
+
 extern "C" int i8tk_decode_exchange_ctas(int BH) { return BH > 0 ? (BH + 3) / 4 : 0; }
+
+extern "C" int i8tk_decode_set_exchange_spin_limit(unsigned int polls) {
+    g_exchange_spin_limit = polls ? polls : kExchangeSpinDefault;
+    return I8TK_OK;
+}
 
 extern "C" int i8tk_decode_attention_seq_sharded(const int8_t* Q, const int8_t* K, const int8_t* V,
                                                  void* out_f16, const float* sQ, const float* sK,
@@ -1060,10 +1102,12 @@ extern "C" int i8tk_decode_attention_seq_sharded(const int8_t* Q, const int8_t* 
     const int empty = S_local == 0 ? 1 : 0;
     if (head_dim == 64)
         I8TK_CUDA(launch_after(decode_exchange_kernel<64>, dim3(grid), dim3(128), 0, st, (const float*)rows, BH, p,
-                               empty, pp, pf, rank, world, epoch, static_cast<__half*>(out_f16), status));
+                               empty, pp, pf, rank, world, epoch, g_exchange_spin_limit, static_cast<__half*>(out_f16),
+                               status));
     else
         I8TK_CUDA(launch_after(decode_exchange_kernel<128>, dim3(grid), dim3(128), 0, st, (const float*)rows, BH, p,
-                               empty, pp, pf, rank, world, epoch, static_cast<__half*>(out_f16), status));
+                               empty, pp, pf, rank, world, epoch, g_exchange_spin_limit, static_cast<__half*>(out_f16),
+                               status));
     return I8TK_OK;
 }
 
@@ -1100,11 +1144,11 @@ extern "C" int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool
     int* hdr = reinterpret_cast<int*>(ws + lay.hdr_off);
     int4* starts = reinterpret_cast<int4*>(ws + lay.starts_off);
     int* prefix = reinterpret_cast<int*>(ws + lay.prefix_off);
-    const PagedKV pg{page_table, seq_lens, heads, page_size, max_pages_per_seq, batch, hdr, prefix, starts};
+    const PagedKV pg{page_table, seq_lens, heads, page_size, max_pages_per_seq, batch, max_seq_len, hdr, prefix, starts};
     const int resident = sm_count() * (head_dim == 64 ? DecodeTraits<64>::CTAS_PER_SM : DecodeTraits<128>::CTAS_PER_SM);
-    I8TK_CUDA(launch_after(decode_ragged_plan_kernel, dim3(1), dim3(1024), 0, st, seq_lens, batch, heads, p.nctas,
-                           resident < p.nctas ? resident : p.nctas, env_int("I8TK_DECODE_TARGET_TILES", kPagedTargetTiles), hdr, prefix,
-                           starts));
+    I8TK_CUDA(launch_after(decode_ragged_plan_kernel, dim3(1), dim3(1024), 0, st, seq_lens, batch, heads, max_seq_len,
+                           p.nctas, resident < p.nctas ? resident : p.nctas, paged_target_tiles(kPagedTargetTiles), hdr,
+                           prefix, starts, status));
     int rc;
     if (head_dim == 64) {
         rc = launch_partial<64, true, true>(Q, K_pool, V_pool, sQ, sK_pool, sV_pool, rows, max_seq_len, p, status, st, pg);

@@ -11,13 +11,22 @@
 //   * a non-zero status from the C ABI raises RuntimeError;
 //   * extra ops the reference only has as Python code or inside its launcher:
 //     quantize_per_token, int8_decode_attention_partial,
-//     int8_decode_combine_partials.
+//     int8_decode_combine_partials, and check_status (the reference checks no
+//     CUDA error; here every device-side wait is bounded and a wait that gave up
+//     is recorded in the scratch block of the stream it ran on).
 // This file contains no kernels and no arithmetic.
 #include <torch/extension.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <c10/cuda/CUDAGraphsC10Utils.h>
 
+#include <cuda_runtime.h>
+
+#include <map>
+#include <mutex>
 #include <tuple>
+#include <utility>
+#include <vector>
 
 #include "../../include/i8tk.h"
 
@@ -31,10 +40,64 @@ i8tk_stream_t current_stream() {
     return static_cast<i8tk_stream_t>(c10::cuda::getCurrentCUDAStream().stream());
 }
 
+// Scratch of the ops.  One grow-only block per (device, stream), kept for the life of the
+// process: calls on one stream run one after the other, so they can share it, and calls on
+// different streams never do.  Its first eight bytes are the status block of the C ABI: word 0
+// is cleared by the first kernel of every call, word 1 counts bounded waits that gave up and
+// is only ever reset by check_status() below -- so a caller may look rarely and still learn
+// that a call in between failed.  While a CUDA graph is being captured the block comes from
+// torch's allocator instead (the capture's private pool owns it), as it did before.
+struct WsKey {
+    int device;
+    cudaStream_t stream;
+    bool operator<(const WsKey& o) const { return device != o.device ? device < o.device : stream < o.stream; }
+};
+std::mutex g_ws_mutex;
+std::map<WsKey, torch::Tensor> g_ws_cache;
+
 torch::Tensor make_workspace(size_t bytes, const torch::Device& dev) {
-    // torch's caching allocator returns 512-byte aligned blocks
-    return torch::empty({static_cast<int64_t>(bytes ? bytes : 256)},
-                        torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+    const int64_t need = static_cast<int64_t>(bytes > 256 ? bytes : 256);
+    const auto opts = torch::TensorOptions().dtype(torch::kUInt8).device(dev);   // 512-byte aligned blocks
+    const auto cur = c10::cuda::getCurrentCUDAStream(dev.index());
+    if (c10::cuda::currentStreamCaptureStatusMayInitCtx() != c10::cuda::CaptureStatus::None)
+        return torch::empty({need}, opts);
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    torch::Tensor& slot = g_ws_cache[WsKey{static_cast<int>(dev.index()), cur.stream()}];
+    if (!slot.defined() || slot.numel() < need) {
+        // grow with headroom; the status block travels to the new block
+        auto grown = torch::empty({need + need / 4}, opts);
+        if (slot.defined()) grown.narrow(0, 0, 256).copy_(slot.narrow(0, 0, 256));
+        else grown.narrow(0, 0, 256).zero_();
+        slot = grown;
+    }
+    return slot;
+}
+
+// Synchronises every stream an op has run on, reads the status blocks back and raises if a
+// bounded device-side wait gave up since the last check (the outputs of such a call are not
+// valid).  Resets the counts.  Returns the number of blocks looked at.
+int64_t check_status_torch() {
+    std::vector<std::pair<WsKey, torch::Tensor>> blocks;
+    {
+        std::lock_guard<std::mutex> lock(g_ws_mutex);
+        for (auto& kv : g_ws_cache) blocks.emplace_back(kv.first, kv.second);
+    }
+    int64_t failures = 0;
+    for (auto& kv : blocks) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(kv.first.device));
+        uint32_t words[2] = {0u, 0u};
+        TORCH_CHECK(cudaMemcpyAsync(words, kv.second.data_ptr(), sizeof(words), cudaMemcpyDeviceToHost,
+                                    kv.first.stream) == cudaSuccess, "status read-back failed");
+        TORCH_CHECK(cudaStreamSynchronize(kv.first.stream) == cudaSuccess, "stream synchronisation failed");
+        if (words[1] != 0u) {
+            failures += words[1];
+            TORCH_CHECK(cudaMemsetAsync(kv.second.data_ptr(), 0, sizeof(words), kv.first.stream) == cudaSuccess,
+                        "status reset failed");
+        }
+    }
+    TORCH_CHECK(failures == 0, "int8_ext: ", failures,
+                " bounded device-side wait(s) gave up since the last check; the outputs of those calls are not valid");
+    return static_cast<int64_t>(blocks.size());
 }
 
 // ---- decode attention (kernels/int8_ext.cu:136-178) -------------------------
@@ -356,5 +419,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           pybind11::arg("residual") = c10::nullopt, "fp16(q * scale[row]) (+ residual) — returns FP16");
     m.def("kv_append_quantize", &kv_append_quantize_torch,
           "Quantise the new token's K and V rows per token and write them into the INT8 cache at pos (in place)");
+    m.def("check_status", &check_status_torch,
+          "Synchronise the streams the ops ran on and raise if a bounded device-side wait gave up since the last check");
     register_mlp_ops(m);
 }

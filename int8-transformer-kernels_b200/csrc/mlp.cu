@@ -91,15 +91,6 @@ struct EpiParams {
 // GELU, tanh form: 0.5 x (1 + tanh(y)), y = kC (x + kA x^3)
 // (kernels/int8_common.cuh:9-13).  tanh.approx has a relative error of about
 // 2^-11, the same size as the fp16 rounding the value goes through next.
-#ifdef I8TK_GEMM_TRACE
-// Development aid (not compiled into the library): per-CTA clock stamps of the GEMM roles.
-constexpr int kTraceSlots = 128;
-__device__ long long g_gemm_trace[148 * kTraceSlots];
-#define I8TK_TRACE(slot) do { if ((slot) < kTraceSlots && blockIdx.x < 148) g_gemm_trace[blockIdx.x * kTraceSlots + (slot)] = clock64(); } while (0)
-#else
-#define I8TK_TRACE(slot) do { } while (0)
-#endif
-
 // GELU on a packed pair: five packed fp32 instructions and two MUFU.TANH.
 __device__ __forceinline__ f32x2 gelu_tanh2(f32x2 x) {
     constexpr float kC = 0.7978845608028654f, kA = 0.044715f;
@@ -248,7 +239,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int kblocks = K / BK;
 
     if (threadIdx.x == 0) {
-        I8TK_TRACE(0);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
@@ -264,7 +254,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
-    if (threadIdx.x == 0) I8TK_TRACE(1);
     pdl_launch_dependents();                    // the next GEMM may set itself up as SMs become free
 
     if (warp == 0) {
@@ -273,14 +262,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int it = 0;
             bool ok = true;
             if (ep.a_from_prev) pdl_wait();              // A comes from the kernel before this one
-            I8TK_TRACE(2);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile / tiles_n) * BM;
                 const int n0 = (tile % tiles_n) * BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % STAGES;
                     if (!mbar_wait_spin_bounded(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) {
-                        atomicExch(status, kDeviceTimeoutMagic);
+                        note_timeout(status);
                         ok = false;
                         break;
                     }
@@ -308,21 +296,19 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
                 const int buf = lt & 1;
                 if (!mbar_wait_spin_bounded(tempty0 + 8 * buf, ((lt >> 1) & 1) ^ 1)) {
-                    atomicExch(status, kDeviceTimeoutMagic);
+                    note_timeout(status);
                     break;
                 }
                 tc_fence_after();
-                I8TK_TRACE(8 + 10 * lt + 0);
                 const uint32_t tmem_d = tmem_base + buf * BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % STAGES;
                     if (!mbar_wait_spin_bounded(full0 + 8 * st, (it / STAGES) & 1)) {
-                        atomicExch(status, kDeviceTimeoutMagic);
+                        note_timeout(status);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    if (kb == 0) I8TK_TRACE(8 + 10 * lt + 1);
                     const uint32_t sa = base_s + st * Cfg::STAGE_BYTES;
                     const uint64_t da = smem_desc_sw128(sa);
                     const uint64_t db = b_mn ? smem_desc_sw128_mn(sa + Cfg::A_BYTES, 128 * BK)
@@ -336,7 +322,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tc_commit(empty0 + 8 * st);           // stage reusable when these MMAs retire
                 }
                 if (ok) tc_commit(tfull0 + 8 * buf);      // accumulator complete
-                I8TK_TRACE(8 + 10 * lt + 2);
             }
         }
     } else {
@@ -372,7 +357,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // Requantisation of a tile whose fp16 values sit in this warp's stash: wait for the
         // maxima of its row block, then 16 columns (16 bytes of int8) per lane and step, a row
         // segment of HC bytes across consecutive lanes.
-        [[maybe_unused]] int trace_lt = 0;
         [[maybe_unused]] uint32_t gahead[(FUSED && DEFER) ? kGatherAhead : 1];
         [[maybe_unused]] auto finalize = [&](int fm0, int fn0, bool looked_ahead) {
             if constexpr (FUSED) {
@@ -383,9 +367,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (looked_ahead) have = gather_check(gahead, &amax);
                 }
                 if (!have) amax = gather_row_max(ep.row_parts + (size_t)fm0 * tiles_n + q * 32 + lane, tiles_n, &ok);
-                if (!ok) atomicExch(status, kDeviceTimeoutMagic);
-                if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * trace_lt + 6);
                 amax = fmaxf(amax, 1e-8f);
+                if (!ok) {
+                    // a sibling CTA never published: the row scale becomes NaN, so the failure
+                    // also shows in the data, downstream and without a host round trip
+                    note_timeout(status);
+                    amax = __int_as_float(0x7fc00000);
+                }
                 const float inv_l = 127.f / amax;
                 if (fn0 == 0 && slice == 0 && fm0 + q * 32 + lane < M) ep.row_scale[fm0 + q * 32 + lane] = amax / 127.f;
                 constexpr int SEGS = HC / 16;              // 16-column segments per row
@@ -412,7 +400,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (__any_sync(0xffffffffu, !(amax <= 65504.f))) body(std::true_type{});
                 else body(std::false_type{});
                 __syncwarp();                              // stash reads done before it is rewritten
-                if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * trace_lt + 7);
             }
         };
 
@@ -436,15 +423,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const f32x2 sa2 = pack2(sa, sa);
             __syncwarp();
             if (tile + (int)gridDim.x < num_tiles) prefetch(tile + gridDim.x);
-            if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 9);
 
             const bool got = mbar_wait_spin_bounded(tfull0 + 8 * buf, (lt >> 1) & 1);
             if (!__all_sync(0xffffffffu, got)) {
-                if (lane == 0) atomicExch(status, kDeviceTimeoutMagic);
+                if (lane == 0) note_timeout(status);
                 break;
             }
             tc_fence_after();
-            if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 3);
 
             float rmax = 0.f;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c0;
@@ -506,7 +491,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
-            if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 4);
 
             if (ep.out_absmax) {
                 float wmax;
@@ -527,7 +511,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int k = 1; k < kSlices; ++k) m4 = fmaxf(m4, cq[k * 32 + lane]);
                     publish_row_max(ep.row_parts + ((size_t)m0 * tiles_n + (tile % tiles_n) * 128) + q * 32 + lane, m4);
                 }
-                trace_lt = lt;
                 if constexpr (DEFER) {
                     // requantise the PREVIOUS tile: by now every CTA that shares its row block
                     // has published, so its maxima are there at the first look
@@ -538,7 +521,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     *reinterpret_cast<uint4*>(cst + lane * (HC * 2) + (stash_swz<HC>(lane, jc) << 4)) =
                         make_uint4(hv[4 * jc], hv[4 * jc + 1], hv[4 * jc + 2], hv[4 * jc + 3]);
                 __syncwarp();
-                if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 8);
                 if constexpr (DEFER) {
                     p_m0 = m0;
                     p_n0 = n0;
@@ -547,7 +529,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     finalize(m0, n0, false);
                 }
             }
-            if (ew == 0 && lane == 0) I8TK_TRACE(8 + 10 * lt + 5);
         }
         if constexpr (FUSED && DEFER) {
             if (p_m0 >= 0) finalize(p_m0, p_n0, false);
@@ -561,7 +542,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
-    if (threadIdx.x == 0) I8TK_TRACE(3);
 }
 
 // ---------------------------------------------------------------------------
@@ -601,9 +581,10 @@ requant_tensor_kernel(const __half* __restrict__ H, const float* __restrict__ ab
 
 // Workspace presets of one forward: `words16` 16-byte words of all ones, one float of zero.
 __global__ void __launch_bounds__(256)
-preset_kernel(uint4* __restrict__ ones, size_t words16, float* __restrict__ zero) {
+preset_kernel(uint4* __restrict__ ones, size_t words16, float* __restrict__ zero, uint32_t* __restrict__ status) {
     pdl_wait();                 // plain stream order towards whatever precedes the call
     pdl_launch_dependents();
+    if (blockIdx.x == 0 && threadIdx.x == 0) clear_call_status(status);
     const uint4 v = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words16; i += (size_t)gridDim.x * blockDim.x)
         ones[i] = v;
@@ -682,13 +663,41 @@ int make_map_mn(CUtensorMap* map, const int8_t* ptr, int K, int N) {
     return I8TK_OK;
 }
 
-int sm_count_mlp() {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
-    return n;
+// Encoded tensor maps of the last few (pointer, shape, box) combinations this thread asked for:
+// a descriptor depends on nothing else, and a serving loop calls with the same weights and
+// the same activation buffers over and over, so the driver call (about a microsecond each,
+// four per forward) is paid once.
+struct MapKey {
+    const void* ptr;
+    int a, b, box, mn;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && box == o.box && mn == o.mn; }
+};
+int cached_map(CUtensorMap* out, const int8_t* ptr, int a, int b, int box, bool mn) {
+    constexpr int kSlots = 16;
+    thread_local MapKey keys[kSlots] = {};
+    thread_local CUtensorMap maps[kSlots];
+    thread_local int next = 0;
+    const MapKey k{ptr, a, b, box, mn ? 1 : 0};
+    for (int i = 0; i < kSlots; ++i)
+        if (keys[i].ptr != nullptr && keys[i] == k) { *out = maps[i]; return I8TK_OK; }
+    const int rc = mn ? make_map_mn(out, ptr, a, b) : make_map(out, ptr, a, b, box);
+    if (rc != I8TK_OK) return rc;
+    keys[next] = k;
+    maps[next] = *out;
+    next = (next + 1) % kSlots;
+    return I8TK_OK;
 }
 
+int sm_count_mlp() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] > 0) return cached[dev];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    cached[dev] = n;
+    return n;
+}
 // CTAs of a persistent launch.  Fused kernels: the CTAs that share a row block wait for
 // one another, so every round of the persistent loop covers whole row blocks.
 int gemm_grid(int M, int N, int bn, bool fused) {
@@ -732,9 +741,9 @@ int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep
         attr_done[dev] = true;
     }
     CUtensorMap tmA, tmB;
-    int rc = make_map(&tmA, A, M, K, BM);
+    int rc = cached_map(&tmA, A, M, K, BM, false);
     if (rc != I8TK_OK) return rc;
-    rc = b_mn ? make_map_mn(&tmB, B, K, N) : make_map(&tmB, B, N, K, BN);
+    rc = b_mn ? cached_map(&tmB, B, K, N, 0, true) : cached_map(&tmB, B, N, K, BN, false);
     if (rc != I8TK_OK) return rc;
     const int grid = gemm_grid(M, N, BN, FUSED);
     I8TK_REQUIRE(!FUSED || N / BN <= sm_count_mlp(), I8TK_ERR_UNSUPPORTED,
@@ -807,18 +816,6 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
 
 using namespace i8tk;
 
-#ifdef I8TK_GEMM_TRACE
-extern "C" int i8tk_debug_gemm_trace(long long* host_dst, int clear) {
-    if (host_dst) I8TK_CUDA(cudaMemcpyFromSymbol(host_dst, g_gemm_trace, sizeof(long long) * 148 * kTraceSlots));
-    if (clear) {
-        void* p = nullptr;
-        I8TK_CUDA(cudaGetSymbolAddress(&p, g_gemm_trace));
-        I8TK_CUDA(cudaMemset(p, 0, sizeof(long long) * 148 * kTraceSlots));
-    }
-    return I8TK_OK;
-}
-#endif
-
 extern "C" int i8tk_transpose_int8_weights(const int8_t* W1, const int8_t* W2, int8_t* W1T,
                                            int8_t* W2T, int d_model, int d_ff, i8tk_stream_t stream) {
     I8TK_REQUIRE(W1 && W2 && W1T && W2T, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
@@ -872,7 +869,7 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
         if (blocks > 296) blocks = 296;
         if (blocks < 1) blocks = 1;
         I8TK_CUDA(launch_after(preset_kernel, dim3(blocks), dim3(256), 0, st, reinterpret_cast<uint4*>(w.parts1),
-                               words, w.tensor_absmax));
+                               words, w.tensor_absmax, w.status));
     }
 
     // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token inside the
@@ -885,9 +882,6 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
         rc = launch_gemm_bn<true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
     }
-#ifdef I8TK_GEMM_TRACE
-    if (getenv("I8TK_TRACE_GEMM1_ONLY")) return I8TK_OK;
-#endif
     if (out_row_scales) {
         // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way, but
         // at once: with K = d_ff the MMAs of the next tile cover the exchange

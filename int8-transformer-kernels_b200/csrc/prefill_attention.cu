@@ -85,9 +85,10 @@ enum Bar : int {
 // 16 elements per thread; rows of D int8.
 __global__ void __launch_bounds__(256)
 dequant_v_kernel(const int8_t* __restrict__ V, const float* __restrict__ sV, __half* __restrict__ V16,
-                 long long vecs, int vecs_per_row) {
+                 long long vecs, int vecs_per_row, uint32_t* __restrict__ status) {
     pdl_wait();
     pdl_launch_dependents();
+    if (blockIdx.x == 0 && threadIdx.x == 0) clear_call_status(status);
     for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < vecs;
          v += (long long)gridDim.x * blockDim.x) {
         const float sc = sV[v / vecs_per_row];
@@ -111,15 +112,6 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-
-#ifdef I8TK_PREFILL_TRACE
-// Development aid (not compiled into the library): clock stamps of one CTA's roles.
-constexpr int kPTraceSlots = 512;
-__device__ long long g_prefill_trace[kPTraceSlots];
-#define I8TK_PTRACE(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (slot) < kPTraceSlots) g_prefill_trace[(slot)] = clock64(); } while (0)
-#else
-#define I8TK_PTRACE(slot) do { } while (0)
-#endif
 
 template <int D>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
@@ -182,7 +174,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             for (int j = 0; j < nt; ++j) {
                 const int st = j % kRing;
                 if (!mbar_wait_spin_bounded(bar(B_KEMPTY + st), ((j / kRing) & 1) ^ 1)) {
-                    atomicExch(status, kDeviceTimeoutMagic);
+                    note_timeout(status);
                     break;
                 }
                 mbar_expect_tx(bar(B_KFULL + st), Cfg::TILE_BYTES);
@@ -193,7 +185,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             for (int j = 0; j < nt; ++j) {
                 const int st = j % kRing;
                 if (!mbar_wait_spin_bounded(bar(B_V16EMPTY + st), ((j / kRing) & 1) ^ 1)) {
-                    atomicExch(status, kDeviceTimeoutMagic);
+                    note_timeout(status);
                     break;
                 }
                 // fp16 V: one box of 128 rows x 64 columns (128 bytes) per slab of the MN-major operand
@@ -250,11 +242,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                         mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * k, db + 2 * k, idesc_qk, k != 0);
                     tc_commit(bar(B_KEMPTY + kst));
                     tc_commit(bar(B_SFULL + st));
-                    I8TK_PTRACE(256 + 4 * j);
                 }
-                if (j >= 2) { ok = issue_pv(j - 2); I8TK_PTRACE(256 + 4 * (j - 2) + 1); }
+                if (j >= 2) ok = issue_pv(j - 2);
             }
-            if (!ok) atomicExch(status, kDeviceTimeoutMagic);
+            if (!ok) note_timeout(status);
         }
     } else {
         // ================= softmax: half a query row (64 KV positions of every tile) per thread =================
@@ -362,7 +353,6 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         for (int j = 0; j < nt && ok; ++j) {
             const int st = j & 1;
             const bool has_next = j + 1 < nt;
-            if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 0);
             // ---- row maximum across the two halves (shared memory, one named barrier per lane quarter) ----
             xch[(st * 2 + half) * kQT + r] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
@@ -398,7 +388,6 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 tmem_st_wait();
             }
             m_ref = m_new;
-            if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 1);
 
             // ---- exponentials of this tile (special-function unit) interleaved, 8 columns at a time,
             // with the conversion of the NEXT tile's scores (integer and FMA pipes), which take over
@@ -412,7 +401,6 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 const bool got = mbar_wait_spin_bounded(bar(B_SFULL + (st ^ 1)), ((j + 1) >> 1) & 1);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
                 tc_fence_after();
-                if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 2);
                 const float* ksc = wsc + (st ^ 1) * 64;
                 const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S0 : Cfg::TM_S1) + half * 64;
                 uint32_t sr[2][16];
@@ -436,12 +424,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 #pragma unroll
                 for (int c = 0; c < 8; ++c) exp8(&y[c * 4], nm2, prow + c * 4);
             }
-            if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 3);
             tmem_st_wait();                              // P is in tensor memory before the MMA thread is told
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_PFULL + st));
-            if (sw == 0 && lane == 0) I8TK_PTRACE(8 * j + 4);
         }
         // ---- epilogue: O / l -> fp16, each thread its half of the output columns ----
         if (ok) {
@@ -474,7 +460,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 }
             }
         } else if (lane == 0) {
-            atomicExch(status, kDeviceTimeoutMagic);
+            note_timeout(status);
         }
     }
 
@@ -505,7 +491,7 @@ int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* ou
     const long long vecs = (long long)rows * (D / 16);
     long long blocks = (vecs + 255) / 256;
     if (blocks > 148ll * 16) blocks = 148ll * 16;
-    I8TK_CUDA(launch_after(dequant_v_kernel, dim3((unsigned)blocks), dim3(256), 0, st, V, sV, V16, vecs, D / 16));
+    I8TK_CUDA(launch_after(dequant_v_kernel, dim3((unsigned)blocks), dim3(256), 0, st, V, sV, V16, vecs, D / 16, status));
 
     const CUtensorMapSwizzle sw = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     CUtensorMap tmQ, tmK, tmV;
@@ -529,13 +515,6 @@ size_t attention_workspace(long long rows, int D) { return 256 + round_up((size_
 }  // namespace i8tk
 
 using namespace i8tk;
-
-#ifdef I8TK_PREFILL_TRACE
-extern "C" int i8tk_debug_prefill_trace(long long* host_dst) {
-    I8TK_CUDA(cudaMemcpyFromSymbol(host_dst, g_prefill_trace, sizeof(long long) * kPTraceSlots));
-    return I8TK_OK;
-}
-#endif
 
 extern "C" size_t i8tk_attention_workspace_bytes(int batch, int heads, int seq_len, int head_dim) {
     if (batch <= 0 || heads <= 0 || seq_len <= 0 || (head_dim != 64 && head_dim != 128)) return 0;

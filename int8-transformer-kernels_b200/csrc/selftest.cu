@@ -19,7 +19,7 @@ __global__ void bounded_wait_probe_kernel(uint32_t* status, uint32_t polls) {
         ok = mbar_try_wait(b, 0, 1000u);            // each poll parks for at most ~1 us
         if (ok) break;
     }
-    if (!ok && threadIdx.x == 0) atomicExch(status, kDeviceTimeoutMagic);
+    if (!ok && threadIdx.x == 0) note_timeout(status);
 }
 
 }  // namespace

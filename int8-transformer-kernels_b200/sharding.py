@@ -110,15 +110,33 @@ class SeqShardedDecoder:
     def _workspace(self, BH, S_local):
         need = max(256, self._lib.i8tk_decode_workspace_bytes(BH, S_local, self.D) if S_local > 0 else 256)
         if need > self._ws_bytes:
-            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+            # zeroed: the status block at its start is read back by check()
+            self._ws = torch.zeros(need, dtype=torch.uint8, device=self.device)
             self._ws_bytes = need
         return self._ws
+
+    def _checked(self, t, name, dtype):
+        if t.dtype != dtype or t.device != self.device or not t.is_contiguous():
+            raise ValueError("%s must be a contiguous %s tensor on %s (a slice of a larger cache has to be "
+                             "copied first: the kernel reads S_local*D contiguous bytes per (b,h) row)"
+                             % (name, dtype, self.device))
+        return t
 
     def __call__(self, Q, K_local, V_local, sQ, sK_local, sV_local):
         B, H, D = Q.shape
         assert (B, H, D) == (self.B, self.H, self.D), "shape differs from the one set up"
         S_local = int(K_local.shape[2])
         BH = B * H
+        self._checked(Q, "Q", torch.int8)
+        self._checked(sQ, "sQ", torch.float32)
+        if S_local:
+            for t, nm, dt in ((K_local, "K_local", torch.int8), (V_local, "V_local", torch.int8),
+                              (sK_local, "sK_local", torch.float32), (sV_local, "sV_local", torch.float32)):
+                self._checked(t, nm, dt)
+            if tuple(K_local.shape) != (B, H, S_local, D) or V_local.shape != K_local.shape:
+                raise ValueError("K_local / V_local must be [B, H, S_local, D]")
+            if sK_local.numel() != BH * S_local or sV_local.numel() != BH * S_local or sQ.numel() != BH:
+                raise ValueError("scales must have one value per row")
         ws = self._workspace(BH, S_local)
         out = torch.empty(B, H, D, dtype=torch.float16, device=self.device)
         self._epoch += 1
@@ -136,4 +154,7 @@ class SeqShardedDecoder:
         """Synchronises and raises if a bounded device-side wait gave up (a rank never arrived)."""
         stream = torch.cuda.current_stream(self.device).cuda_stream
         if self._ws is not None:
-            self._cabi.check(self._lib.i8tk_check_status_word(self._ws.data_ptr(), stream), "seq-sharded decode")
+            rc = self._lib.i8tk_check_status_word(self._ws.data_ptr(), stream)
+            if rc != self._cabi.OK:
+                self._ws[:8].zero_()          # the record has been delivered
+            self._cabi.check(rc, "seq-sharded decode")

@@ -11,6 +11,12 @@ It imports the reference's own Python functions (no CUDA is touched) --
 ``validation/check_decode.py:65-68``, runs them on seeded CPU inputs and
 stores inputs + outputs as small ``.npz`` files beside this script.  The
 tests only read the ``.npz`` files; the reference is not needed to run them.
+
+``validation_sets.npz`` holds slices of the reference's eight validation datasets
+(``validation/generate_test_data.py:174-338``: normal, outlier, boundary, stress, short_seq,
+long_seq, zeros, constant; CPU generator, seed 42), each with the outputs of the reference's
+own fp reference (``common/baseline.py``) and int8 simulation (``sim_attention`` / ``sim_mlp``,
+``validation/validate_int8.py:144-225``) ON THE SLICE, and the dataset's thresholds.
 """
 import os
 import sys
@@ -74,10 +80,60 @@ def layernorm_quantize_cases(test_int8):
     np.savez_compressed(os.path.join(HERE, "layernorm_quantize.npz"), **out)
 
 
+def validation_sets(validate_int8):
+    """Slices of the reference's eight validation datasets with its own references on them.
+
+    The generator draws everything from one seeded CPU generator except the heavy-tailed
+    "stress" attention tensors, which come from torch's global generator
+    (``generate_test_data.py:137-139``): that one is seeded here (42) so the file is reproducible.
+    Slices: attention keeps batch 0, two heads (one for long_seq) and the first 256 positions
+    (1024 for long_seq, all 4 for short_seq); the MLP keeps batch 0's first 128 tokens (all of
+    short_seq's) and every 2nd input channel / every 8th hidden channel, so log-spaced channel
+    magnitudes keep their spread.  The reference outputs are computed on the slices, in fp32
+    on the CPU (``attention_baseline`` / ``mlp_baseline`` run in fp16 on CUDA in the reference).
+    """
+    import json
+    import generate_test_data as gtd
+    import baseline
+    torch.manual_seed(gtd.SEED)
+    sets = gtd.build_datasets()
+    out = {}
+    meta = {}
+    for name, d in sets.items():
+        a = d["attention"]
+        seq = a["Q"].shape[2]
+        heads = 1 if name == "long_seq" else 2
+        keep = {"long_seq": 1024, "short_seq": seq}.get(name, 256)
+        Q, K, V = (a[k][:1, :heads, :keep].contiguous() for k in ("Q", "K", "V"))
+        ref = baseline.attention_baseline(Q.float(), K.float(), V.float())
+        sim = validate_int8.sim_attention(Q, K, V)["out"]
+        for k, t in (("Q", Q), ("K", K), ("V", V)):
+            out[f"{name}__attn_{k}"] = t.numpy()
+        out[f"{name}__attn_ref"] = ref.half().numpy()        # the reference keeps this one in fp16
+        out[f"{name}__attn_sim"] = sim.numpy()
+        m = d["mlp"]
+        x = m["x"][:1, :128, ::2].contiguous()
+        W1 = m["W1"][::2, ::8].contiguous()
+        W2 = m["W2"][::8, ::2].contiguous()
+        ref = baseline.mlp_baseline(x.float(), W1.float(), W2.float())
+        sim = validate_int8.sim_mlp(x, W1, W2)["out"]
+        for k, t in (("x", x), ("W1", W1), ("W2", W2)):
+            out[f"{name}__mlp_{k}"] = t.numpy()
+        out[f"{name}__mlp_ref"] = ref.half().numpy()
+        out[f"{name}__mlp_sim"] = sim.numpy()
+        meta[name] = {"thresholds": d["thresholds"], "xfail": sorted(d.get("xfail", {})),
+                      "edge": name in validate_int8.EDGE_DATASETS, "seq_len": d["seq_len"]}
+    out["meta_json"] = np.frombuffer(json.dumps(meta, sort_keys=True).encode(), dtype=np.uint8)
+    np.savez_compressed(os.path.join(HERE, "validation_sets.npz"), **out)
+
+
 def main(ref_root, only=None):
     test_int8, validate_int8 = _import_reference(ref_root)
     if only == "layernorm":
         layernorm_quantize_cases(test_int8)
+        return
+    if only == "validation":
+        validation_sets(validate_int8)
         return
     torch.manual_seed(0)
     gen = torch.Generator().manual_seed(20240607)
@@ -161,7 +217,8 @@ def main(ref_root, only=None):
 
 if __name__ == "__main__":
     if len(sys.argv) not in (2, 3):
-        sys.exit("usage: make_golden.py <path to the reference checkout> [layernorm]")
+        sys.exit("usage: make_golden.py <path to the reference checkout> [layernorm|validation]")
     main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)
     if len(sys.argv) == 2:
         main(sys.argv[1], "layernorm")
+        main(sys.argv[1], "validation")

@@ -1,0 +1,100 @@
+"""Decode attention at the sizes the benchmark configurations name, compared with the oracle on
+sampled (b,h) rows (the oracle is float64 numpy: a row of 32768 positions takes milliseconds, the
+whole tensor would take minutes).  Inputs are drawn and quantised on the device exactly as the
+benchmark draws them; the sampled rows travel to the host.
+
+  config 1  B32 H12 D64 ctx 32768                  (the headline shape)
+  config 2  B64 H32 D128 ctx 8192, 1 % of channels x 20 (outlier columns)
+  config 3  B4 H32 D128, one GPU's chunk of 524288 / 8 = 65536 positions, left as the
+            unnormalised (m, l, acc) partial that crosses NVLink
+
+Tolerance: cosine > 0.9999, max-abs < 0.05 (validation/check_decode.py:73); in practice the
+error is fp16 output rounding, checked as 2e-3 of the output's range.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import decode as odec
+from helpers import ext, cosine
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(B, H, S, D, outliers, seed):
+    e = ext()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    Qi, sQ = e.quantize_per_token(torch.randn(B, H, D, device="cuda", dtype=torch.float16, generator=g))
+    kv = []
+    for _ in range(2):
+        x = torch.randn(B, H, S, D, device="cuda", generator=g)
+        if outliers:
+            ch = torch.randperm(D, device="cuda", generator=g)[: max(1, int(0.01 * D))]
+            x[..., ch] *= 20.0
+        kv.append(e.quantize_per_token(x))
+        del x
+    (Ki, sK), (Vi, sV) = kv
+    return Qi, Ki, Vi, sQ, sK, sV
+
+
+def _row(t, b, h):
+    return t[b:b + 1, h:h + 1].contiguous().cpu().numpy()
+
+
+def _check_rows(out, args, rows, tag):
+    Qi, Ki, Vi, sQ, sK, sV = args
+    worst = (1.0, 0.0)
+    for (b, h) in rows:
+        ref = odec.decode_attention(*[_row(t, b, h) for t in (Qi, Ki, Vi, sQ, sK, sV)])
+        got = out[b:b + 1, h:h + 1].float().cpu().numpy()
+        assert not np.isnan(got).any(), (tag, b, h)
+        c, err = cosine(got, ref), float(np.abs(got - ref).max())
+        assert c > 0.9999 and err < 0.05, (tag, b, h, c, err)
+        assert err < 2e-3 * max(1.0, float(np.abs(ref).max())), (tag, b, h, err)
+        worst = (min(worst[0], c), max(worst[1], err))
+    print(f"{tag}: {len(rows)} sampled rows, worst cosine {worst[0]:.7f}, worst max-abs {worst[1]:.2e}")
+
+
+def test_config1_headline_shape_ctx32768():
+    B, H, D, S = 32, 12, 64, 32768
+    args = _inputs(B, H, S, D, False, 0)
+    out = ext().int8_decode_attention_forward(*args)
+    assert out.shape == (B, H, D)
+    _check_rows(out, args, [(0, 0), (13, 5), (31, 11), (20, 7)], "config 1 B32 H12 D64 ctx32768")
+    # every row was written: a row the scan skipped would keep torch.empty's content or be zero
+    assert torch.isfinite(out.float()).all() and int((out.float().abs().amax(dim=-1) == 0).sum()) == 0
+
+
+def test_config2_full_size_with_outlier_channels():
+    B, H, D, S = 64, 32, 128, 8192
+    args = _inputs(B, H, S, D, True, 0)
+    # the outlier channel dominates every row's scale, as the configuration intends
+    assert float(args[4].median()) > 20.0 / 127.0
+    out = ext().int8_decode_attention_forward(*args)
+    _check_rows(out, args, [(0, 0), (63, 31), (17, 9), (40, 22)], "config 2 B64 H32 D128 ctx8192 outliers")
+    assert torch.isfinite(out.float()).all()
+
+
+def test_config3_per_gpu_chunk_as_partial():
+    B, H, D, S = 4, 32, 128, 65536
+    args = _inputs(B, H, S, D, True, 103)
+    Qi, Ki, Vi, sQ, sK, sV = args
+    part = ext().int8_decode_attention_partial(*args)          # [B, H, D+4]: m (log2 units), l, 0, 0, acc
+    assert part.shape == (B, H, D + 4) and part.dtype == torch.float32
+    for (b, h) in [(0, 0), (3, 31), (2, 14)]:
+        m, l, acc = odec.decode_partial(*[_row(t, b, h) for t in (Qi, Ki, Vi, sQ, sK, sV)], 0, S)
+        p = part[b, h].double().cpu().numpy()
+        # the kernel's reference maximum may differ from the true one; compare at a common one
+        shift = p[0] * math.log(2.0) - m[0, 0]
+        assert abs(shift) < 1e-3 * max(1.0, abs(m[0, 0])), (b, h, shift)
+        f = math.exp(shift)
+        assert abs(p[1] * f - l[0, 0]) < 1e-3 * l[0, 0], (b, h)
+        assert np.abs(p[4:] * f - acc[0, 0]).max() < 1e-3 * max(1.0, float(np.abs(acc).max())), (b, h)
+        assert p[2] == 0.0 and p[3] == 0.0
+    # merged with itself as two "shards" it gives the single-GPU forward
+    two = torch.stack([part, part])
+    merged = ext().int8_decode_combine_partials(two)
+    full = ext().int8_decode_attention_forward(*args)
+    assert (merged.float() - full.float()).abs().max().item() < 2e-3 * max(1.0, float(full.float().abs().max()))

@@ -116,3 +116,25 @@ def test_layernorm_quantize_against_torch_cpu():
         dq = np.abs(q.astype(np.int32) - g[n + "__q"].astype(np.int32))
         assert dq.max() <= 1 and np.mean(dq != 0) < 2e-3, (n, dq.max(), np.mean(dq != 0))
         assert np.allclose(s, g[n + "__s"], rtol=1e-3, atol=0), n
+
+
+VALIDATION_SETS = ["normal", "outlier", "boundary", "stress", "short_seq", "long_seq", "zeros", "constant"]
+
+
+@pytest.mark.parametrize("name", VALIDATION_SETS)
+def test_oracle_reproduces_the_reference_simulations_on_its_validation_sets(name):
+    """Slices of the eight datasets of validation/generate_test_data.py:174-338 with the outputs
+    of the reference's own int8 simulations on them (sim_attention / sim_mlp,
+    validation/validate_int8.py:144-225): the numpy restatements must give the same numbers,
+    up to fp32-vs-float64 accumulation and a one-step flip of an int8 code on a rounding tie."""
+    g = _load("validation_sets.npz")
+    Q, K, V = (g[f"{name}__attn_{k}"] for k in ("Q", "K", "V"))
+    (qi, sq), (ki, sk), (vi, sv) = (quant.quantize_per_token(t) for t in (Q, K, V))
+    got = decode.prefill_attention(qi, ki, vi, sq, sk, sv)
+    sim = g[f"{name}__attn_sim"]
+    assert np.abs(got - sim).max() <= 1e-4 * max(1.0, float(np.abs(sim).max())), name
+    x, W1, W2 = (g[f"{name}__mlp_{k}"] for k in ("x", "W1", "W2"))
+    got = mlp.sim_mlp(x, W1, W2)["out"].reshape(x.shape)
+    sim = g[f"{name}__mlp_sim"]
+    assert np.abs(got - sim).max() <= 1.01 * max(1e-6, float(np.abs(sim).max())) / 127, name
+    assert _cos(got, sim) > 0.99999 or float(np.abs(sim).max()) == 0.0, name

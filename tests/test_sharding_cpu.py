@@ -87,3 +87,46 @@ def test_seq_sharded_exchange_over_gloo(world, seq, tmp_path):
     for r in range(world):
         err = float(open(tmp_path / f"r{r}.txt").read())
         assert err < 1e-5, (r, err)
+
+
+def _withholding_worker(rank, world, port, result_dir):
+    """Step 1 runs on every rank; the last rank then leaves between steps, so step 2 is one
+    partial short.  The ranks that stay must get an error from the exchange, not a wrong answer
+    and not a hang (the process group carries a short timeout)."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    sh = pkg().sharding
+    rng = np.random.default_rng(1)
+    B, H, D, seq = 1, 2, 64, 256
+    Qi, sQ = quant.quantize_per_token(rng.standard_normal((B, H, D)).astype(np.float16))
+    Ki, sK = quant.quantize_per_token(rng.standard_normal((B, H, seq, D)).astype(np.float32))
+    Vi, sV = quant.quantize_per_token(rng.standard_normal((B, H, seq, D)).astype(np.float32))
+    a, b = sh.seq_shard_range(seq, world, rank)
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    args = (t(Qi), t(Ki[:, :, a:b]), t(Vi[:, :, a:b]), t(sQ), t(sK[:, :, a:b]), t(sV[:, :, a:b]))
+    step = lambda: sh.decode_attention_seq_sharded(*args, partial_fn=_partial_np, combine_fn=_combine_np)
+    out = step()
+    ok1 = float(np.abs(out.numpy() - odec.decode_attention(Qi, Ki, Vi, sQ, sK, sV)).max()) < 1e-5
+    verdict = "step1-bad"
+    if ok1:
+        if rank == world - 1:
+            verdict = "left"                      # withholds its partial of step 2
+        else:
+            try:
+                step()
+                verdict = "step2-returned"        # must not happen: a partial is missing
+            except Exception as e:                # noqa: BLE001  (gloo raises RuntimeError / DistBackendError)
+                verdict = "error:" + type(e).__name__
+    with open(os.path.join(result_dir, f"r{rank}.txt"), "w") as f:
+        f.write(verdict)
+    os._exit(0)                                   # no collective teardown with a rank gone
+
+
+def test_rank_that_withholds_its_partial_surfaces_as_an_error(tmp_path):
+    world = 2
+    port = 29500 + (os.getpid() % 2000) + 911
+    mp.spawn(_withholding_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert open(tmp_path / "r1.txt").read() == "left"
+    assert open(tmp_path / "r0.txt").read().startswith("error:")
