@@ -321,11 +321,21 @@ int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V, vo
  * three on 128 and otherwise takes a static-scale fallback that leaves
  * out_row_scales unwritten (kernels/int8_mlp.cu:1023-1026,1194-1225).
  * All pointers 16-byte aligned.
+ *
+ * Rounding of the first epilogue.  By default v = fma(acc*sx, sW1, b1) and GELU uses the
+ * hardware tanh approximation (relative error 2^-11, the size of the fp16 rounding that
+ * follows): against the reference's source order this moves an int8 code of the hidden
+ * activations by one step on about 1 % of the elements, inside the reference's own
+ * tolerance for its kernel (max-abs 0.05 against its simulation).  With
+ * I8TK_MLP_REFERENCE_ROUNDING the epilogue follows the reference's source operation by
+ * operation -- (acc*sx)*sW1 then + b1, each rounded, and tanhf (kernels/int8_mlp.cu:437-440,
+ * kernels/int8_common.cuh:9-13) -- at roughly half the GEMM1 speed.
  * ---------------------------------------------------------------------- */
 enum i8tk_mlp_flags {
     I8TK_MLP_X_PER_TOKEN = 1,
     I8TK_MLP_W_PER_CHANNEL = 2,
-    I8TK_MLP_PREPACKED = 4
+    I8TK_MLP_PREPACKED = 4,
+    I8TK_MLP_REFERENCE_ROUNDING = 8
 };
 size_t i8tk_mlp_workspace_bytes(int T, int d_model, int d_ff, int flags);
 int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out,

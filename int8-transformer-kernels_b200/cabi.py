@@ -21,6 +21,7 @@ ERR_DEVICE_TIMEOUT = 6
 MLP_X_PER_TOKEN = 1
 MLP_W_PER_CHANNEL = 2
 MLP_PREPACKED = 4
+MLP_REFERENCE_ROUNDING = 8
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int

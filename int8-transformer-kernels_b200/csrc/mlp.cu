@@ -104,6 +104,20 @@ __device__ __forceinline__ f32x2 gelu_tanh2(f32x2 x) {
     return fma2(hx, pack2(t0, t1), hx);
 }
 
+// The reference's source order, one rounding per operation and the library tanh
+// (kernels/int8_mlp.cu:437-440, kernels/int8_common.cuh:9-13): what I8TK_MLP_REFERENCE_ROUNDING
+// selects.  About three times the instructions of the packed form above.
+__device__ __forceinline__ float epilogue_exact(float acc, float sa, float sb, float bias, bool gelu) {
+    float v = __fadd_rn(__fmul_rn(__fmul_rn(acc, sa), sb), bias);
+    if (gelu) {
+        constexpr float kC = 0.7978845608028654f, kA = 0.044715f;
+        const float cube = __fmul_rn(__fmul_rn(__fmul_rn(kA, v), v), v);
+        const float t = tanhf(__fmul_rn(kC, __fadd_rn(v, cube)));
+        v = __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.f, t));
+    }
+    return v;
+}
+
 // int32 accumulator -> fp32 (cvt.rn.f32.s32).  An integer/FMA-pipe emulation through 2^23
 // magic numbers was measured and is slower: the conversion unit is not the bottleneck.
 __device__ __forceinline__ float i2f(uint32_t acc) { return (float)(int)acc; }
@@ -208,7 +222,7 @@ __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
 // N % BN == 0, K % 128 == 0; any M >= 1: the last row block may be partial (TMA fills the
 // missing rows of A with zeros; nothing is stored for rows >= M).
 // ---------------------------------------------------------------------------
-template <int BN, bool GELU, bool FUSED, bool DEFER>
+template <int BN, bool GELU, bool FUSED, bool DEFER, bool EXACT = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                EpiParams ep, int M, int N, int K, int b_mn, uint32_t* __restrict__ status) {
@@ -452,11 +466,19 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int j = 0; j < 16; j += 4) {
                     const float4 s4 = *reinterpret_cast<const float4*>(sb + cc * 16 + j);
                     const float4 b4 = *reinterpret_cast<const float4*>(bb + cc * 16 + j);
-                    f32x2 v01 = fma2(mul2(pack2(i2f(rr[j]), i2f(rr[j + 1])), sa2), pack2(s4.x, s4.y), pack2(b4.x, b4.y));
-                    f32x2 v23 = fma2(mul2(pack2(i2f(rr[j + 2]), i2f(rr[j + 3])), sa2), pack2(s4.z, s4.w), pack2(b4.z, b4.w));
-                    if (GELU) {
-                        v01 = gelu_tanh2(v01);
-                        v23 = gelu_tanh2(v23);
+                    f32x2 v01, v23;
+                    if constexpr (EXACT) {
+                        v01 = pack2(epilogue_exact(i2f(rr[j]), sa, s4.x, b4.x, GELU),
+                                    epilogue_exact(i2f(rr[j + 1]), sa, s4.y, b4.y, GELU));
+                        v23 = pack2(epilogue_exact(i2f(rr[j + 2]), sa, s4.z, b4.z, GELU),
+                                    epilogue_exact(i2f(rr[j + 3]), sa, s4.w, b4.w, GELU));
+                    } else {
+                        v01 = fma2(mul2(pack2(i2f(rr[j]), i2f(rr[j + 1])), sa2), pack2(s4.x, s4.y), pack2(b4.x, b4.y));
+                        v23 = fma2(mul2(pack2(i2f(rr[j + 2]), i2f(rr[j + 3])), sa2), pack2(s4.z, s4.w), pack2(b4.z, b4.w));
+                        if (GELU) {
+                            v01 = gelu_tanh2(v01);
+                            v23 = gelu_tanh2(v23);
+                        }
                     }
                     const float2 a = unpack2(v01), b = unpack2(v23);
                     rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(a.x), fabsf(a.y))), fmaxf(fabsf(b.x), fabsf(b.y)));
@@ -727,7 +749,7 @@ int pick_bn(int M, int N, bool b_mn, bool fused) {
     return best;
 }
 
-template <int BN, bool GELU, bool FUSED, bool DEFER>
+template <int BN, bool GELU, bool FUSED, bool DEFER, bool EXACT = false>
 int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                 uint32_t* status, cudaStream_t st) {
     using Cfg = GemmCfg<BN, FUSED>;
@@ -736,7 +758,7 @@ int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU, FUSED, DEFER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU, FUSED, DEFER, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::SMEM_BYTES));
         attr_done[dev] = true;
     }
@@ -748,18 +770,18 @@ int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep
     const int grid = gemm_grid(M, N, BN, FUSED);
     I8TK_REQUIRE(!FUSED || N / BN <= sm_count_mlp(), I8TK_ERR_UNSUPPORTED,
                  "row of %d tiles does not fit one round of CTAs", N / BN);
-    I8TK_CUDA(launch_after(gemm_i8_kernel<BN, GELU, FUSED, DEFER>, dim3(grid), dim3(kGemmThreads), Cfg::SMEM_BYTES, st,
+    I8TK_CUDA(launch_after(gemm_i8_kernel<BN, GELU, FUSED, DEFER, EXACT>, dim3(grid), dim3(kGemmThreads), Cfg::SMEM_BYTES, st,
                            tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status));
     return I8TK_OK;
 }
 
-template <bool GELU, bool FUSED, bool DEFER>
+template <bool GELU, bool FUSED, bool DEFER, bool EXACT = false>
 int launch_gemm_bn(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                    uint32_t* status, cudaStream_t st) {
     const int best = pick_bn(M, N, b_mn, FUSED);
-    if (best == 256) return launch_gemm<256, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
-    if (best == 192) return launch_gemm<192, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
-    return launch_gemm<128, GELU, FUSED, DEFER>(A, B, b_mn, ep, M, N, K, status, st);
+    if (best == 256) return launch_gemm<256, GELU, FUSED, DEFER, EXACT>(A, B, b_mn, ep, M, N, K, status, st);
+    if (best == 192) return launch_gemm<192, GELU, FUSED, DEFER, EXACT>(A, B, b_mn, ep, M, N, K, status, st);
+    return launch_gemm<128, GELU, FUSED, DEFER, EXACT>(A, B, b_mn, ep, M, N, K, status, st);
 }
 
 int requant_grid(long long vecs) {
@@ -843,7 +865,7 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     I8TK_REQUIRE(out_row_scales || out_tensor_scale, I8TK_ERR_INVALID_ARGUMENT,
                  "one of out_row_scales / out_tensor_scale must be given");
     I8TK_REQUIRE(T > 0 && d_model > 0 && d_ff > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
-    I8TK_REQUIRE((flags & ~7) == 0, I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
+    I8TK_REQUIRE((flags & ~15) == 0, I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
     I8TK_REQUIRE(d_model % 128 == 0 && d_ff % 128 == 0, I8TK_ERR_UNSUPPORTED,
                  "d_model and d_ff must be multiples of 128 (got %d, %d)", d_model, d_ff);
     I8TK_REQUIRE(aligned_to(x, 16) && aligned_to(W1, 16) && aligned_to(W2, 16) && aligned_to(out, 16),
@@ -879,7 +901,10 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     {
         EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, per_token, per_channel,
                      w.hid_i8, w.hid_scale, w.parts1, 0};
-        rc = launch_gemm_bn<true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
+        if (flags & I8TK_MLP_REFERENCE_ROUNDING)
+            rc = launch_gemm_bn<true, true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
+        else
+            rc = launch_gemm_bn<true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
     }
     if (out_row_scales) {

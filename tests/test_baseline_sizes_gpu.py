@@ -70,8 +70,9 @@ def test_config1_headline_shape_ctx32768():
 def test_config2_full_size_with_outlier_channels():
     B, H, D, S = 64, 32, 128, 8192
     args = _inputs(B, H, S, D, True, 0)
-    # the outlier channel dominates every row's scale, as the configuration intends
-    assert float(args[4].median()) > 20.0 / 127.0
+    # the outlier channel sets most rows' scale, as the configuration intends (a plain N(0,1) row
+    # of 128 values has absmax/127 near 0.022; 20 x |N(0,1)| has median 13.5/127 = 0.106)
+    assert float(args[4].median()) > 0.05
     out = ext().int8_decode_attention_forward(*args)
     _check_rows(out, args, [(0, 0), (63, 31), (17, 9), (40, 22)], "config 2 B64 H32 D128 ctx8192 outliers")
     assert torch.isfinite(out.float()).all()

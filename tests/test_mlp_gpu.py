@@ -243,3 +243,31 @@ def test_full_size_config_properties(M, dm, dff):
     ref = omlp.kernel_mlp(xi[0, sub].cpu().numpy(), w1i, w2i, sx.reshape(-1)[sub].cpu().numpy(), s1, s2,
                           b1=b1.cpu().numpy())
     _compare_with_kernel_oracle(out_s[0].cpu().numpy(), osc_s.cpu().numpy(), ref)
+
+
+def test_reference_rounding_mode_matches_the_stage_by_stage_restatement():
+    """With I8TK_MLP_REFERENCE_ROUNDING the first epilogue follows the reference's source operation by
+    operation (kernels/int8_mlp.cu:437-440, kernels/int8_common.cuh:9-13), so what is left against
+    oracle.mlp.kernel_mlp is tanhf against numpy's tanh (an ulp now and then): at least ten times
+    fewer differing codes than the default build, and none off by more than one step."""
+    rng = np.random.default_rng(77)
+    T, dm, dff = 512, 768, 3072
+    x = rng.standard_normal((T, dm)).astype(np.float16)
+    W1 = (rng.standard_normal((dm, dff)) * 0.02).astype(np.float32)
+    W2 = (rng.standard_normal((dff, dm)) * 0.02).astype(np.float32)
+    b1 = (rng.standard_normal(dff) * 0.01).astype(np.float32)
+    args = _prep(x, W1, W2)
+    ref = omlp.kernel_mlp(*args, b1=b1)
+    fast_i8, fast_sc = _run_pc(*args, b1=b1)
+    was = ext().set_mlp_reference_rounding(True)
+    try:
+        exact_i8, exact_sc = _run_pc(*args, b1=b1)
+    finally:
+        ext().set_mlp_reference_rounding(was)
+    rate_fast = float((fast_i8 != ref["out_i8"]).mean())
+    rate_exact = float((exact_i8 != ref["out_i8"]).mean())
+    print(f"int8 output codes differing from the restatement: default {100 * rate_fast:.3f} %, "
+          f"reference rounding {100 * rate_exact:.4f} %")
+    assert np.abs(exact_i8.astype(np.int32) - ref["out_i8"].astype(np.int32)).max() <= 1
+    assert rate_exact <= max(1e-4, rate_fast / 10.0), (rate_exact, rate_fast)
+    assert np.allclose(exact_sc, ref["out_scale"], rtol=1e-5, atol=0)
