@@ -29,7 +29,7 @@ typedef void* i8tk_stream_t;
 enum i8tk_status {
     I8TK_OK = 0,
     I8TK_ERR_INVALID_ARGUMENT = 1,  /* null pointer, non-positive size, bad flag      */
-    I8TK_ERR_UNSUPPORTED = 2,       /* head_dim not in {64,128}, MLP width not % 128  */
+    I8TK_ERR_UNSUPPORTED = 2,       /* a head_dim the kernel does not take, a shape too large */
     I8TK_ERR_WORKSPACE = 3,         /* workspace null or smaller than *_workspace_bytes */
     I8TK_ERR_ALIGNMENT = 4,         /* pointer not aligned as documented              */
     I8TK_ERR_CUDA = 5,              /* a CUDA runtime/driver call or launch failed    */
@@ -153,6 +153,21 @@ int i8tk_decode_attention_forward(const int8_t* Q, const int8_t* K, const int8_t
                                   int BH, int S, int head_dim,
                                   void* workspace, size_t workspace_bytes,
                                   i8tk_stream_t stream);
+
+/* The same forward with the result leaving as INT8 for the GEMM that follows attention (the
+ * output projection): one scale per token over its heads*head_dim outputs,
+ *   out_scales[b] = max(|fp16 out[b]|, 1e-8) / 127,   out_i8[b][:] = rne(fp16 out[b][:] / scale)
+ * -- exactly what i8tk_quantize_per_token_f16 gives on the fp16 result viewed as
+ * [batch, heads*head_dim], without writing and re-reading that tensor (the eager
+ * quantise-after-attention step of bench/bench_block.py:107-113; OPTIMIZATION.md:241-246).
+ *   out_i8 int8 [batch, heads*head_dim]; out_scales fp32 [batch]; out_f16 fp16 [batch*heads,
+ *   head_dim] or NULL.  1 <= heads <= 32.  Workspace as i8tk_decode_attention_forward with
+ *   BH = batch*heads.  No counterpart among the reference's launchers. */
+int i8tk_decode_attention_forward_q8(const int8_t* Q, const int8_t* K, const int8_t* V,
+                                     int8_t* out_i8, float* out_scales, void* out_f16,
+                                     const float* sQ, const float* sK, const float* sV,
+                                     int batch, int heads, int S, int head_dim,
+                                     void* workspace, size_t workspace_bytes, i8tk_stream_t stream);
 
 /* The same operation for callers that must not allocate device memory and have
  * no spare buffer to lend: plugin "enqueue" hooks of serving runtimes, code
@@ -316,11 +331,15 @@ int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V, vo
  *                   token and its scales written here.  NULL: legacy dynamic
  *                   per-tensor output scale, written to *out_tensor_scale.
  *   out_tensor_scale device fp32[1] or NULL (required when out_row_scales is NULL)
- * d_model and d_ff must be multiples of 128 (other widths return
- * I8TK_ERR_UNSUPPORTED); T is any positive row count -- the reference gates all
- * three on 128 and otherwise takes a static-scale fallback that leaves
- * out_row_scales unwritten (kernels/int8_mlp.cu:1023-1026,1194-1225).
- * All pointers 16-byte aligned.
+ * Any positive T, d_model and d_ff.  Widths that are multiples of 128 run in place (all
+ * pointers 16-byte aligned); other widths are first copied into zero-padded buffers of the
+ * next multiple of 128 inside the workspace, which changes no result (no alignment needed
+ * then).  The reference gates T, d_model and d_ff on 128 and otherwise takes scalar kernels
+ * under static scales that leave out_row_scales unwritten
+ * (kernels/int8_mlp.cu:1023-1026,1194-1225); that arithmetic is available here, for any
+ * shape, as I8TK_MLP_STATIC_SCALES: per-tensor scales only, no bias, hidden codes under the
+ * scale sx*sW1*d_model and output codes under that * sW2 * d_ff, which is written to
+ * *out_tensor_scale (out_row_scales must be NULL).
  *
  * Rounding of the first epilogue.  By default v = fma(acc*sx, sW1, b1) and GELU uses the
  * hardware tanh approximation (relative error 2^-11, the size of the fp16 rounding that
@@ -335,7 +354,8 @@ enum i8tk_mlp_flags {
     I8TK_MLP_X_PER_TOKEN = 1,
     I8TK_MLP_W_PER_CHANNEL = 2,
     I8TK_MLP_PREPACKED = 4,
-    I8TK_MLP_REFERENCE_ROUNDING = 8
+    I8TK_MLP_REFERENCE_ROUNDING = 8,
+    I8TK_MLP_STATIC_SCALES = 16
 };
 size_t i8tk_mlp_workspace_bytes(int T, int d_model, int d_ff, int flags);
 int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out,
@@ -343,6 +363,17 @@ int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t
                      const float* bias1, float* out_row_scales, float* out_tensor_scale,
                      int T, int d_model, int d_ff, int flags,
                      void* workspace, size_t workspace_bytes, i8tk_stream_t stream);
+
+/* One INT8 GEMM of the MLP on its own: out fp16 [T, N] = (x . W) * scale_x[row] * scale_W[col]
+ * (+ bias[col]), x int8 [T, K], W int8 [K, N] (or [N, K] with I8TK_MLP_PREPACKED), scale_x fp32
+ * [T] with I8TK_MLP_X_PER_TOKEN else [1], scale_W fp32 [N] with I8TK_MLP_W_PER_CHANNEL else [1].
+ * The tensor-core kernel of i8tk_mlp_forward with its plain epilogue
+ * (kernels/int8_mlp.cu:333-485 with apply_gelu = false and no row statistics); used for the
+ * attention output projection when attention hands over INT8 (i8tk_decode_attention_forward_q8).
+ * K and N multiples of 128; workspace: 256 bytes (the status block). */
+int i8tk_linear_i8_f16(const int8_t* x, const int8_t* W, const float* scale_x, const float* scale_W,
+                       const float* bias, void* out_f16, int T, int K, int N, int flags,
+                       void* workspace, size_t workspace_bytes, i8tk_stream_t stream);
 
 /* W1 [d_model,d_ff] -> W1T [d_ff,d_model]; W2 [d_ff,d_model] -> W2T [d_model,d_ff].
  * Replaces transpose_int8_weights (kernels/int8_ext.cu:58-61,

@@ -22,6 +22,7 @@ MLP_X_PER_TOKEN = 1
 MLP_W_PER_CHANNEL = 2
 MLP_PREPACKED = 4
 MLP_REFERENCE_ROUNDING = 8
+MLP_STATIC_SCALES = 16
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
@@ -46,6 +47,7 @@ SIGNATURES = {
     "i8tk_dequantize_int8_to_fp16": (_i, [_vp, _vp, _f, _i64, _vp]),
     "i8tk_decode_workspace_bytes": (_sz, [_i, _i, _i]),
     "i8tk_decode_attention_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "i8tk_decode_attention_forward_q8": (_i, [_vp] * 9 + [_i] * 4 + [_vp, _sz, _vp]),
     "i8tk_decode_static_scratch_bytes": (_sz, []),
     "i8tk_decode_attention_forward_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "i8tk_decode_static_check_status": (_i, [_vp]),
@@ -64,6 +66,7 @@ SIGNATURES = {
     "i8tk_mlp_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "i8tk_mlp_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                               _i, _i, _i, _i, _vp, _sz, _vp]),
+    "i8tk_linear_i8_f16": (_i, [_vp] * 6 + [_i] * 4 + [_vp, _sz, _vp]),
     "i8tk_transpose_int8_weights": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
 }
 

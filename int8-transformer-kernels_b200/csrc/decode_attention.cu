@@ -565,15 +565,27 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
 // ---------------------------------------------------------------------------
 // RAGGED (with FLAT): the rows were written under the device-side plan of a paged cache; a
 // request without positions gets a zero output row.
-template <int D, bool FLAT, bool RAGGED = false>
-__global__ void __launch_bounds__(128)
+// QUANT: one CTA per request with one warp per head (blockDim = 32 * heads); besides (or
+// instead of) the fp16 row, the token's heads*D outputs leave as int8 codes with ONE scale per
+// token -- the input format of the INT8 GEMM that follows attention (the output projection):
+// scale = max(|fp16 out|, 1e-8) / 127 over the whole token, code = rne(fp16 out / scale), the
+// per-token quantiser's arithmetic (tests/test_int8.py:47-63) on the fp16 values.
+struct QuantOut {
+    int8_t* codes;           // [B][heads * D]
+    float* scales;           // [B]
+};
+
+template <int D, bool FLAT, bool RAGGED = false, bool QUANT = false>
+__global__ void __launch_bounds__(QUANT ? 1024 : 128)
 decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, DecodePlan plan,
-                      __half* __restrict__ out, float* __restrict__ row_out, PagedKV pg) {
+                      __half* __restrict__ out, float* __restrict__ row_out, PagedKV pg, QuantOut qo) {
     constexpr int ROW = D + 4;
     constexpr int DPL = D / 32;
+    [[maybe_unused]] __shared__ float head_max[32];
     pdl_wait();                                 // rows of the scan launched just before this kernel
-    const int bh = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (bh >= BH) return;
+    const int wpc = QUANT ? (int)(blockDim.x >> 5) : 4;      // (b,h) rows per CTA
+    const int bh = blockIdx.x * wpc + (threadIdx.x >> 5);
+    if (!QUANT && bh >= BH) return;
     const int lane = threadIdx.x & 31;
 
     int c_first = 0, n = nparts;
@@ -629,6 +641,38 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, Decode
         }
     }
 
+    if constexpr (QUANT) {
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        float v[DPL];
+        float amax = 0.f;
+#pragma unroll
+        for (int k = 0; k < DPL; ++k) {
+            v[k] = __half2float(__float2half_rn(a[k] * inv));        // the fp16 output, widened again
+            amax = fmaxf(amax, fabsf(v[k]));
+        }
+        amax = warp_max(amax);
+        if (lane == 0) head_max[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        float tmax = lane < wpc ? head_max[lane] : 0.f;
+        tmax = fmaxf(warp_max(tmax), 1e-8f);
+        const float scale = __fdiv_rn(tmax, 127.f);
+        uint32_t packed = 0;
+#pragma unroll
+        for (int k = 0; k < DPL; ++k) {
+            const int c = __float2int_rn(fmaxf(-128.f, fminf(127.f, __fdiv_rn(v[k], scale))));
+            packed |= (uint32_t)(c & 0xff) << (8 * k);
+        }
+        int8_t* q = qo.codes + (size_t)bh * D + lane * DPL;
+        if constexpr (DPL == 4) *reinterpret_cast<uint32_t*>(q) = packed;
+        else *reinterpret_cast<uint16_t*>(q) = (uint16_t)packed;
+        if (threadIdx.x == 0) qo.scales[blockIdx.x] = scale;
+        if (out != nullptr) {
+            __half* o = out + (size_t)bh * D + lane * DPL;
+#pragma unroll
+            for (int k = 0; k < DPL; ++k) o[k] = __float2half_rn(v[k]);
+        }
+        return;
+    }
     if (out != nullptr) {
         const float inv = L > 0.f ? 1.0f / L : 0.f;     // no positions at all: zeros
         __half* o = out + (size_t)bh * D + lane * DPL;
@@ -905,7 +949,7 @@ int launch_partial(const int8_t* Q, const int8_t* K, const int8_t* V, const floa
 template <int D>
 int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, float* part,
                   const float* sQ, const float* sK, const float* sV, int BH, int S,
-                  void* workspace, size_t wbytes, cudaStream_t stream) {
+                  void* workspace, size_t wbytes, cudaStream_t stream, QuantOut qo = QuantOut{}, int heads = 0) {
     using T = DecodeTraits<D>;
     const DecodePlan p = make_plan(BH, S, D, sm_count());
     const size_t need = 256 + rows_bytes(p, D);
@@ -924,8 +968,13 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
         rc = launch_partial<D, false>(Q, K, V, sQ, sK, sV, rows, S, p, status, stream);
     if (rc != I8TK_OK) return rc;
     // the merge may be scheduled while the scan drains: it waits (pdl_wait) for the scan's rows
+    if (qo.codes != nullptr) {
+        I8TK_CUDA(launch_after(decode_combine_kernel<D, true, false, true>, dim3(BH / heads), dim3(32 * heads), 0,
+                               stream, (const float*)rows, BH, 0, p, out, part, PagedKV{}, qo));
+        return I8TK_OK;
+    }
     I8TK_CUDA(launch_after(decode_combine_kernel<D, true>, dim3((BH + 3) / 4), dim3(128), 0, stream,
-                           (const float*)rows, BH, 0, p, out, part, PagedKV{}));
+                           (const float*)rows, BH, 0, p, out, part, PagedKV{}, QuantOut{}));
     return I8TK_OK;
 }
 
@@ -1008,6 +1057,31 @@ extern "C" int i8tk_decode_attention_forward(const int8_t* Q, const int8_t* K, c
                                  workspace, workspace_bytes, st);
     return launch_decode<128>(Q, K, V, static_cast<__half*>(out_f16), nullptr, sQ, sK, sV, BH, S,
                               workspace, workspace_bytes, st);
+}
+
+extern "C" int i8tk_decode_attention_forward_q8(const int8_t* Q, const int8_t* K, const int8_t* V,
+                                                int8_t* out_i8, float* out_scales, void* out_f16,
+                                                const float* sQ, const float* sK, const float* sV,
+                                                int batch, int heads, int S, int head_dim,
+                                                void* workspace, size_t workspace_bytes, i8tk_stream_t stream) {
+    I8TK_REQUIRE(out_i8 && out_scales, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(batch > 0 && heads > 0 && heads <= 32, I8TK_ERR_UNSUPPORTED,
+                 "per-token output quantisation takes 1..32 heads (one warp per head), got %d", heads);
+    I8TK_REQUIRE((long long)batch * heads < (1ll << 31), I8TK_ERR_UNSUPPORTED, "batch * heads too large");
+    I8TK_REQUIRE(aligned_to(out_i8, 4) && aligned_to(out_scales, 4), I8TK_ERR_ALIGNMENT,
+                 "out_i8 and out_scales must be 4-byte aligned");
+    const int BH = batch * heads;
+    // the fp16 row is optional here: any aligned non-null pointer satisfies the common checks
+    const int rc = check_decode_args(Q, K, V, out_f16 ? out_f16 : static_cast<void*>(out_i8), sQ, sK, sV, BH, S, head_dim);
+    if (rc != I8TK_OK) return rc;
+    I8TK_REQUIRE(out_f16 != nullptr || aligned_to(out_i8, 16), I8TK_ERR_ALIGNMENT, "out_i8 must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const QuantOut qo{out_i8, out_scales};
+    if (head_dim == 64)
+        return launch_decode<64>(Q, K, V, static_cast<__half*>(out_f16), nullptr, sQ, sK, sV, BH, S, workspace,
+                                 workspace_bytes, st, qo, heads);
+    return launch_decode<128>(Q, K, V, static_cast<__half*>(out_f16), nullptr, sQ, sK, sV, BH, S, workspace,
+                              workspace_bytes, st, qo, heads);
 }
 
 extern "C" size_t i8tk_decode_static_scratch_bytes(void) { return kStaticScratchBytes; }
@@ -1154,12 +1228,12 @@ extern "C" int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool
         rc = launch_partial<64, true, true>(Q, K_pool, V_pool, sQ, sK_pool, sV_pool, rows, max_seq_len, p, status, st, pg);
         if (rc != I8TK_OK) return rc;
         I8TK_CUDA(launch_after(decode_combine_kernel<64, true, true>, dim3((BH + 3) / 4), dim3(128), 0, st,
-                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr, pg));
+                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr, pg, QuantOut{}));
     } else {
         rc = launch_partial<128, true, true>(Q, K_pool, V_pool, sQ, sK_pool, sV_pool, rows, max_seq_len, p, status, st, pg);
         if (rc != I8TK_OK) return rc;
         I8TK_CUDA(launch_after(decode_combine_kernel<128, true, true>, dim3((BH + 3) / 4), dim3(128), 0, st,
-                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr, pg));
+                               (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr, pg, QuantOut{}));
     }
     return I8TK_OK;
 }
@@ -1191,10 +1265,10 @@ extern "C" int i8tk_decode_combine_partials(const float* parts, int nparts, int 
     const DecodePlan none{};
     if (head_dim == 64)
         decode_combine_kernel<64, false><<<grid, 128, 0, st>>>(parts, BH, nparts, none,
-                                                               static_cast<__half*>(out_f16), nullptr, PagedKV{});
+                                                               static_cast<__half*>(out_f16), nullptr, PagedKV{}, QuantOut{});
     else
         decode_combine_kernel<128, false><<<grid, 128, 0, st>>>(parts, BH, nparts, none,
-                                                                static_cast<__half*>(out_f16), nullptr, PagedKV{});
+                                                                static_cast<__half*>(out_f16), nullptr, PagedKV{}, QuantOut{});
     I8TK_CUDA(cudaGetLastError());
     return I8TK_OK;
 }

@@ -86,6 +86,10 @@ struct EpiParams {
     // marks as not yet written (the caller fills the array with 0xFF bytes)
     uint32_t* row_parts;
     int a_from_prev;          // A is written by the kernel launched just before this one
+    // static-scale mode (non-fused kernels): when set, the epilogue writes int8 codes
+    // rne(clamp(v * static_inv[0])) to C8 instead of fp16 to C
+    const float* static_inv;
+    int clear_status;         // this launch is the first of its call: it clears the call's status word
 };
 
 // GELU, tanh form: 0.5 x (1 + tanh(y)), y = kC (x + kA x^3)
@@ -366,6 +370,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             pf_sa = ld_nc_now(ep.a_per_row ? ep.scale_a + min(pm0 + q * 32 + lane, M - 1) : ep.scale_a);
         };
         pdl_wait();     // row scales and the row-maxima flags come from the kernels before this one
+        if (ep.clear_status && blockIdx.x == 0 && ew == 0 && lane == 0) clear_call_status(status);
         if ((int)blockIdx.x < num_tiles) prefetch(blockIdx.x);
 
         // Requantisation of a tile whose fp16 values sit in this warp's stash: wait for the
@@ -462,6 +467,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 const uint32_t* rr = r[cc & 1];
                 uint32_t packed[8];
+                [[maybe_unused]] float vf[FUSED ? 1 : 16];    // non-fused: the fp32 values, for the static-scale store
 #pragma unroll
                 for (int j = 0; j < 16; j += 4) {
                     const float4 s4 = *reinterpret_cast<const float4*>(sb + cc * 16 + j);
@@ -481,6 +487,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                     }
                     const float2 a = unpack2(v01), b = unpack2(v23);
+                    if constexpr (!FUSED) {
+                        vf[j] = a.x; vf[j + 1] = a.y; vf[j + 2] = b.x; vf[j + 3] = b.y;
+                    }
                     rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(a.x), fabsf(a.y))), fmaxf(fabsf(b.x), fabsf(b.y)));
                     const __half2 ha = __floats2half2_rn(a.x, a.y);
                     const __half2 hb = __floats2half2_rn(b.x, b.y);
@@ -490,6 +499,26 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if constexpr (FUSED) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) hv[cc * 8 + j] = packed[j];
+                } else if (ep.static_inv != nullptr) {
+                    // static-scale mode: the code is rne(clamp(v * inv)) of the fp32 value
+                    // (kernels/int8_mlp.cu:905-909, kernels/int8_common.cuh:17-19); this lane's
+                    // 16 codes are 16 contiguous bytes of its row
+                    const float inv = *ep.static_inv;
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t w = 0;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float v = vf[4 * j + e];
+                            const int c = __float2int_rn(fmaxf(-128.f, fminf(127.f, v * inv)));
+                            w |= (uint32_t)(c & 0xff) << (8 * e);
+                        }
+                        w4[j] = w;
+                    }
+                    if (m0 + q * 32 + lane < M)
+                        *reinterpret_cast<uint4*>(ep.C8 + (size_t)(m0 + q * 32 + lane) * N + n0 + c0 + cc * 16) =
+                            make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 } else {
                     // 32 rows x 32 bytes through this warp's staging block, so that two lanes
                     // store each row's 32 bytes and a store instruction covers 16 rows
@@ -795,6 +824,7 @@ int requant_grid(long long vecs) {
 struct MlpWorkspace {
     uint32_t* status;
     float* tensor_absmax; // [1]   starts at zero (legacy per-tensor output scale only)
+    float* static_scales; // [4]   static-scale mode: hidden scale, its inverse, output scale, its inverse
     uint32_t* parts1;     // [T/128][d_ff / BN1][128]     row maxima of GEMM1 per tile; these two
     uint32_t* parts2;     // [T/128][d_model / BN2][128]  are contiguous and start as 0xFF bytes
     float* hid_scale;     // [T]
@@ -804,6 +834,7 @@ struct MlpWorkspace {
     size_t ones_bytes;    // parts1 .. parts2
 };
 
+// d_model and d_ff are multiples of 128 here (the caller pads other widths first).
 MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
     MlpWorkspace w{};
     size_t off = 0;
@@ -811,7 +842,8 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
     unsigned char* b = static_cast<unsigned char*>(base);
     const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
     const size_t o_status = take(256);
-    const size_t o_tabs = take(256);
+    const size_t o_tabs = take(128);
+    const size_t o_stat = take(128);
     const size_t Tp = (size_t)((T + 127) / 128) * 128;       // rows of the flag arrays: whole row blocks
     const size_t o_p1 = take(Tp * (d_ff / pick_bn(T, d_ff, b_mn, true)) * 4);
     const size_t o_p2 = take(Tp * (d_model / pick_bn(T, d_model, b_mn, true)) * 4);
@@ -824,6 +856,7 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
     if (b) {
         w.status = reinterpret_cast<uint32_t*>(b + o_status);
         w.tensor_absmax = reinterpret_cast<float*>(b + o_tabs);
+        w.static_scales = reinterpret_cast<float*>(b + o_stat);
         w.parts1 = reinterpret_cast<uint32_t*>(b + o_p1);
         w.parts2 = reinterpret_cast<uint32_t*>(b + o_p2);
         w.hid_scale = reinterpret_cast<float*>(b + o_hsc);
@@ -831,6 +864,146 @@ MlpWorkspace carve(void* base, int T, int d_model, int d_ff, int flags) {
         w.out_f16 = reinterpret_cast<__half*>(b + o_o16);
     }
     return w;
+}
+
+// Static-scale mode (kernels/int8_mlp.cu:830-844): hidden scale = sx*sw1*d_model (a bound that
+// holds for any input), output scale = that * sw2 * d_ff; both with their reciprocals.  The
+// widths are the caller's, not the padded ones.  Also clears the call's status word.
+__global__ void static_scales_kernel(const float* __restrict__ sx, const float* __restrict__ sw1,
+                                     const float* __restrict__ sw2, float* __restrict__ out4,
+                                     float* __restrict__ out_tensor_scale, int d_model, int d_ff,
+                                     uint32_t* __restrict__ status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if (threadIdx.x != 0) return;
+    clear_call_status(status);
+    const float sh = sx[0] * sw1[0] * (float)d_model;
+    const float so = sh * sw2[0] * (float)d_ff;
+    out4[0] = sh;
+    out4[1] = 1.f / sh;
+    out4[2] = so;
+    out4[3] = 1.f / so;
+    if (out_tensor_scale) *out_tensor_scale = so;
+}
+
+// Zero-padded copy of a row-major matrix of `elem`-byte elements: dst [drows][dcols] receives
+// src [srows][scols] in its top-left corner and zeros elsewhere (either may be the larger one
+// in each dimension: the same kernel crops).  One thread per destination element.
+__global__ void __launch_bounds__(256)
+pad_copy_kernel(const unsigned char* __restrict__ src, long long srows, long long scols,
+                unsigned char* __restrict__ dst, long long drows, long long dcols, int elem) {
+    const long long total = drows * dcols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / dcols, c = i - r * dcols;
+        const bool in = r < srows && c < scols;
+        for (int e = 0; e < elem; ++e) dst[i * elem + e] = in ? src[(r * scols + c) * elem + e] : (unsigned char)0;
+    }
+}
+
+int pad_copy(const void* src, long long srows, long long scols, void* dst, long long drows, long long dcols,
+             int elem, cudaStream_t st) {
+    const long long total = drows * dcols;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148ll * 16) blocks = 148ll * 16;
+    if (blocks < 1) blocks = 1;
+    pad_copy_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const unsigned char*>(src), srows, scols,
+                                                      static_cast<unsigned char*>(dst), drows, dcols, elem);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
+}
+
+inline int pad128(int v) { return (v + 127) / 128 * 128; }
+
+// Buffers of the padded route (widths that are not multiples of 128), behind the core's workspace.
+struct PadLayout {
+    size_t x, w1, w2, s1, s2, b1, out, total;
+};
+PadLayout pad_layout(size_t core_bytes, int T, int dmp, int dffp) {
+    PadLayout l;
+    size_t off = core_bytes;
+    auto take = [&](size_t n) { size_t o = off; off = round_up(off + n, 256); return o; };
+    l.x = take((size_t)T * dmp);
+    l.w1 = take((size_t)dmp * dffp);
+    l.w2 = take((size_t)dmp * dffp);
+    l.s1 = take((size_t)dffp * 4);
+    l.s2 = take((size_t)dmp * 4);
+    l.b1 = take((size_t)dffp * 4);
+    l.out = take((size_t)T * dmp);
+    l.total = off;
+    return l;
+}
+
+// The forward on widths that are multiples of 128.  `true_dm` / `true_dff` are the caller's
+// widths (they differ from d_model / d_ff on the padded route and only enter the static scales).
+int mlp_core(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out, const float* scale_x,
+             const float* scale_W1, const float* scale_W2, const float* bias1, float* out_row_scales,
+             float* out_tensor_scale, int T, int d_model, int d_ff, int true_dm, int true_dff, int flags,
+             const MlpWorkspace& w, cudaStream_t st) {
+    // Weights as the caller holds them ([K][N], N contiguous) are read in place through
+    // MN-major operand descriptors; prepacked ones ([N][K]) through K-major descriptors.
+    const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
+    const bool exact = (flags & I8TK_MLP_REFERENCE_ROUNDING) != 0;
+    int rc;
+    const int per_token = (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0;
+    const int per_channel = (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0;
+
+    if (flags & I8TK_MLP_STATIC_SCALES) {
+        // GEMM1 writes int8 hidden codes under the static hidden scale, GEMM2 int8 output codes
+        // under the static output scale (kernels/int8_mlp.cu:1194-1225); no row maxima, no fp16.
+        I8TK_CUDA(launch_after(static_scales_kernel, dim3(1), dim3(32), 0, st, scale_x, scale_W1, scale_W2,
+                               w.static_scales, out_tensor_scale, true_dm, true_dff, w.status));
+        EpiParams e1{scale_x, scale_W1, nullptr, nullptr, nullptr, 0, 0, w.hid_i8, nullptr, nullptr, 1,
+                     w.static_scales + 1, 0};
+        rc = exact ? launch_gemm<128, true, false, false, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st)
+                   : launch_gemm<128, true, false, false, false>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
+        if (rc != I8TK_OK) return rc;
+        EpiParams e2{w.static_scales, scale_W2, nullptr, nullptr, nullptr, 0, 0, out, nullptr, nullptr, 1,
+                     w.static_scales + 3, 0};
+        return launch_gemm<128, false, false, false, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
+    }
+
+    // presets: row-maxima flags all ones, the tensor-wide maximum zero, the call's status word
+    // clear.  A kernel rather than a memset so that GEMM1 can be launched behind it
+    // programmatically and set itself up meanwhile.
+    {
+        const size_t words = w.ones_bytes / 16;
+        int blocks = (int)((words + 255) / 256);
+        if (blocks > 296) blocks = 296;
+        if (blocks < 1) blocks = 1;
+        I8TK_CUDA(launch_after(preset_kernel, dim3(blocks), dim3(256), 0, st, reinterpret_cast<uint4*>(w.parts1),
+                               words, w.tensor_absmax, w.status));
+    }
+
+    // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token inside the
+    // GEMM's epilogue: the fp16 values of a tile wait in shared memory while the row
+    // maxima of its row block (12-16 tiles on as many SMs) are exchanged through global
+    // memory, and are quantised one tile later, when that exchange has long finished.
+    {
+        EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, per_token, per_channel,
+                     w.hid_i8, w.hid_scale, w.parts1, 0, nullptr, 0};
+        if (exact)
+            rc = launch_gemm_bn<true, true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
+        else
+            rc = launch_gemm_bn<true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
+        if (rc != I8TK_OK) return rc;
+    }
+    if (out_row_scales) {
+        // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way, but
+        // at once: with K = d_ff the MMAs of the next tile cover the exchange
+        EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, nullptr, 1, per_channel,
+                     out, out_row_scales, w.parts2, 1, nullptr, 0};
+        return launch_gemm_bn<false, true, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
+    }
+    // legacy per-tensor output scale: fp16 out + global absmax, then one requant pass
+    EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, w.tensor_absmax, 1, per_channel,
+                 nullptr, nullptr, nullptr, 1, nullptr, 0};
+    rc = launch_gemm_bn<false, false, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
+    if (rc != I8TK_OK) return rc;
+    requant_tensor_kernel<<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
+        w.out_f16, w.tensor_absmax, out, out_tensor_scale, T, d_model);
+    I8TK_CUDA(cudaGetLastError());
+    return I8TK_OK;
 }
 
 }  // namespace
@@ -850,9 +1023,32 @@ extern "C" int i8tk_transpose_int8_weights(const int8_t* W1, const int8_t* W2, i
     return transpose_i8(W2, W2T, d_ff, d_model, st);
 }
 
+extern "C" int i8tk_linear_i8_f16(const int8_t* x, const int8_t* W, const float* scale_x, const float* scale_W,
+                                  const float* bias, void* out_f16, int T, int K, int N, int flags,
+                                  void* workspace, size_t workspace_bytes, i8tk_stream_t stream) {
+    I8TK_REQUIRE(x && W && scale_x && scale_W && out_f16, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
+    I8TK_REQUIRE(T > 0 && K > 0 && N > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
+    I8TK_REQUIRE((flags & ~(I8TK_MLP_PREPACKED | I8TK_MLP_X_PER_TOKEN | I8TK_MLP_W_PER_CHANNEL)) == 0,
+                 I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
+    I8TK_REQUIRE(K % 128 == 0 && N % 128 == 0, I8TK_ERR_UNSUPPORTED,
+                 "K and N must be multiples of 128 (got %d, %d)", K, N);
+    I8TK_REQUIRE(aligned_to(x, 16) && aligned_to(W, 16) && aligned_to(out_f16, 16), I8TK_ERR_ALIGNMENT,
+                 "x, W and out must be 16-byte aligned");
+    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= 256 && aligned_to(workspace, 256), I8TK_ERR_WORKSPACE,
+                 "workspace: 256 bytes, 256-byte aligned (the status block)");
+    const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
+    EpiParams e{scale_x, scale_W, bias, static_cast<__half*>(out_f16), nullptr, (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0,
+                (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0, nullptr, nullptr, nullptr, 0, nullptr, 1};
+    return launch_gemm_bn<false, false, false>(x, W, b_mn, e, T, N, K, static_cast<uint32_t*>(workspace),
+                                               static_cast<cudaStream_t>(stream));
+}
+
 extern "C" size_t i8tk_mlp_workspace_bytes(int T, int d_model, int d_ff, int flags) {
     if (T <= 0 || d_model <= 0 || d_ff <= 0) return 0;
-    return carve(nullptr, T, d_model, d_ff, flags).bytes;
+    const int dmp = pad128(d_model), dffp = pad128(d_ff);
+    const size_t core = carve(nullptr, T, dmp, dffp, flags).bytes;
+    if (dmp == d_model && dffp == d_ff) return core;
+    return pad_layout(core, T, dmp, dffp).total;
 }
 
 extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out,
@@ -865,64 +1061,63 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     I8TK_REQUIRE(out_row_scales || out_tensor_scale, I8TK_ERR_INVALID_ARGUMENT,
                  "one of out_row_scales / out_tensor_scale must be given");
     I8TK_REQUIRE(T > 0 && d_model > 0 && d_ff > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
-    I8TK_REQUIRE((flags & ~15) == 0, I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
-    I8TK_REQUIRE(d_model % 128 == 0 && d_ff % 128 == 0, I8TK_ERR_UNSUPPORTED,
-                 "d_model and d_ff must be multiples of 128 (got %d, %d)", d_model, d_ff);
-    I8TK_REQUIRE(aligned_to(x, 16) && aligned_to(W1, 16) && aligned_to(W2, 16) && aligned_to(out, 16),
-                 I8TK_ERR_ALIGNMENT, "x, W1, W2 and out must be 16-byte aligned");
-    const MlpWorkspace w = carve(workspace, T, d_model, d_ff, flags);
-    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= w.bytes, I8TK_ERR_WORKSPACE,
-                 "mlp workspace too small: need %zu bytes, got %zu", w.bytes, workspace_bytes);
+    I8TK_REQUIRE((flags & ~31) == 0, I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
+    if (flags & I8TK_MLP_STATIC_SCALES) {
+        I8TK_REQUIRE(!(flags & (I8TK_MLP_X_PER_TOKEN | I8TK_MLP_W_PER_CHANNEL)) && bias1 == nullptr &&
+                         out_row_scales == nullptr && out_tensor_scale != nullptr,
+                     I8TK_ERR_INVALID_ARGUMENT,
+                     "static-scale mode takes per-tensor scales, no bias, and reports one output scale");
+    }
+    const int dmp = pad128(d_model), dffp = pad128(d_ff);
+    const bool padded = dmp != d_model || dffp != d_ff;
+    const size_t core_bytes = carve(nullptr, T, dmp, dffp, flags).bytes;
+    const size_t need = padded ? pad_layout(core_bytes, T, dmp, dffp).total : core_bytes;
+    I8TK_REQUIRE(workspace != nullptr && workspace_bytes >= need, I8TK_ERR_WORKSPACE,
+                 "mlp workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
     I8TK_REQUIRE(aligned_to(workspace, 256), I8TK_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-
-    // Weights as the caller holds them ([K][N], N contiguous) are read in place through
-    // MN-major operand descriptors; prepacked ones ([N][K]) through K-major descriptors.
-    const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
-    int rc;
-    const int per_token = (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0;
-    const int per_channel = (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0;
-
-    // presets: row-maxima flags all ones, the tensor-wide maximum zero.  A kernel rather than a
-    // memset so that GEMM1 can be launched behind it programmatically and set itself up meanwhile.
-    {
-        const size_t words = w.ones_bytes / 16;
-        int blocks = (int)((words + 255) / 256);
-        if (blocks > 296) blocks = 296;
-        if (blocks < 1) blocks = 1;
-        I8TK_CUDA(launch_after(preset_kernel, dim3(blocks), dim3(256), 0, st, reinterpret_cast<uint4*>(w.parts1),
-                               words, w.tensor_absmax, w.status));
+    const MlpWorkspace w = carve(workspace, T, dmp, dffp, flags);
+    if (!padded) {
+        I8TK_REQUIRE(aligned_to(x, 16) && aligned_to(W1, 16) && aligned_to(W2, 16) && aligned_to(out, 16),
+                     I8TK_ERR_ALIGNMENT, "x, W1, W2 and out must be 16-byte aligned");
+        return mlp_core(x, W1, W2, out, scale_x, scale_W1, scale_W2, bias1, out_row_scales, out_tensor_scale, T,
+                        d_model, d_ff, d_model, d_ff, flags, w, st);
     }
 
-    // GEMM1: hidden = GELU((x . W1) * sx * sW1 + b1), requantised per token inside the
-    // GEMM's epilogue: the fp16 values of a tile wait in shared memory while the row
-    // maxima of its row block (12-16 tiles on as many SMs) are exchanged through global
-    // memory, and are quantised one tile later, when that exchange has long finished.
-    {
-        EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, per_token, per_channel,
-                     w.hid_i8, w.hid_scale, w.parts1, 0};
-        if (flags & I8TK_MLP_REFERENCE_ROUNDING)
-            rc = launch_gemm_bn<true, true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
-        else
-            rc = launch_gemm_bn<true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
-        if (rc != I8TK_OK) return rc;
-    }
-    if (out_row_scales) {
-        // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way, but
-        // at once: with K = d_ff the MMAs of the next tile cover the exchange
-        EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, nullptr, 1, per_channel,
-                     out, out_row_scales, w.parts2, 1};
-        rc = launch_gemm_bn<false, true, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
-        if (rc != I8TK_OK) return rc;
-        return I8TK_OK;
-    }
-    // legacy per-tensor output scale: fp16 out + global absmax, then one requant pass
-    EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, w.tensor_absmax, 1, per_channel,
-                 nullptr, nullptr, nullptr, 1};
-    rc = launch_gemm_bn<false, false, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
+    // Widths that are not multiples of 128 (the reference sends these to its scalar kernels,
+    // kernels/int8_mlp.cu:1023-1026): operands are copied into zero-padded buffers of the next
+    // multiple of 128 and the tensor-core forward runs on those.  Zero columns of x and zero
+    // rows of W1 add nothing to a dot product; padded hidden channels are GELU(0) = 0, never the
+    // row maximum, and meet zero rows of W2; padded output columns are zero and are cropped.
+    unsigned char* base = static_cast<unsigned char*>(workspace);
+    const PadLayout l = pad_layout(core_bytes, T, dmp, dffp);
+    int8_t* xp = reinterpret_cast<int8_t*>(base + l.x);
+    int8_t* w1p = reinterpret_cast<int8_t*>(base + l.w1);
+    int8_t* w2p = reinterpret_cast<int8_t*>(base + l.w2);
+    float* s1p = reinterpret_cast<float*>(base + l.s1);
+    float* s2p = reinterpret_cast<float*>(base + l.s2);
+    float* b1p = reinterpret_cast<float*>(base + l.b1);
+    int8_t* outp = reinterpret_cast<int8_t*>(base + l.out);
+    const bool prepacked = (flags & I8TK_MLP_PREPACKED) != 0;
+    const bool per_channel = (flags & I8TK_MLP_W_PER_CHANNEL) != 0;
+    int rc = pad_copy(x, T, d_model, xp, T, dmp, 1, st);
     if (rc != I8TK_OK) return rc;
-    requant_tensor_kernel<<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
-        w.out_f16, w.tensor_absmax, out, out_tensor_scale, T, d_model);
-    I8TK_CUDA(cudaGetLastError());
-    return I8TK_OK;
+    rc = prepacked ? pad_copy(W1, d_ff, d_model, w1p, dffp, dmp, 1, st) : pad_copy(W1, d_model, d_ff, w1p, dmp, dffp, 1, st);
+    if (rc != I8TK_OK) return rc;
+    rc = prepacked ? pad_copy(W2, d_model, d_ff, w2p, dmp, dffp, 1, st) : pad_copy(W2, d_ff, d_model, w2p, dffp, dmp, 1, st);
+    if (rc != I8TK_OK) return rc;
+    if (per_channel) {
+        rc = pad_copy(scale_W1, 1, d_ff, s1p, 1, dffp, 4, st);
+        if (rc != I8TK_OK) return rc;
+        rc = pad_copy(scale_W2, 1, d_model, s2p, 1, dmp, 4, st);
+        if (rc != I8TK_OK) return rc;
+    }
+    if (bias1) {
+        rc = pad_copy(bias1, 1, d_ff, b1p, 1, dffp, 4, st);
+        if (rc != I8TK_OK) return rc;
+    }
+    rc = mlp_core(xp, w1p, w2p, outp, scale_x, per_channel ? s1p : scale_W1, per_channel ? s2p : scale_W2,
+                  bias1 ? b1p : nullptr, out_row_scales, out_tensor_scale, T, dmp, dffp, d_model, d_ff, flags, w, st);
+    if (rc != I8TK_OK) return rc;
+    return pad_copy(outp, T, dmp, out, T, d_model, 1, st);
 }

@@ -35,8 +35,10 @@
 // * Every mbarrier wait is bounded; on expiry a status word is set and all
 //   roles fall through to the common exit, which frees tensor memory.
 //
-// Supported: head_dim 64 or 128, any seq_len (a partial last tile is masked: the operand tiles
-// then hold rows of the next head or TMA's zero fill, whose scores are set to -inf).
+// Supported: head_dim 64, 128 (KV tiles of 128 positions) and 256 (tiles of 64: the score, P and
+// 256-column output accumulators of a 128-position tile exceed tensor memory), any seq_len (a
+// partial last tile is masked: the operand tiles then hold rows of the next head or TMA's zero
+// fill, whose scores are set to -inf).
 #include "tcgen05.cuh"
 
 #include <cmath>
@@ -45,28 +47,39 @@ namespace i8tk {
 namespace {
 
 constexpr int kQT = 128;                 // query rows per CTA
-constexpr int kKT = 128;                 // KV positions per tile
 constexpr int kSoftmaxWarps = 8;         // two per TMEM lane quarter: each thread owns half of a score row
 constexpr int kPrefillThreads = (2 + kSoftmaxWarps) * 32;   // TMA, MMA, 8 softmax warps
 constexpr int kRing = 3;                 // stages of the K ring and of the V16 ring
 constexpr float kLazyStep = 8.0f;        // log2 units the true max may run ahead of the reference max
 
-template <int D>
+// D: head_dim; KT: KV positions per tile (128, or 64 at head_dim 256, where a 128-position tile
+// would need 128 + 128 score columns, 128 for P and 256 for the output: more than the 512
+// columns of tensor memory, and K + V16 stages of 96 KB each).
+template <int D, int KT>
 struct PrefillCfg {
-    static constexpr int TILE_BYTES = kKT * D;             // one int8 tile (Q, K or raw V)
-    static constexpr int V16_BYTES = kKT * D * 2;          // fp16 V tile
-    static constexpr int SLAB_BYTES = kKT * 128;           // 128 rows of 128 bytes
+    static constexpr int HK = KT / 2;                      // KV positions of a tile per softmax thread
+    static constexpr int ROW_BYTES = D < 128 ? D : 128;    // bytes of a Q/K row per swizzled slab
+    static constexpr int QK_SLABS = D / ROW_BYTES;         // 128-byte slabs of a Q or K row (2 at head_dim 256)
+    static constexpr int Q_SLAB = kQT * ROW_BYTES;
+    static constexpr int K_SLAB = KT * ROW_BYTES;
+    static constexpr int Q_BYTES = kQT * D;                // int8 query tile
+    static constexpr int K_BYTES = KT * D;                 // int8 key tile
+    static constexpr int V16_BYTES = KT * D * 2;           // fp16 V tile
+    static constexpr int V_SLAB = KT * 128;                // KT rows of 128 bytes (64 fp16 columns)
     static constexpr int OFF_Q = 0;
-    static constexpr int OFF_K = OFF_Q + TILE_BYTES;
-    static constexpr int OFF_V16 = OFF_K + kRing * TILE_BYTES;
-    static constexpr int OFF_SCALES = OFF_V16 + kRing * V16_BYTES; // 8 warps x 2 tiles x sK[64] fp32
-    static constexpr int OFF_XCH = OFF_SCALES + kSoftmaxWarps * 2 * 64 * 4;    // [2][2 halves][128 rows] fp32
+    static constexpr int OFF_K = OFF_Q + Q_BYTES;
+    static constexpr int OFF_V16 = OFF_K + kRing * K_BYTES;
+    static constexpr int OFF_SCALES = OFF_V16 + kRing * V16_BYTES; // 8 warps x 2 tiles x sK[HK] fp32
+    static constexpr int OFF_XCH = OFF_SCALES + kSoftmaxWarps * 2 * HK * 4;    // [2][2 halves][128 rows] fp32
     static constexpr int OFF_BARS = OFF_XCH + 2 * 2 * kQT * 4;
     static constexpr int NUM_BARS = 24;
     static constexpr int SMEM_BYTES = 1024 + OFF_BARS + NUM_BARS * 8 + 16;
-    static constexpr int TMEM_COLS = 512;                  // S0 | S1 | O (D columns) | P0 | P1
-    static constexpr int TM_S0 = 0, TM_S1 = 128, TM_O = 256;
-    static constexpr int TM_P = 384;                       // two fp16 P tiles, 64 columns each (two values per column)
+    static constexpr int TMEM_COLS = 512;                  // S0 | S1 | P0 | P1 | O
+    static constexpr int TM_S0 = 0, TM_S1 = KT;            // two score tiles of KT int32 columns
+    static constexpr int TM_P = 2 * KT;                    // two fp16 P tiles of KT / 2 columns (two values per column)
+    static constexpr int TM_O = (D == 256) ? 256 : 3 * KT; // fp32 output, D columns
+    static_assert(TM_P + KT <= TM_O && TM_O + D <= TMEM_COLS, "tensor-memory layout");
+    static_assert(SMEM_BYTES <= 232448, "shared memory of an SM");
 };
 
 enum Bar : int {
@@ -113,14 +126,16 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int D>
+template <int D, int KT>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const float* __restrict__ sQ,
                          const float* __restrict__ sK,
                          __half* __restrict__ out, int S, float score_scale_log2,
                          uint32_t* __restrict__ status) {
-    using Cfg = PrefillCfg<D>;
+    using Cfg = PrefillCfg<D, KT>;
+    constexpr int kKT = KT;
+    constexpr int HK = Cfg::HK;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw_s = smem_u32(smem_raw);
     const uint32_t base_s = (raw_s + 1023u) & ~1023u;       // swizzle patterns are functions of address bits
@@ -169,17 +184,21 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         // V16 tiles by P.V; one loop waiting for both would make Q.K^T of tile j wait for P.V of
         // tile j-2, which is issued after it.
         if (lane == 0) {
-            mbar_expect_tx(bar(B_QFULL), Cfg::TILE_BYTES);
-            tma_load_2d(base_s + Cfg::OFF_Q, &tmQ, 0, row_base + q0, bar(B_QFULL));
+            mbar_expect_tx(bar(B_QFULL), Cfg::Q_BYTES);
+#pragma unroll
+            for (int sl = 0; sl < Cfg::QK_SLABS; ++sl)
+                tma_load_2d(base_s + Cfg::OFF_Q + sl * Cfg::Q_SLAB, &tmQ, sl * 128, row_base + q0, bar(B_QFULL));
             for (int j = 0; j < nt; ++j) {
                 const int st = j % kRing;
                 if (!mbar_wait_spin_bounded(bar(B_KEMPTY + st), ((j / kRing) & 1) ^ 1)) {
                     note_timeout(status);
                     break;
                 }
-                mbar_expect_tx(bar(B_KFULL + st), Cfg::TILE_BYTES);
-                tma_load_2d(base_s + Cfg::OFF_K + st * Cfg::TILE_BYTES, &tmK, 0, row_base + j * kKT,
-                            bar(B_KFULL + st));
+                mbar_expect_tx(bar(B_KFULL + st), Cfg::K_BYTES);
+#pragma unroll
+                for (int sl = 0; sl < Cfg::QK_SLABS; ++sl)
+                    tma_load_2d(base_s + Cfg::OFF_K + st * Cfg::K_BYTES + sl * Cfg::K_SLAB, &tmK, sl * 128,
+                                row_base + j * kKT, bar(B_KFULL + st));
             }
         } else if (lane == 1) {
             for (int j = 0; j < nt; ++j) {
@@ -188,11 +207,11 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                     note_timeout(status);
                     break;
                 }
-                // fp16 V: one box of 128 rows x 64 columns (128 bytes) per slab of the MN-major operand
+                // fp16 V: one box of KT rows x 64 columns (128 bytes) per slab of the MN-major operand
                 mbar_expect_tx(bar(B_V16FULL + st), Cfg::V16_BYTES);
 #pragma unroll
                 for (int sl = 0; sl < D / 64; ++sl)
-                    tma_load_2d(base_s + Cfg::OFF_V16 + st * Cfg::V16_BYTES + sl * Cfg::SLAB_BYTES, &tmV, sl * 128,
+                    tma_load_2d(base_s + Cfg::OFF_V16 + st * Cfg::V16_BYTES + sl * Cfg::V_SLAB, &tmV, sl * 128,
                                 row_base + j * kKT, bar(B_V16FULL + st));
             }
         }
@@ -209,11 +228,11 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 if (!mbar_wait_spin_bounded(bar(B_V16FULL + vs), (t / kRing) & 1)) return false;
                 tc_fence_after();
                 const uint32_t v16 = base_s + Cfg::OFF_V16 + vs * Cfg::V16_BYTES;
-                const uint64_t db0 = smem_desc_sw128_mn(v16, Cfg::SLAB_BYTES);
+                const uint64_t db0 = smem_desc_sw128_mn(v16, Cfg::V_SLAB);
 #pragma unroll
                 for (int i = 0; i < kKT / 16; ++i) {
                     // A: P in tensor memory, 8 columns (16 KV positions as fp16 pairs) per step
-                    const uint32_t ta = tmem_base + Cfg::TM_P + (t & 1) * 64 + i * 8;
+                    const uint32_t ta = tmem_base + Cfg::TM_P + (t & 1) * (kKT / 2) + i * 8;
                     // B: MN-major fp16, 16 rows of 128 bytes per step
                     const uint64_t db = db0 + (uint64_t)(128 * i);
                     mma_f16_ta(tmem_base + Cfg::TM_O, ta, db, idesc_pv, (t | i) != 0);
@@ -234,12 +253,18 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t ks = base_s + Cfg::OFF_K + kst * Cfg::TILE_BYTES;
-                    const uint64_t da = (D == 128) ? smem_desc_sw128(base_s + Cfg::OFF_Q) : smem_desc_sw64(base_s + Cfg::OFF_Q);
-                    const uint64_t db = (D == 128) ? smem_desc_sw128(ks) : smem_desc_sw64(ks);
+                    const uint32_t ks = base_s + Cfg::OFF_K + kst * Cfg::K_BYTES;
+                    // 32 bytes of a row per instruction: +2 (16-byte units) inside a swizzled slab,
+                    // the next slab after four of them (head_dim 256)
 #pragma unroll
-                    for (int k = 0; k < D / 32; ++k)
-                        mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * k, db + 2 * k, idesc_qk, k != 0);
+                    for (int k = 0; k < D / 32; ++k) {
+                        const uint32_t qa = base_s + Cfg::OFF_Q + (k / 4) * Cfg::Q_SLAB;
+                        const uint32_t ka = ks + (k / 4) * Cfg::K_SLAB;
+                        const uint64_t da = (D >= 128) ? smem_desc_sw128(qa) : smem_desc_sw64(qa);
+                        const uint64_t db = (D >= 128) ? smem_desc_sw128(ka) : smem_desc_sw64(ka);
+                        mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * (k % 4), db + 2 * (k % 4), idesc_qk,
+                               k != 0);
+                    }
                     tc_commit(bar(B_KEMPTY + kst));
                     tc_commit(bar(B_SFULL + st));
                 }
@@ -253,7 +278,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         const int q = warp & 3;                          // TMEM lane quarter of this warp
         const int half = sw >> 2;                        // columns half*64 .. +63 of every score tile
         const int r = q * 32 + lane;                     // row inside the tile
-        float* wsc = reinterpret_cast<float*>(base + Cfg::OFF_SCALES) + sw * 128;   // [tile & 1][sK[64]] of these columns
+        float* wsc = reinterpret_cast<float*>(base + Cfg::OFF_SCALES) + sw * (2 * HK);   // [tile & 1][sK[HK]] of these columns
         float* xch = reinterpret_cast<float*>(base + Cfg::OFF_XCH);                 // [2][half][row]
         // query rows past the end of a ragged sequence are computed on clamped operands and never stored
         const float qscale = sQ[min((long long)row_base + q0 + r, total_rows - 1)] * score_scale_log2;     // > 0
@@ -267,18 +292,18 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         f32x2 l2 = 0ull;
         bool ok = true;
         // this warp's per-position scales, fetched ahead of the tile that uses them
-        float pk0, pk1;
+        float pk0, pk1 = 0.f;
         auto prefetch = [&](int j) {
             // positions past the end of the arrays (ragged last tile of the last head) read the last element
-            const long long o0 = (long long)row_base + j * kKT + half * 64 + lane;
+            const long long o0 = (long long)row_base + j * kKT + half * HK + lane;
             const size_t oa = (size_t)min(o0, total_rows - 1), ob = (size_t)min(o0 + 32, total_rows - 1);
             asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk0) : "l"(sK + oa));
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk1) : "l"(sK + ob));
+            if constexpr (HK > 32) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(pk1) : "l"(sK + ob));
         };
         auto commit_scales = [&](int j) {                // prefetched registers -> this warp's block for tile j
-            float* w = wsc + (j & 1) * 64;
+            float* w = wsc + (j & 1) * HK;
             w[lane] = pk0;
-            w[32 + lane] = pk1;
+            if constexpr (HK > 32) w[32 + lane] = pk1;
             __syncwarp();
         };
         // y = (q.k) * sK for 8 columns of a score block held in registers, and their maximum
@@ -302,9 +327,9 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         auto mask_tail = [&](f32x2* yy, float& mx) {
             mx = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
+            for (int e = 0; e < HK / 2; ++e) {
                 float2 v = unpack2(yy[e]);
-                const int col = half * 64 + 2 * e;
+                const int col = half * HK + 2 * e;
                 if (col >= tail_valid) v.x = -INFINITY;
                 if (col + 1 >= tail_valid) v.y = -INFINITY;
                 yy[e] = pack2(v.x, v.y);
@@ -323,7 +348,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         };
 
         // ---- prologue: scores of tile 0 into registers ----
-        f32x2 y[32];
+        f32x2 y[HK / 2];
         float mx = -INFINITY;
         prefetch(0);
         commit_scales(0);
@@ -334,12 +359,12 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             if (ok) {
                 tc_fence_after();
                 uint32_t sr[2][16];
-                const uint32_t s_addr = lane_addr + Cfg::TM_S0 + half * 64;
+                const uint32_t s_addr = lane_addr + Cfg::TM_S0 + half * HK;
                 tmem_ld16(s_addr, sr[0]);
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
+                for (int cc = 0; cc < HK / 16; ++cc) {
                     tmem_ld_wait(sr[cc & 1]);
-                    if (cc < 3) tmem_ld16(s_addr + (cc + 1) * 16, sr[(cc + 1) & 1]);
+                    if (cc < HK / 16 - 1) tmem_ld16(s_addr + (cc + 1) * 16, sr[(cc + 1) & 1]);
                     convert8(&sr[cc & 1][0], wsc + cc * 16, &y[cc * 8], mx);
                     convert8(&sr[cc & 1][8], wsc + cc * 16 + 8, &y[cc * 8 + 4], mx);
                 }
@@ -392,7 +417,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             // ---- exponentials of this tile (special-function unit) interleaved, 8 columns at a time,
             // with the conversion of the NEXT tile's scores (integer and FMA pipes), which take over
             // the registers the exponentials have just released ----
-            const uint32_t prow = lane_addr + Cfg::TM_P + st * 64 + half * 32;   // this thread's 32 columns of P
+            const uint32_t prow = lane_addr + Cfg::TM_P + st * (kKT / 2) + half * (HK / 2);   // this thread's HK / 2 columns of P
             const f32x2 nm2 = pack2(-m_ref, -m_ref);
             mx = -INFINITY;
             if (has_next) {
@@ -401,14 +426,14 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 const bool got = mbar_wait_spin_bounded(bar(B_SFULL + (st ^ 1)), ((j + 1) >> 1) & 1);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
                 tc_fence_after();
-                const float* ksc = wsc + (st ^ 1) * 64;
-                const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S0 : Cfg::TM_S1) + half * 64;
+                const float* ksc = wsc + (st ^ 1) * HK;
+                const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S0 : Cfg::TM_S1) + half * HK;
                 uint32_t sr[2][16];
                 tmem_ld16(s_addr, sr[0]);
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
+                for (int cc = 0; cc < HK / 16; ++cc) {
                     tmem_ld_wait(sr[cc & 1]);
-                    if (cc < 3) tmem_ld16(s_addr + (cc + 1) * 16, sr[(cc + 1) & 1]);
+                    if (cc < HK / 16 - 1) tmem_ld16(s_addr + (cc + 1) * 16, sr[(cc + 1) & 1]);
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int c = cc * 2 + h;        // 16-byte chunk of P / 8 columns
@@ -422,7 +447,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 if (lane == 0) mbar_arrive(bar(B_SEMPTY + (st ^ 1)));
             } else {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) exp8(&y[c * 4], nm2, prow + c * 4);
+                for (int c = 0; c < HK / 8; ++c) exp8(&y[c * 4], nm2, prow + c * 4);
             }
             tmem_st_wait();                              // P is in tensor memory before the MMA thread is told
             tc_fence_before();
@@ -473,16 +498,16 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     }
 }
 
-template <int D>
+template <int D, int KT>
 int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, const float* sQ,
                    const float* sK, const float* sV, int BH, int S, uint32_t* status, __half* V16,
                    cudaStream_t st) {
-    using Cfg = PrefillCfg<D>;
+    using Cfg = PrefillCfg<D, KT>;
     static bool attr_done[64] = {false};
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        I8TK_CUDA(cudaFuncSetAttribute(prefill_attention_kernel<D, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::SMEM_BYTES));
         attr_done[dev] = true;
     }
@@ -493,19 +518,20 @@ int launch_prefill(const int8_t* Q, const int8_t* K, const int8_t* V, __half* ou
     if (blocks > 148ll * 16) blocks = 148ll * 16;
     I8TK_CUDA(launch_after(dequant_v_kernel, dim3((unsigned)blocks), dim3(256), 0, st, V, sV, V16, vecs, D / 16, status));
 
-    const CUtensorMapSwizzle sw = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    // Q and K as byte matrices [rows][D]: boxes of one swizzled slab (a whole row up to 128 bytes)
+    const CUtensorMapSwizzle sw = (D >= 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     CUtensorMap tmQ, tmK, tmV;
-    int rc = encode_map_2d_u8(&tmQ, Q, rows, D, kKT, D, sw);
+    int rc = encode_map_2d_u8(&tmQ, Q, rows, D, kQT, Cfg::ROW_BYTES, sw);
     I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
-    rc = encode_map_2d_u8(&tmK, K, rows, D, kKT, D, sw);
+    rc = encode_map_2d_u8(&tmK, K, rows, D, KT, Cfg::ROW_BYTES, sw);
     I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
-    // fp16 V as a byte matrix [rows][2*D]: boxes of 128 rows x 128 bytes (64 columns), 128-byte swizzle
-    rc = encode_map_2d_u8(&tmV, V16, rows, 2ull * D, kKT, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    // fp16 V as a byte matrix [rows][2*D]: boxes of KT rows x 128 bytes (64 columns), 128-byte swizzle
+    rc = encode_map_2d_u8(&tmV, V16, rows, 2ull * D, KT, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     I8TK_REQUIRE(rc == 0, I8TK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", rc);
     const float score_scale_log2 = 1.4426950408889634f / sqrtf((float)D);
     dim3 grid((S + kQT - 1) / kQT, BH);
-    I8TK_CUDA(launch_after(prefill_attention_kernel<D>, grid, dim3(kPrefillThreads), Cfg::SMEM_BYTES, st, tmQ, tmK, tmV,
-                           sQ, sK, out, S, score_scale_log2, status));
+    I8TK_CUDA(launch_after(prefill_attention_kernel<D, KT>, grid, dim3(kPrefillThreads), Cfg::SMEM_BYTES, st, tmQ, tmK,
+                           tmV, sQ, sK, out, S, score_scale_log2, status));
     return I8TK_OK;
 }
 
@@ -517,7 +543,7 @@ size_t attention_workspace(long long rows, int D) { return 256 + round_up((size_
 using namespace i8tk;
 
 extern "C" size_t i8tk_attention_workspace_bytes(int batch, int heads, int seq_len, int head_dim) {
-    if (batch <= 0 || heads <= 0 || seq_len <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
+    if (batch <= 0 || heads <= 0 || seq_len <= 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256)) return 0;
     return attention_workspace((long long)batch * heads * seq_len, head_dim);
 }
 
@@ -527,8 +553,8 @@ extern "C" int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const in
                                       size_t workspace_bytes, i8tk_stream_t stream) {
     I8TK_REQUIRE(Q && K && V && out_f16 && sQ && sK && sV, I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
     I8TK_REQUIRE(batch > 0 && heads > 0 && seq_len > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
-    I8TK_REQUIRE(head_dim == 64 || head_dim == 128, I8TK_ERR_UNSUPPORTED,
-                 "prefill attention supports head_dim 64 or 128 (got %d)", head_dim);
+    I8TK_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, I8TK_ERR_UNSUPPORTED,
+                 "prefill attention supports head_dim 64, 128 or 256 (got %d)", head_dim);
     I8TK_REQUIRE((long long)batch * heads <= 65535, I8TK_ERR_UNSUPPORTED, "batch*heads must be <= 65535");
     I8TK_REQUIRE((long long)batch * heads * seq_len < (1ll << 31), I8TK_ERR_UNSUPPORTED, "too many rows");
     I8TK_REQUIRE(aligned_to(Q, 16) && aligned_to(K, 16) && aligned_to(V, 16) && aligned_to(out_f16, 16),
@@ -542,6 +568,8 @@ extern "C" int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const in
     __half* V16 = reinterpret_cast<__half*>(static_cast<unsigned char*>(workspace) + 256);
     const int BH = batch * heads;
     if (head_dim == 64)
-        return launch_prefill<64>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
-    return launch_prefill<128>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
+        return launch_prefill<64, 128>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
+    if (head_dim == 128)
+        return launch_prefill<128, 128>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
+    return launch_prefill<256, 64>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
 }

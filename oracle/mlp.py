@@ -131,3 +131,31 @@ def kernel_mlp(x_i8, W1_i8, W2_i8, sx, sw1, sw2, b1=None, per_token_out=True):
         so = np.float32(so_rows[0])
     return {"hidden_f16": h16, "hidden_i8": hi, "hidden_scale": sh,
             "out_f16": o16, "out_i8": oi, "out_scale": so}
+
+
+def static_mlp(x_i8, W1_i8, W2_i8, sx, sw1, sw2):
+    """The reference's static-scale pipeline, the one it runs on shapes off its 128-tiles.
+
+    Follows ``kernels/int8_mlp.cu:830-844`` (``compute_static_scales_kernel``: hidden scale
+    ``sx*sw1*d_model``, output scale ``hidden_scale*sw2*d_ff``, and their reciprocals),
+    ``:905-909`` / ``:946-949`` (epilogue ``v = acc * (sa*sb)``, GELU on GEMM1, then
+    ``f32_to_i8(v, inv_scale)`` = ``rne(clamp(v * inv))``, ``kernels/int8_common.cuh:17-19``)
+    and ``:1194-1225`` (the two launches).  Per-tensor scalar scales only.  Accumulation is
+    exact here; the reference's scalar kernel accumulates in fp32, which is exact too while
+    ``K * 127^2 < 2^24``.
+
+    Returns dict with ``hidden_i8``, ``out_i8``, ``hidden_scale``, ``out_scale`` (fp32 scalars).
+    """
+    d_model, d_ff = W1_i8.shape
+    sx, sw1, sw2 = np.float32(sx), np.float32(sw1), np.float32(sw2)
+    sh = np.float32(np.float32(sx * sw1) * np.float32(d_model))
+    so = np.float32(np.float32(sh * sw2) * np.float32(d_ff))
+    inv_h = np.float32(np.float32(1.0) / sh)
+    inv_o = np.float32(np.float32(1.0) / so)
+    acc1 = _igemm(x_i8, W1_i8).astype(np.float32)
+    v = gelu_tanh((acc1 * np.float32(sx * sw1)).astype(np.float32))
+    hi = np.rint(np.clip((v * inv_h).astype(np.float32), -128.0, 127.0)).astype(np.int8)
+    acc2 = _igemm(hi, W2_i8).astype(np.float32)
+    o = (acc2 * np.float32(sh * sw2)).astype(np.float32)
+    oi = np.rint(np.clip((o * inv_o).astype(np.float32), -128.0, 127.0)).astype(np.int8)
+    return {"hidden_i8": hi, "out_i8": oi, "hidden_scale": sh, "out_scale": so}

@@ -185,6 +185,7 @@ int main(int argc, char** argv) {
     fails += decode_case(6, 1024, 128);
     fails += prefill_case(1, 2, 200, 64);
     fails += prefill_case(1, 2, 256, 128);
+    fails += prefill_case(1, 1, 200, 256);
     fails += mlp_cases(2, 128, 256, 512);
     fails += quant_case(5000);
     // a head_dim the kernels do not take: nothing is launched, the status says so

@@ -42,7 +42,10 @@ def _run(args):
                                      (1, 2, 640, 64), (1, 1, 896, 128),
                                      # ragged lengths (the reference's scalar-fallback shapes): partial last tile
                                      (1, 1, 1, 64), (2, 2, 63, 128), (1, 3, 129, 64), (2, 2, 200, 128),
-                                     (1, 2, 1000, 64), (1, 1, 2049, 128)])
+                                     (1, 2, 1000, 64), (1, 1, 2049, 128),
+                                     # head_dim 256 (kernels/int8_attention.cu:1012, tests/test_int8.py:82-85): 64-position tiles
+                                     (1, 1, 128, 256), (2, 2, 256, 256), (1, 3, 512, 256), (1, 2, 1024, 256),
+                                     (1, 1, 1, 256), (2, 2, 63, 256), (1, 2, 200, 256), (1, 1, 1090, 256)])
 def test_vs_oracle(B, H, S, D):
     args = _case(B, H, S, D, seed=S + D)
     out = _run(args)
@@ -77,8 +80,8 @@ def test_unsupported_shapes_raise():
     e = ext()
     mk = lambda S, D: torch.zeros(1, 1, S, D, dtype=torch.int8, device="cuda")
     sc = lambda S: torch.ones(S, device="cuda")
-    with pytest.raises(RuntimeError, match="head_dim 64 or 128"):
-        e.int8_attention_forward(mk(128, 256), mk(128, 256), mk(128, 256), sc(128), sc(128), sc(128))
+    with pytest.raises(RuntimeError, match="head_dim 64, 128 or 256"):
+        e.int8_attention_forward(mk(128, 96), mk(128, 96), mk(128, 96), sc(128), sc(128), sc(128))
     with pytest.raises(RuntimeError, match="shape mismatch"):
         e.int8_attention_forward(mk(128, 64), mk(256, 64), mk(128, 64), sc(128), sc(128), sc(128))
 
@@ -88,7 +91,7 @@ def test_matches_reference_kernel_when_built():
         pytest.skip("reference kernels not built (oracle/build_ref.py)")
     ref = ctypes.CDLL(REF_LIB)
     ref.ref_attention_forward.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 4
-    for (B, H, S, D) in [(2, 4, 512, 64), (2, 4, 512, 128)]:
+    for (B, H, S, D) in [(2, 4, 512, 64), (2, 4, 512, 128), (1, 4, 512, 256)]:
         args = _case(B, H, S, D, seed=11)
         t = [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in args]
         ours = ext().int8_attention_forward(*t)
