@@ -154,6 +154,27 @@ torch::Tensor int8_decode_attention_forward_torch(torch::Tensor Q, torch::Tensor
     return out;
 }
 
+// Decode attention whose result leaves as INT8 for the output projection: (int8 [B, H*D], fp32 [B]).
+std::tuple<torch::Tensor, torch::Tensor> int8_decode_attention_forward_quantized_torch(
+    torch::Tensor Q, torch::Tensor K, torch::Tensor V, torch::Tensor scale_Q, torch::Tensor scale_K,
+    torch::Tensor scale_V) {
+    DecodeArgs a = check_decode(Q, K, V, scale_Q, scale_K, scale_V);
+    TORCH_CHECK(Q.size(1) <= 32, "per-token output quantisation takes at most 32 heads");
+    c10::cuda::CUDAGuard guard(Q.device());
+    auto out = torch::empty({Q.size(0), Q.size(1) * Q.size(2)},
+                            torch::TensorOptions().dtype(torch::kInt8).device(Q.device()));
+    auto sc = torch::empty({Q.size(0)}, torch::TensorOptions().dtype(torch::kFloat32).device(Q.device()));
+    const size_t wbytes = i8tk_decode_workspace_bytes(a.BH, a.S, a.D);
+    auto ws = make_workspace(wbytes, Q.device());
+    check_status(i8tk_decode_attention_forward_q8(
+                     Q.data_ptr<int8_t>(), K.data_ptr<int8_t>(), V.data_ptr<int8_t>(), out.data_ptr<int8_t>(),
+                     sc.data_ptr<float>(), nullptr, a.sQ.data_ptr<float>(), a.sK.data_ptr<float>(),
+                     a.sV.data_ptr<float>(), static_cast<int>(Q.size(0)), static_cast<int>(Q.size(1)), a.S, a.D,
+                     ws.data_ptr(), static_cast<size_t>(ws.numel()), current_stream()),
+                 "int8_decode_attention_forward_quantized");
+    return {out, sc};
+}
+
 // Paged INT8 KV cache, one length per request.  Pools int8 [num_pages, H, page, D] and fp32
 // [num_pages, H, page]; page_table int32 [B, max_pages]; seq_lens int32 [B]; max_seq_len is the
 // caller's host-side bound on seq_lens.
@@ -403,6 +424,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "INT8 attention with per-token quantization (CUDA) — returns FP16");
     m.def("int8_decode_attention_forward", &int8_decode_attention_forward_torch,
           "INT8 flash-decoding attention (seq_q==1, INT8 KV cache) — returns FP16");
+    m.def("int8_decode_attention_forward_quantized", &int8_decode_attention_forward_quantized_torch,
+          "INT8 flash-decoding attention whose output is quantised per token for the next INT8 GEMM — "
+          "returns (int8 [B, H*D], fp32 scales [B])");
     m.def("int8_decode_attention_paged", &int8_decode_attention_paged_torch,
           "INT8 flash-decoding attention over a paged INT8 KV cache with per-request lengths — returns FP16");
     m.def("int8_decode_attention_partial", &int8_decode_attention_partial_torch,

@@ -134,3 +134,45 @@ def test_dequantize_per_token_with_and_without_residual():
     assert torch.equal(got, exact.half())               # one rounding of the exact sum (fma in fp32 is exact enough here)
     with pytest.raises(RuntimeError):
         e.dequantize_per_token(q[..., :8].contiguous(), s)
+
+
+@pytest.mark.parametrize("B,H,D,S", [(3, 12, 64, 700), (128, 16, 64, 1024), (5, 32, 128, 300), (2, 1, 128, 64),
+                                     (4, 8, 128, 4096)])
+def test_decode_output_quantised_per_token_is_bit_exact(B, H, D, S):
+    """int8_decode_attention_forward_quantized == quantize_per_token of the fp16 forward viewed as
+    [B, H*D]: same codes, same scale bits -- the merge kernel runs the quantiser's arithmetic on the
+    fp16-rounded values it would have stored."""
+    e = ext()
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + S)
+    Qi, sQ = e.quantize_per_token(torch.randn(B, H, D, device="cuda", dtype=torch.float16, generator=g))
+    Ki, sK = e.quantize_per_token(torch.randn(B, H, S, D, device="cuda", generator=g))
+    Vi, sV = e.quantize_per_token(torch.randn(B, H, S, D, device="cuda", generator=g) * 3.0)
+    out = e.int8_decode_attention_forward(Qi, Ki, Vi, sQ, sK, sV)
+    q_ref, s_ref = e.quantize_per_token(out.reshape(B, H * D))
+    q, s = e.int8_decode_attention_forward_quantized(Qi, Ki, Vi, sQ, sK, sV)
+    assert q.shape == (B, H * D) and q.dtype == torch.int8 and s.shape == (B,)
+    assert torch.equal(q, q_ref)
+    assert torch.equal(s.view(torch.int32), s_ref.view(torch.int32))
+    # and against the CPU oracle's quantiser on the same fp16 values
+    qo, so = quant.quantize_per_token(out.reshape(B, H * D).cpu().numpy())
+    assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(s.cpu().numpy().view(np.uint32), so.view(np.uint32))
+
+
+@pytest.mark.parametrize("T,K,N,bias", [(128, 128, 128, False), (7, 256, 384, True), (300, 1024, 1024, True),
+                                        (4096, 768, 768, False)])
+def test_int8_linear_matches_the_dequantised_product(T, K, N, bias):
+    e = ext()
+    g = torch.Generator(device="cuda").manual_seed(T + K + N)
+    xi, sx = e.quantize_per_token(torch.randn(T, K, device="cuda", dtype=torch.float16, generator=g))
+    W = torch.randn(K, N, device="cuda", generator=g) * 0.03
+    sw = W.abs().amax(dim=0).clamp_min(1e-8) / 127.0
+    wi = torch.clamp(torch.round(W / sw), -128, 127).to(torch.int8).contiguous()
+    b = torch.randn(N, device="cuda", generator=g) * 0.1 if bias else None
+    out = e.int8_linear(xi, sx, wi, sw, b)
+    assert out.shape == (T, N) and out.dtype == torch.float16
+    acc = (xi.double() @ wi.double())                                    # exact integer products
+    ref = acc * sx.double()[:, None] * sw.double()[None, :] + (b.double() if bias else 0.0)
+    err = (out.double() - ref).abs().max().item()
+    assert err <= 2e-3 * max(1.0, ref.abs().max().item()), err           # fp16 output rounding
+    with pytest.raises(RuntimeError, match="multiples of 128"):
+        e.int8_linear(xi[:, :64].contiguous(), sx, wi[:64].contiguous(), sw)
