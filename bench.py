@@ -492,10 +492,13 @@ def mlp_headline(torch, ext, cabi):
         osc = torch.empty(M, device="cuda")
         st = torch.cuda.current_stream().cuda_stream
 
+        kept = [0]        # the workspace is this loop's alone: from the second call on the library is told so
+
         def fwd():
             cabi.check(lib.i8tk_mlp_forward(xi.data_ptr(), W1T.data_ptr(), W2T.data_ptr(), o.data_ptr(),
                                             sxf.data_ptr(), s1.data_ptr(), s2.data_ptr(), b1.data_ptr(),
-                                            osc.data_ptr(), None, M, dm, dff, flags, ws.data_ptr(), wb, st))
+                                            osc.data_ptr(), None, M, dm, dff, flags | kept[0], ws.data_ptr(), wb, st))
+            kept[0] = cabi.MLP_WORKSPACE_KEPT
 
         t_med, t_min, t_max = median_of_windows(torch, fwd, 50, repeats=5, min_seconds=0.05)
         cabi.check(lib.i8tk_check_status_word(ws.data_ptr(), st), "fused MLP")
@@ -789,10 +792,13 @@ def mlp_sweep(torch, ext, cabi):
             osc = torch.empty(M, device="cuda")
             st = torch.cuda.current_stream().cuda_stream
 
+            kept = [0]    # the workspace is this loop's alone: from the second call on the library is told so
+
             def prepacked():
                 cabi.check(lib.i8tk_mlp_forward(xi.data_ptr(), W1T.data_ptr(), W2T.data_ptr(), o.data_ptr(),
                                                 sxf.data_ptr(), s1.data_ptr(), s2.data_ptr(), b1.data_ptr(),
-                                                osc.data_ptr(), None, M, dm, dff, flags, ws.data_ptr(), wb, st))
+                                                osc.data_ptr(), None, M, dm, dff, flags | kept[0], ws.data_ptr(), wb, st))
+                kept[0] = cabi.MLP_WORKSPACE_KEPT
 
             steps = 50
             el = timed_settled(torch, prepacked, steps, 5)

@@ -341,6 +341,13 @@ int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const int8_t* V, vo
  * scale sx*sW1*d_model and output codes under that * sW2 * d_ff, which is written to
  * *out_tensor_scale (out_row_scales must be NULL).
  *
+ * Workspace reuse.  A forward starts with a small kernel that presets the row-maxima flag
+ * arrays in the workspace.  Both GEMMs also leave those arrays preset when they are done with
+ * them, so a caller that gives the SAME workspace to consecutive calls of the SAME T, d_model,
+ * d_ff and layout flags on one stream, and lets nothing else write to it in between, may pass
+ * I8TK_MLP_WORKSPACE_KEPT from the second call on: the preset kernel is then skipped (2-4 us
+ * per forward).  The first call on a workspace, or after a change of shape, must not pass it.
+ *
  * Rounding of the first epilogue.  By default v = fma(acc*sx, sW1, b1) and GELU uses the
  * hardware tanh approximation (relative error 2^-11, the size of the fp16 rounding that
  * follows): against the reference's source order this moves an int8 code of the hidden
@@ -355,7 +362,8 @@ enum i8tk_mlp_flags {
     I8TK_MLP_W_PER_CHANNEL = 2,
     I8TK_MLP_PREPACKED = 4,
     I8TK_MLP_REFERENCE_ROUNDING = 8,
-    I8TK_MLP_STATIC_SCALES = 16
+    I8TK_MLP_STATIC_SCALES = 16,
+    I8TK_MLP_WORKSPACE_KEPT = 32
 };
 size_t i8tk_mlp_workspace_bytes(int T, int d_model, int d_ff, int flags);
 int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out,

@@ -23,6 +23,7 @@ MLP_W_PER_CHANNEL = 2
 MLP_PREPACKED = 4
 MLP_REFERENCE_ROUNDING = 8
 MLP_STATIC_SCALES = 16
+MLP_WORKSPACE_KEPT = 32
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int

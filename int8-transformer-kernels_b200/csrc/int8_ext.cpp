@@ -73,6 +73,45 @@ torch::Tensor make_workspace(size_t bytes, const torch::Device& dev) {
     return slot;
 }
 
+// The fused MLP gets a scratch block of its own per (device, stream): nothing else writes to
+// it, so from the second forward of a shape on it the library can be told that the block is as
+// the previous forward left it (I8TK_MLP_WORKSPACE_KEPT: no preset kernel).  `tag` identifies
+// shape and layout; *kept says whether the previous forward on this block had the same tag.
+struct MlpWs {
+    torch::Tensor buf;
+    uint64_t tag = 0;
+};
+std::map<WsKey, MlpWs> g_mlp_ws_cache;
+
+torch::Tensor make_mlp_workspace(size_t bytes, const torch::Device& dev, uint64_t tag, bool* kept) {
+    const int64_t need = static_cast<int64_t>(bytes > 256 ? bytes : 256);
+    const auto opts = torch::TensorOptions().dtype(torch::kUInt8).device(dev);
+    *kept = false;
+    const auto cur = c10::cuda::getCurrentCUDAStream(dev.index());
+    if (c10::cuda::currentStreamCaptureStatusMayInitCtx() != c10::cuda::CaptureStatus::None)
+        return torch::empty({need}, opts);
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    MlpWs& slot = g_mlp_ws_cache[WsKey{static_cast<int>(dev.index()), cur.stream()}];
+    if (!slot.buf.defined() || slot.buf.numel() < need) {
+        auto grown = torch::empty({need + need / 4}, opts);
+        if (slot.buf.defined()) grown.narrow(0, 0, 256).copy_(slot.buf.narrow(0, 0, 256));
+        else grown.narrow(0, 0, 256).zero_();
+        slot.buf = grown;
+        slot.tag = 0;
+    }
+    *kept = slot.tag == tag && tag != 0;
+    slot.tag = tag;
+    return slot.buf;
+}
+
+// After a failed forward the block's state is unknown: the next call presets it again.
+void forget_mlp_workspace(const torch::Device& dev) {
+    const auto cur = c10::cuda::getCurrentCUDAStream(dev.index());
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    auto it = g_mlp_ws_cache.find(WsKey{static_cast<int>(dev.index()), cur.stream()});
+    if (it != g_mlp_ws_cache.end()) it->second.tag = 0;
+}
+
 // Synchronises every stream an op has run on, reads the status blocks back and raises if a
 // bounded device-side wait gave up since the last check (the outputs of such a call are not
 // valid).  Resets the counts.  Returns the number of blocks looked at.
@@ -81,6 +120,7 @@ int64_t check_status_torch() {
     {
         std::lock_guard<std::mutex> lock(g_ws_mutex);
         for (auto& kv : g_ws_cache) blocks.emplace_back(kv.first, kv.second);
+        for (auto& kv : g_mlp_ws_cache) blocks.emplace_back(kv.first, kv.second.buf);
     }
     int64_t failures = 0;
     for (auto& kv : blocks) {

@@ -90,6 +90,10 @@ struct EpiParams {
     // rne(clamp(v * static_inv[0])) to C8 instead of fp16 to C
     const float* static_inv;
     int clear_status;         // this launch is the first of its call: it clears the call's status word
+    float* zero_word;         // ... and zeroes this float (the tensor-wide maximum of the legacy output)
+    // row-maxima flags of the OTHER GEMM of the layer, set to all ones for that GEMM's next run
+    uint4* preset_ptr;
+    unsigned long long preset_words16;
 };
 
 // GELU, tanh form: 0.5 x (1 + tanh(y)), y = kC (x + kA x^3)
@@ -370,7 +374,22 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             pf_sa = ld_nc_now(ep.a_per_row ? ep.scale_a + min(pm0 + q * 32 + lane, M - 1) : ep.scale_a);
         };
         pdl_wait();     // row scales and the row-maxima flags come from the kernels before this one
-        if (ep.clear_status && blockIdx.x == 0 && ew == 0 && lane == 0) clear_call_status(status);
+        if (ew == 0) {
+            if (ep.clear_status && blockIdx.x == 0 && lane == 0) {
+                clear_call_status(status);
+                if (ep.zero_word) *ep.zero_word = 0.f;
+            }
+            // Each GEMM of the layer leaves the other one's flag array as it must be found: GEMM2
+            // runs when GEMM1 has finished with its flags and the next forward's GEMM1 cannot read
+            // them before GEMM2 is complete, and the other way round.  A caller that keeps the
+            // workspace to itself can therefore skip the preset kernel from the second call on.
+            if (ep.preset_ptr) {
+                const uint4 ones = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+                for (unsigned long long i = (unsigned long long)blockIdx.x * 32 + lane; i < ep.preset_words16;
+                     i += (unsigned long long)gridDim.x * 32)
+                    ep.preset_ptr[i] = ones;
+            }
+        }
         if ((int)blockIdx.x < num_tiles) prefetch(blockIdx.x);
 
         // Requantisation of a tile whose fp16 values sit in this warp's stash: wait for the
@@ -954,19 +973,25 @@ int mlp_core(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out, c
         I8TK_CUDA(launch_after(static_scales_kernel, dim3(1), dim3(32), 0, st, scale_x, scale_W1, scale_W2,
                                w.static_scales, out_tensor_scale, true_dm, true_dff, w.status));
         EpiParams e1{scale_x, scale_W1, nullptr, nullptr, nullptr, 0, 0, w.hid_i8, nullptr, nullptr, 1,
-                     w.static_scales + 1, 0};
+                     w.static_scales + 1, 0, nullptr, nullptr, 0};
         rc = exact ? launch_gemm<128, true, false, false, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st)
                    : launch_gemm<128, true, false, false, false>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
         if (rc != I8TK_OK) return rc;
         EpiParams e2{w.static_scales, scale_W2, nullptr, nullptr, nullptr, 0, 0, out, nullptr, nullptr, 1,
-                     w.static_scales + 3, 0};
+                     w.static_scales + 3, 0, nullptr, nullptr, 0};
         return launch_gemm<128, false, false, false, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
     }
 
     // presets: row-maxima flags all ones, the tensor-wide maximum zero, the call's status word
     // clear.  A kernel rather than a memset so that GEMM1 can be launched behind it
-    // programmatically and set itself up meanwhile.
-    {
+    // programmatically and set itself up meanwhile.  With I8TK_MLP_WORKSPACE_KEPT the previous
+    // forward on this workspace has left the flags preset (each GEMM resets the other's array)
+    // and GEMM1 clears the two words itself: no preset launch.
+    const bool kept = (flags & I8TK_MLP_WORKSPACE_KEPT) != 0;
+    // sizes of the two flag arrays as carve() lays them out
+    const size_t p1_words = (size_t)(reinterpret_cast<unsigned char*>(w.parts2) - reinterpret_cast<unsigned char*>(w.parts1)) / 16;
+    const size_t p2_words = w.ones_bytes / 16 - p1_words;
+    if (!kept) {
         const size_t words = w.ones_bytes / 16;
         int blocks = (int)((words + 255) / 256);
         if (blocks > 296) blocks = 296;
@@ -981,7 +1006,8 @@ int mlp_core(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out, c
     // memory, and are quantised one tile later, when that exchange has long finished.
     {
         EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, per_token, per_channel,
-                     w.hid_i8, w.hid_scale, w.parts1, 0, nullptr, 0};
+                     w.hid_i8, w.hid_scale, w.parts1, 0, nullptr, kept ? 1 : 0, w.tensor_absmax,
+                     reinterpret_cast<uint4*>(w.parts2), p2_words};
         if (exact)
             rc = launch_gemm_bn<true, true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
         else
@@ -992,12 +1018,12 @@ int mlp_core(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out, c
         // GEMM2: out = (hidden_i8 . W2) * sh * sW2, requantised per token the same way, but
         // at once: with K = d_ff the MMAs of the next tile cover the exchange
         EpiParams e2{w.hid_scale, scale_W2, nullptr, nullptr, nullptr, 1, per_channel,
-                     out, out_row_scales, w.parts2, 1, nullptr, 0};
+                     out, out_row_scales, w.parts2, 1, nullptr, 0, nullptr, reinterpret_cast<uint4*>(w.parts1), p1_words};
         return launch_gemm_bn<false, true, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
     }
     // legacy per-tensor output scale: fp16 out + global absmax, then one requant pass
     EpiParams e2{w.hid_scale, scale_W2, nullptr, w.out_f16, w.tensor_absmax, 1, per_channel,
-                 nullptr, nullptr, nullptr, 1, nullptr, 0};
+                 nullptr, nullptr, nullptr, 1, nullptr, 0, nullptr, reinterpret_cast<uint4*>(w.parts1), p1_words};
     rc = launch_gemm_bn<false, false, false>(w.hid_i8, W2, b_mn, e2, T, d_model, d_ff, w.status, st);
     if (rc != I8TK_OK) return rc;
     requant_tensor_kernel<<<requant_grid((long long)T * d_model / 16), 256, 0, st>>>(
@@ -1038,7 +1064,7 @@ extern "C" int i8tk_linear_i8_f16(const int8_t* x, const int8_t* W, const float*
                  "workspace: 256 bytes, 256-byte aligned (the status block)");
     const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
     EpiParams e{scale_x, scale_W, bias, static_cast<__half*>(out_f16), nullptr, (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0,
-                (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0, nullptr, nullptr, nullptr, 0, nullptr, 1};
+                (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0, nullptr, nullptr, nullptr, 0, nullptr, 1, nullptr, nullptr, 0};
     return launch_gemm_bn<false, false, false>(x, W, b_mn, e, T, N, K, static_cast<uint32_t*>(workspace),
                                                static_cast<cudaStream_t>(stream));
 }
@@ -1061,7 +1087,7 @@ extern "C" int i8tk_mlp_forward(const int8_t* x, const int8_t* W1, const int8_t*
     I8TK_REQUIRE(out_row_scales || out_tensor_scale, I8TK_ERR_INVALID_ARGUMENT,
                  "one of out_row_scales / out_tensor_scale must be given");
     I8TK_REQUIRE(T > 0 && d_model > 0 && d_ff > 0, I8TK_ERR_INVALID_ARGUMENT, "sizes must be positive");
-    I8TK_REQUIRE((flags & ~31) == 0, I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
+    I8TK_REQUIRE((flags & ~63) == 0, I8TK_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", flags);
     if (flags & I8TK_MLP_STATIC_SCALES) {
         I8TK_REQUIRE(!(flags & (I8TK_MLP_X_PER_TOKEN | I8TK_MLP_W_PER_CHANNEL)) && bias1 == nullptr &&
                          out_row_scales == nullptr && out_tensor_scale != nullptr,

@@ -357,3 +357,49 @@ def test_static_scale_mode(T, dm, dff):
         W1T, W2T = ext().transpose_int8_weights(w1_t, w2_t)
         out3, osc3 = ext().int8_mlp_forward_prepacked(x_t, W1T, W2T, float(sx), float(s1), float(s2), static_scales=True)
         assert torch.equal(out3, out) and osc3 == osc
+
+
+def test_workspace_kept_flag_gives_identical_results():
+    """I8TK_MLP_WORKSPACE_KEPT: from the second forward of a shape on a workspace nothing else touches, the
+    preset kernel may be skipped (both GEMMs leave the flag arrays preset).  Same bytes out, on a run of
+    calls, for the per-token and the legacy per-tensor output, and through the ops (which track it)."""
+    c = cabi()
+    lib = c.load()
+    e = ext()
+    torch.manual_seed(5)
+    for (T, dm, dff) in [(384, 256, 1024), (1000, 768, 3072)]:
+        xs = [e.quantize_per_token(torch.randn(1, T, dm, device="cuda", dtype=torch.float16))[0] for _ in range(3)]
+        sx = torch.rand(T, device="cuda") * 0.01 + 0.01
+        w1 = torch.randint(-127, 128, (dm, dff), dtype=torch.int8, device="cuda")
+        w2 = torch.randint(-127, 128, (dff, dm), dtype=torch.int8, device="cuda")
+        s1 = torch.rand(dff, device="cuda") * 1e-4 + 1e-4
+        s2 = torch.rand(dm, device="cuda") * 1e-4 + 1e-4
+        st = torch.cuda.current_stream().cuda_stream
+        for per_token_out in (True, False):
+            flags = c.MLP_X_PER_TOKEN | c.MLP_W_PER_CHANNEL
+            wb = lib.i8tk_mlp_workspace_bytes(T, dm, dff, flags)
+            fresh = lambda: torch.randint(0, 255, (wb,), dtype=torch.uint8, device="cuda")     # garbage on purpose
+            ws_kept = fresh()
+
+            def run(x, ws, fl):
+                o = torch.empty(1, T, dm, dtype=torch.int8, device="cuda")
+                rs = torch.empty(T, device="cuda")
+                ts = torch.empty(1, device="cuda")
+                c.check(lib.i8tk_mlp_forward(x.data_ptr(), w1.data_ptr(), w2.data_ptr(), o.data_ptr(), sx.data_ptr(),
+                                             s1.data_ptr(), s2.data_ptr(), None, rs.data_ptr() if per_token_out else None,
+                                             None if per_token_out else ts.data_ptr(), T, dm, dff, fl, ws.data_ptr(), wb, st))
+                return o, (rs if per_token_out else ts)
+
+            for i, x in enumerate(xs + xs):
+                want = run(x, fresh(), flags)
+                got = run(x, ws_kept, flags | (c.MLP_WORKSPACE_KEPT if i > 0 else 0))
+                assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]), (T, per_token_out, i)
+                assert lib.i8tk_check_status_word(ws_kept.data_ptr(), st) == c.OK
+        # the ops: a run of calls of one shape, another shape in between
+        b1 = torch.randn(dff, device="cuda") * 0.01
+        first = e.int8_mlp_forward_per_channel_bias(xs[0], w1, w2, sx, s1, s2, b1)
+        e.int8_mlp_forward_per_channel_bias(xs[1][:, :128].contiguous(), w1, w2, sx[:128].contiguous(), s1, s2, b1)
+        for _ in range(3):
+            again = e.int8_mlp_forward_per_channel_bias(xs[0], w1, w2, sx, s1, s2, b1)
+            assert torch.equal(again[0], first[0]) and torch.equal(again[1], first[1])
+    e.check_status()
