@@ -162,6 +162,8 @@ def run_reference_arm(args):
     if rank != 0:
         return
     import torch
+    # every host core: a launcher may have set OMP_NUM_THREADS=1 for its ranks (torchrun does)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     budget = min(20.0, max(2.0, 1.0 * args.steps))
     gbs, per_iter, threads, desc = cpu_reference_rate(seconds_budget=budget)
     line = {
@@ -295,11 +297,13 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback")
     torch.cuda.set_device(local_rank)
     distributed = world > 1
+    # stdout carries exactly one JSON line: whatever a library prints to file descriptor 1 from
+    # here on (NCCL's version and, when the caller sets NCCL_DEBUG=INFO, its transport lines) is
+    # sent to stderr instead; the line itself is written to the saved descriptor at the end
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if distributed:
-        # a level the caller set (e.g. INFO, to see which transports the communicator chose) is
-        # kept; NCCL's own lines go to stderr so that stdout stays the one JSON line
-        os.environ.setdefault("NCCL_DEBUG", "WARN")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     pkg = importlib.import_module("int8-transformer-kernels_b200")
@@ -440,7 +444,8 @@ def main():
         line["sweep"] = sweep(torch, ext, cabi, world, rank, barrier, dist if distributed else None)
 
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if distributed:
         dist.destroy_process_group()
 
