@@ -62,6 +62,8 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
         diff = (got.float() - want.float()).abs().max().item()
         assert not torch.isnan(got).any()
         assert diff <= 2e-3, diff
+    # the block's status record is reachable only through the library: no wait gave up
+    assert lib.i8tk_decode_static_check_status(torch.cuda.current_stream().cuda_stream) == cabi().OK
 
 
 def test_static_scratch_entry_refuses_shapes_beyond_its_block():
