@@ -160,9 +160,12 @@ class Int8Block:
         self.weights = BlockWeights.random(d_model, heads, d_ff, device=device, seed=seed)
         self.routes = {False: Fp16Route(self.weights), True: Int8Route(self.weights)}
 
-    def forward_prefill(self, x, use_int8):
+    def forward_prefill(self, x, use_int8, fp16_attention=False):
+        """``fp16_attention`` with ``use_int8``: the mixed route -- attention through torch's fp16
+        flash kernel, feed-forward on the INT8 MLP with its fused LayerNorm/quantise/dequantise."""
         route = self.routes[bool(use_int8)]
-        return route.feed_forward(route.attend_prefill(x))
+        attend = self.routes[False].attend_prefill if (use_int8 and fp16_attention) else route.attend_prefill
+        return route.feed_forward(attend(x))
 
     def forward_decode(self, x, cache, use_int8):
         route = self.routes[bool(use_int8)]

@@ -48,6 +48,7 @@ PROFILE_CASES = {
     "quantize_f32_64": (3145728, 64),      # rows, cols: 1.0 GB through the per-token quantiser
     "prefill_d64": (2, 8, 4096, 64),       # B, H, S, D: 512 CTAs of 128 query rows
     "prefill_d128": (2, 8, 4096, 128),
+    "prefill_d256": (2, 8, 2048, 256),     # 64-position KV tiles
     "paged_d64_p64": (8, 12, 64, 16384, 64),   # B, H, D, longest request, page: lengths 2048..16384, shuffled table
     "lnquant_f16_1024": (131072, 1024),    # rows, cols: 268 MB in, 134 MB of codes out
 }

@@ -26,6 +26,8 @@ def test_prefill_block_matches_fp16_block(B, H, Dh, dff, S):
     f16 = blk.forward_prefill(x, False)
     assert i8.shape == f16.shape and not torch.isnan(i8).any()
     assert _cos(i8, f16) > 0.999
+    mixed = blk.forward_prefill(x, True, fp16_attention=True)     # fp16 attention, INT8 feed-forward
+    assert _cos(mixed, f16) > 0.999
 
 
 @pytest.mark.parametrize("B,H,Dh,dff,Skv", [(128, 8, 64, 2048, 1024), (128, 4, 128, 1024, 777)])
