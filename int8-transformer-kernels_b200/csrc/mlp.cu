@@ -52,11 +52,14 @@ constexpr int kEpiWarps = 16;    // four per TMEM lane quarter, each takes a qua
 constexpr int kSlices = kEpiWarps / 4;
 constexpr int kGemmThreads = (kEpiWarp0 + kEpiWarps) * 32;
 
-// FUSED kernels keep a whole tile of fp16 values in shared memory (the stash of the fused
-// requantisation), paid for with one pipeline stage at the wider tiles.
-template <int BN, bool FUSED>
+// STASH kernels (fused requantisation deferred by a tile: GEMM1) keep a whole tile of fp16
+// values in shared memory, paid for with one pipeline stage at the wider tiles.  The kernel
+// that requantises at once (GEMM2) does it from registers and spends that memory on a deeper
+// operand ring: its main loop is bound by how many bytes are in flight, not by the tensor
+// pipe (two stages 161 k cycles, three 110 k at M=16384 1024->4096).
+template <int BN, bool FUSED, bool STASH>
 struct GemmCfg {
-    static constexpr int STAGES = (BN == 256) ? (FUSED ? 3 : 4) : (BN == 192 ? 4 : (FUSED ? 5 : 6));
+    static constexpr int STAGES = (BN == 256) ? (STASH ? 3 : 4) : (BN == 192 ? ((FUSED && !STASH) ? 5 : 4) : (STASH ? 5 : 6));
     static constexpr int HC = BN / kSlices;                  // columns per epilogue warp
     static constexpr int A_BYTES = BM * BK;
     static constexpr int B_BYTES = BN * BK;
@@ -64,8 +67,9 @@ struct GemmCfg {
     static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;   // two accumulator buffers, power of two
     static constexpr int AUX_BYTES = kEpiWarps * 2 * HC * 4;        // per epilogue warp: [scale|bias][HC] fp32
     static constexpr int CMB_BYTES = 2 * kEpiWarps * 32 * 4;        // [2][quarter][slice][32 rows] row maxima
-    // per epilogue warp: 32 rows x HC fp16 (FUSED), or 32 rows x 16 fp16 of store staging
-    static constexpr int CSTAGE_WARP_BYTES = FUSED ? 32 * HC * 2 : 32 * 32;
+    // per epilogue warp: 32 rows x HC fp16 (STASH), 32 rows x 16 fp16 of store staging for the
+    // fp16 output, nothing when the codes leave from registers
+    static constexpr int CSTAGE_WARP_BYTES = STASH ? 32 * HC * 2 : (FUSED ? 0 : 32 * 32);
     static constexpr int CSTAGE_BYTES = kEpiWarps * CSTAGE_WARP_BYTES;
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES + CMB_BYTES + BAR_BYTES + CSTAGE_BYTES;
@@ -234,7 +238,7 @@ template <int BN, bool GELU, bool FUSED, bool DEFER, bool EXACT = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                EpiParams ep, int M, int N, int K, int b_mn, uint32_t* __restrict__ status) {
-    using Cfg = GemmCfg<BN, FUSED>;
+    using Cfg = GemmCfg<BN, FUSED, FUSED && DEFER>;
     constexpr int STAGES = Cfg::STAGES;
 
     extern __shared__ unsigned char smem_raw[];
@@ -586,17 +590,43 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // has published, so its maxima are there at the first look
                     if (p_m0 >= 0) finalize(p_m0, p_n0, tiles_n <= kGatherAhead);
                 }
-#pragma unroll
-                for (int jc = 0; jc < HC / 8; ++jc)
-                    *reinterpret_cast<uint4*>(cst + lane * (HC * 2) + (stash_swz<HC>(lane, jc) << 4)) =
-                        make_uint4(hv[4 * jc], hv[4 * jc + 1], hv[4 * jc + 2], hv[4 * jc + 3]);
-                __syncwarp();
                 if constexpr (DEFER) {
+#pragma unroll
+                    for (int jc = 0; jc < HC / 8; ++jc)
+                        *reinterpret_cast<uint4*>(cst + lane * (HC * 2) + (stash_swz<HC>(lane, jc) << 4)) =
+                            make_uint4(hv[4 * jc], hv[4 * jc + 1], hv[4 * jc + 2], hv[4 * jc + 3]);
+                    __syncwarp();
                     p_m0 = m0;
                     p_n0 = n0;
                 } else {
-                    // at once: with a long K loop the MMAs of the next tile cover the wait
-                    finalize(m0, n0, false);
+                    // at once, straight from the registers that hold this lane's row: with a long K
+                    // loop the MMAs of the next tile cover the wait for the other tiles' maxima.
+                    // 16 codes = one 16-byte store per 16-column block of the lane's own row.
+                    bool ok = true;
+                    float amax = gather_row_max(ep.row_parts + (size_t)m0 * tiles_n + q * 32 + lane, tiles_n, &ok);
+                    amax = fmaxf(amax, 1e-8f);
+                    if (!ok) {
+                        note_timeout(status);                 // a sibling CTA never published
+                        amax = __int_as_float(0x7fc00000);    // NaN scale: the failure travels with the data
+                    }
+                    if (n0 == 0 && slice == 0 && m0 + q * 32 + lane < M) ep.row_scale[m0 + q * 32 + lane] = amax / 127.f;
+                    const float inv = 127.f / amax;
+                    const f32x2 inv2 = pack2(inv, inv);
+                    int8_t* c8row = ep.C8 + (size_t)(m0 + q * 32 + lane) * N + n0 + c0;
+                    const bool store = m0 + q * 32 + lane < M;
+                    auto codes = [&](auto clamp_tag) {
+                        constexpr bool kClamp = decltype(clamp_tag)::value;
+#pragma unroll
+                        for (int cc = 0; cc < NCH; ++cc) {
+                            const uint2 w0 = quant8_f16<kClamp>(make_uint4(hv[8 * cc], hv[8 * cc + 1], hv[8 * cc + 2], hv[8 * cc + 3]), inv2);
+                            const uint2 w1 = quant8_f16<kClamp>(make_uint4(hv[8 * cc + 4], hv[8 * cc + 5], hv[8 * cc + 6], hv[8 * cc + 7]), inv2);
+                            if (store) *reinterpret_cast<uint4*>(c8row + cc * 16) = make_uint4(w0.x, w0.y, w1.x, w1.y);
+                        }
+                    };
+                    // values above the fp16 range were stored as inf: only then can a product leave
+                    // [-128, 127], so ordinary rows skip the clamp
+                    if (__any_sync(0xffffffffu, !(amax <= 65504.f))) codes(std::true_type{});
+                    else codes(std::false_type{});
                 }
             }
         }
@@ -800,7 +830,7 @@ int pick_bn(int M, int N, bool b_mn, bool fused) {
 template <int BN, bool GELU, bool FUSED, bool DEFER, bool EXACT = false>
 int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                 uint32_t* status, cudaStream_t st) {
-    using Cfg = GemmCfg<BN, FUSED>;
+    using Cfg = GemmCfg<BN, FUSED, FUSED && DEFER>;
     static_assert(Cfg::SMEM_BYTES <= 232448, "tile configuration exceeds the shared memory of an SM");
     static bool attr_done[64] = {false};
     int dev = 0;
