@@ -57,12 +57,16 @@ constexpr int kGemmThreads = (kEpiWarp0 + kEpiWarps) * 32;
 // that requantises at once (GEMM2) does it from registers and spends that memory on a deeper
 // operand ring: its main loop is bound by how many bytes are in flight, not by the tensor
 // pipe (two stages 161 k cycles, three 110 k at M=16384 1024->4096).
-template <int BN, bool FUSED, bool STASH>
+// PAIR: two CTAs share a 256-row tile (cta_group::2); each stages its own 128 rows of A and
+// half of B's columns, so a stage is a third smaller and the ring a half deeper.
+template <int BN, bool FUSED, bool STASH, bool PAIR = false>
 struct GemmCfg {
-    static constexpr int STAGES = (BN == 256) ? (STASH ? 3 : 4) : (BN == 192 ? ((FUSED && !STASH) ? 5 : 4) : (STASH ? 5 : 6));
+    static_assert(!PAIR || BN == 256, "CTA pairs are built for the 256-wide tile");
+    static constexpr int STAGES = PAIR ? (STASH ? 4 : 6)
+        : (BN == 256) ? (STASH ? 3 : 4) : (BN == 192 ? ((FUSED && !STASH) ? 5 : 4) : (STASH ? 5 : 6));
     static constexpr int HC = BN / kSlices;                  // columns per epilogue warp
     static constexpr int A_BYTES = BM * BK;
-    static constexpr int B_BYTES = BN * BK;
+    static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;   // two accumulator buffers, power of two
     static constexpr int AUX_BYTES = kEpiWarps * 2 * HC * 4;        // per epilogue warp: [scale|bias][HC] fp32
@@ -234,11 +238,11 @@ __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
 // N % BN == 0, K % 128 == 0; any M >= 1: the last row block may be partial (TMA fills the
 // missing rows of A with zeros; nothing is stored for rows >= M).
 // ---------------------------------------------------------------------------
-template <int BN, bool GELU, bool FUSED, bool DEFER, bool EXACT = false>
+template <int BN, bool GELU, bool FUSED, bool DEFER, bool EXACT = false, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                EpiParams ep, int M, int N, int K, int b_mn, uint32_t* __restrict__ status) {
-    using Cfg = GemmCfg<BN, FUSED, FUSED && DEFER>;
+    using Cfg = GemmCfg<BN, FUSED, FUSED && DEFER, PAIR>;
     constexpr int STAGES = Cfg::STAGES;
 
     extern __shared__ unsigned char smem_raw[];
@@ -261,8 +265,15 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int tiles_n = N / BN;
-    const int num_tiles = ((M + BM - 1) / BM) * tiles_n;
+    const int row_blocks = (M + BM - 1) / BM;
+    // a unit of the persistent loop: one tile, or with PAIR the two tiles of a 256-row block
+    // that a CTA pair works on together (the odd CTA's tile may lie wholly below row M)
+    const int num_tiles = PAIR ? ((row_blocks + 1) / 2) * tiles_n : row_blocks * tiles_n;
     const int kblocks = K / BK;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+    const int u0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int ustride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    auto unit_m0 = [&](int u) { return PAIR ? (u / tiles_n) * (2 * BM) + (int)cta_rank * BM : (u / tiles_n) * BM; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -271,13 +282,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull0 + 8 * b, 1);
-            mbar_init(tempty0 + 8 * b, kEpiWarps);     // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * b, PAIR ? 2 * kEpiWarps : kEpiWarps);     // one arrival per epilogue warp
         }
         fence_mbar_init();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    if (warp == 1) {
+        if constexpr (PAIR) tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+        else tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();    // the partner's barriers exist before anything is sent to them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
     pdl_launch_dependents();                    // the next GEMM may set itself up as SMs become free
@@ -288,8 +303,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int it = 0;
             bool ok = true;
             if (ep.a_from_prev) pdl_wait();              // A comes from the kernel before this one
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / tiles_n) * BM;
+            for (int tile = u0; tile < num_tiles && ok; tile += ustride) {
+                const int m0 = unit_m0(tile);
                 const int n0 = (tile % tiles_n) * BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % STAGES;
@@ -299,6 +314,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         break;
                     }
                     const uint32_t sa = base_s + st * Cfg::STAGE_BYTES;
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are counted on the even CTA's barrier: its MMA warp
+                        // starts when the whole 256-row stage is there
+                        const uint32_t fbar = mapa_shared(full0 + 8 * st, 0);
+                        if (cta_rank == 0) mbar_expect_tx(full0 + 8 * st, 2 * Cfg::STAGE_BYTES);
+                        const int nb = n0 + (int)cta_rank * (BN / 2);
+                        tma_load_2d_pair(sa, &tmA, kb * BK, m0, fbar);
+                        if (!b_mn) tma_load_2d_pair(sa + Cfg::A_BYTES, &tmB, kb * BK, nb, fbar);
+                        else tma_load_2d_pair(sa + Cfg::A_BYTES, &tmB, nb, kb * BK, fbar);
+                        continue;
+                    }
                     mbar_expect_tx(full0 + 8 * st, Cfg::STAGE_BYTES);
                     tma_load_2d(sa, &tmA, kb * BK, m0, full0 + 8 * st);
                     if (!b_mn) {
@@ -315,11 +341,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        if (elect_one()) {
-            const uint32_t idesc = idesc_i8(BM, BN, b_mn != 0);
+        if (cta_rank == 0 && elect_one()) {
+            const uint32_t idesc = idesc_i8(PAIR ? 2 * BM : BM, BN, b_mn != 0);
             int it = 0, lt = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+            for (int tile = u0; tile < num_tiles && ok; tile += ustride, ++lt) {
                 const int buf = lt & 1;
                 if (!mbar_wait_spin_bounded(tempty0 + 8 * buf, ((lt >> 1) & 1) ^ 1)) {
                     note_timeout(status);
@@ -343,11 +369,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // units); the MN-major one advances 32 rows of 128 bytes (+256)
                     const uint32_t db_step = b_mn ? 256u : 2u;
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k)
-                        mma_i8(tmem_d, da + 2 * k, db + (uint64_t)(db_step * k), idesc, (kb | k) != 0);
-                    tc_commit(empty0 + 8 * st);           // stage reusable when these MMAs retire
+                    for (int k = 0; k < BK / 32; ++k) {
+                        if constexpr (PAIR) mma_i8_pair(tmem_d, da + 2 * k, db + (uint64_t)(db_step * k), idesc, (kb | k) != 0);
+                        else mma_i8(tmem_d, da + 2 * k, db + (uint64_t)(db_step * k), idesc, (kb | k) != 0);
+                    }
+                    // stage reusable when these MMAs retire (PAIR: in both CTAs)
+                    if constexpr (PAIR) tc_commit_pair(empty0 + 8 * st, 3);
+                    else tc_commit(empty0 + 8 * st);
                 }
-                if (ok) tc_commit(tfull0 + 8 * buf);      // accumulator complete
+                if (ok) {                                 // accumulator complete
+                    if constexpr (PAIR) tc_commit_pair(tfull0 + 8 * buf, 3);
+                    else tc_commit(tfull0 + 8 * buf);
+                }
             }
         }
     } else {
@@ -367,7 +400,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // dropped into this warp's block of shared memory just before the tile that uses them.
         float pf_s[NPF], pf_b[NPF], pf_sa = 0.f;
         auto prefetch = [&](int tile) {
-            const int pm0 = (tile / tiles_n) * BM, pn0 = (tile % tiles_n) * BN;
+            const int pm0 = unit_m0(tile), pn0 = (tile % tiles_n) * BN;
 #pragma unroll
             for (int j = 0; j < NPF; ++j) {
                 const int cj = j * 32 + lane;
@@ -394,7 +427,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     ep.preset_ptr[i] = ones;
             }
         }
-        if ((int)blockIdx.x < num_tiles) prefetch(blockIdx.x);
+        if (u0 < num_tiles) prefetch(u0);
 
         // Requantisation of a tile whose fp16 values sit in this warp's stash: wait for the
         // maxima of its row block, then 16 columns (16 bytes of int8) per lane and step, a row
@@ -447,9 +480,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
         int p_m0 = -1, p_n0 = 0;                          // DEFER: tile waiting in the stash
         int lt = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+        for (int tile = u0; tile < num_tiles; tile += ustride, ++lt) {
             const int buf = lt & 1;
-            const int m0 = (tile / tiles_n) * BM;
+            const int m0 = unit_m0(tile);
             const int n0 = (tile % tiles_n) * BN;
 
             __syncwarp();
@@ -464,7 +497,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const float sa = pf_sa;
             const f32x2 sa2 = pack2(sa, sa);
             __syncwarp();
-            if (tile + (int)gridDim.x < num_tiles) prefetch(tile + gridDim.x);
+            if (tile + ustride < num_tiles) prefetch(tile + ustride);
 
             const bool got = mbar_wait_spin_bounded(tfull0 + 8 * buf, (lt >> 1) & 1);
             if (!__all_sync(0xffffffffu, got)) {
@@ -564,7 +597,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // accumulator buffer drained: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(tempty0 + 8 * buf, 0));   // the MMA warp sits in the even CTA
+                else mbar_arrive(tempty0 + 8 * buf);
+            }
 
             if (ep.out_absmax) {
                 float wmax;
@@ -579,7 +615,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 float* cq = cmb + (buf * 4 + q) * (kSlices * 32);
                 cq[slice * 32 + lane] = rmax;
                 asm volatile("bar.sync %0, %1;" ::"r"(1 + q), "n"(kSlices * 32) : "memory");
-                if (slice == 0) {
+                const bool live = !PAIR || m0 < M;          // the odd CTA's rows may all lie below M
+                if (slice == 0 && live) {
                     float m4 = rmax;
 #pragma unroll
                     for (int k = 1; k < kSlices; ++k) m4 = fmaxf(m4, cq[k * 32 + lane]);
@@ -596,9 +633,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         *reinterpret_cast<uint4*>(cst + lane * (HC * 2) + (stash_swz<HC>(lane, jc) << 4)) =
                             make_uint4(hv[4 * jc], hv[4 * jc + 1], hv[4 * jc + 2], hv[4 * jc + 3]);
                     __syncwarp();
-                    p_m0 = m0;
+                    p_m0 = live ? m0 : -1;
                     p_n0 = n0;
-                } else {
+                } else if (live) {
                     // at once, straight from the registers that hold this lane's row: with a long K
                     // loop the MMAs of the next tile cover the wait for the other tiles' maxima.
                     // 16 codes = one 16-byte store per 16-column block of the lane's own row.
@@ -638,9 +675,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // common exit: every role ends here, then the allocating warp frees TMEM
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();    // neither CTA leaves while the other may still signal it
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+        else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
 }
 
@@ -800,10 +839,17 @@ int sm_count_mlp() {
 }
 // CTAs of a persistent launch.  Fused kernels: the CTAs that share a row block wait for
 // one another, so every round of the persistent loop covers whole row blocks.
-int gemm_grid(int M, int N, int bn, bool fused) {
+int gemm_grid(int M, int N, int bn, bool fused, bool pair = false) {
     const int sms = sm_count_mlp();
     const int tiles_n = N / bn;
-    const long long tiles = (long long)((M + BM - 1) / BM) * tiles_n;
+    const int row_blocks = (M + BM - 1) / BM;
+    if (pair) {     // counted in CTA pairs, each on one 256-row unit at a time
+        const long long units = (long long)((row_blocks + 1) / 2) * tiles_n;
+        int pairs = units < sms / 2 ? (int)units : sms / 2;
+        if (fused && pairs > tiles_n) pairs = (pairs / tiles_n) * tiles_n;
+        return 2 * (pairs > 0 ? pairs : 1);
+    }
+    const long long tiles = (long long)row_blocks * tiles_n;
     int grid = tiles < sms ? (int)tiles : sms;
     if (fused && grid > tiles_n) grid = (grid / tiles_n) * tiles_n;
     return grid > 0 ? grid : 1;
@@ -827,36 +873,56 @@ int pick_bn(int M, int N, bool b_mn, bool fused) {
     return best;
 }
 
-template <int BN, bool GELU, bool FUSED, bool DEFER, bool EXACT = false>
+template <int BN, bool GELU, bool FUSED, bool DEFER, bool EXACT = false, bool PAIR = false>
 int launch_gemm(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                 uint32_t* status, cudaStream_t st) {
-    using Cfg = GemmCfg<BN, FUSED, FUSED && DEFER>;
+    using Cfg = GemmCfg<BN, FUSED, FUSED && DEFER, PAIR>;
     static_assert(Cfg::SMEM_BYTES <= 232448, "tile configuration exceeds the shared memory of an SM");
     static bool attr_done[64] = {false};
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU, FUSED, DEFER, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        I8TK_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, GELU, FUSED, DEFER, EXACT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::SMEM_BYTES));
         attr_done[dev] = true;
     }
     CUtensorMap tmA, tmB;
     int rc = cached_map(&tmA, A, M, K, BM, false);
     if (rc != I8TK_OK) return rc;
-    rc = b_mn ? cached_map(&tmB, B, K, N, 0, true) : cached_map(&tmB, B, N, K, BN, false);
+    rc = b_mn ? cached_map(&tmB, B, K, N, 0, true) : cached_map(&tmB, B, N, K, PAIR ? BN / 2 : BN, false);
     if (rc != I8TK_OK) return rc;
-    const int grid = gemm_grid(M, N, BN, FUSED);
-    I8TK_REQUIRE(!FUSED || N / BN <= sm_count_mlp(), I8TK_ERR_UNSUPPORTED,
+    const int grid = gemm_grid(M, N, BN, FUSED, PAIR);
+    I8TK_REQUIRE(!FUSED || N / BN <= sm_count_mlp() / (PAIR ? 2 : 1), I8TK_ERR_UNSUPPORTED,
                  "row of %d tiles does not fit one round of CTAs", N / BN);
-    I8TK_CUDA(launch_after(gemm_i8_kernel<BN, GELU, FUSED, DEFER, EXACT>, dim3(grid), dim3(kGemmThreads), Cfg::SMEM_BYTES, st,
-                           tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status));
+    I8TK_CUDA(launch_after_clustered(gemm_i8_kernel<BN, GELU, FUSED, DEFER, EXACT, PAIR>, dim3(grid), dim3(kGemmThreads),
+                                     Cfg::SMEM_BYTES, st, PAIR ? 2 : 1, tmA, tmB, ep, M, N, K, b_mn ? 1 : 0, status));
     return I8TK_OK;
+}
+
+// I8TK_MLP_PAIRS (read once): 0 keeps every GEMM on single CTAs, 1 puts the requantise-at-once
+// GEMM on CTA pairs wherever it has two row blocks; unset: pairs where they were measured to
+// pay, i.e. when the persistent loop runs more than one round (1-4 % of the forward at
+// M = 8192 and 16384: a third less operand traffic into each SM, a half deeper ring; with one
+// tile per CTA the cluster launch and the paired start cost more than that saves: M=4096
+// 44.2 vs 42.9 us).
+int pairs_mode() {
+    static const int mode = [] {
+        const char* e = std::getenv("I8TK_MLP_PAIRS");
+        return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : 2;
+    }();
+    return mode;
 }
 
 template <bool GELU, bool FUSED, bool DEFER, bool EXACT = false>
 int launch_gemm_bn(const int8_t* A, const int8_t* B, bool b_mn, const EpiParams& ep, int M, int N, int K,
                    uint32_t* status, cudaStream_t st) {
     const int best = pick_bn(M, N, b_mn, FUSED);
+    if constexpr (FUSED && !DEFER && !EXACT) {
+        const int mode = pairs_mode();
+        const long long tiles = (long long)((M + BM - 1) / BM) * (N / 256);
+        if (best == 256 && M > BM && (mode == 1 || (mode == 2 && tiles > sm_count_mlp())))
+            return launch_gemm<256, GELU, FUSED, DEFER, EXACT, true>(A, B, b_mn, ep, M, N, K, status, st);
+    }
     if (best == 256) return launch_gemm<256, GELU, FUSED, DEFER, EXACT>(A, B, b_mn, ep, M, N, K, status, st);
     if (best == 192) return launch_gemm<192, GELU, FUSED, DEFER, EXACT>(A, B, b_mn, ep, M, N, K, status, st);
     return launch_gemm<128, GELU, FUSED, DEFER, EXACT>(A, B, b_mn, ep, M, N, K, status, st);

@@ -43,8 +43,10 @@ def make_inputs(torch, ext, b, h, s, d, outliers=False, seed=0):
 PROFILE_CASES = {
     "decode_d64": (8, 12, 64, 16384),      # 201 MB of int8 K+V
     "decode_d128": (8, 8, 128, 8192),      # 134 MB
+    "mlp_m512_768": (512, 768, 3072),      # the reference's own benchmark shape: latency, not throughput
     "mlp_m4096_768": (4096, 768, 3072),    # fused MLP forward (L2 resident by nature: 30 MB of operands)
     "mlp_m4096_1024": (4096, 1024, 4096),
+    "mlp_m16384_1024": (16384, 1024, 4096),   # several rounds of the persistent loop per CTA
     "quantize_f32_64": (3145728, 64),      # rows, cols: 1.0 GB through the per-token quantiser
     "prefill_d64": (2, 8, 4096, 64),       # B, H, S, D: 512 CTAs of 128 query rows
     "prefill_d128": (2, 8, 4096, 128),

@@ -220,7 +220,8 @@ def test_any_number_of_rows(T):
 
 @pytest.mark.parametrize("M,dm,dff", [(4096, 768, 3072),     # benchmark geometry: 3 tiles per CTA in GEMM1
                                       (16384, 1024, 4096),   # 15 tiles per CTA, 16 tiles per row block
-                                      (1024, 256, 8192)])    # 32 tiles per row block: maxima not read ahead
+                                      (1024, 256, 8192),     # 32 tiles per row block: maxima not read ahead
+                                      (4900, 1024, 1024)])   # GEMM2 on CTA pairs, 39 row blocks: one CTA of the last pair has no rows
 def test_full_size_config_properties(M, dm, dff):
     """Large geometries (several tiles per persistent CTA, requantisation deferred by a tile):
     determinism, row independence (a row's result does not depend on the other rows) and the
@@ -242,6 +243,11 @@ def test_full_size_config_properties(M, dm, dff):
     out_s, osc_s = e.int8_mlp_forward_per_channel_bias(xi[:, sub].contiguous(), w1_t, w2_t,
                                                        sx.reshape(-1)[sub].contiguous(), s1_t, s2_t, b1)
     assert torch.equal(out_s[0], out[0, sub]) and torch.equal(osc_s, osc[sub])
+    last = slice(M - (M % 128 or 128), M)                       # the last, possibly partial, row block
+    out_l, osc_l = e.int8_mlp_forward_per_channel_bias(xi[:, last].contiguous(), w1_t, w2_t,
+                                                       sx.reshape(-1)[last].contiguous(), s1_t, s2_t, b1)
+    assert torch.equal(out_l[0], out[0, last]) and torch.equal(osc_l, osc[last])
+    e.check_status()                                            # raises if any bounded wait ran out
     ref = omlp.kernel_mlp(xi[0, sub].cpu().numpy(), w1i, w2i, sx.reshape(-1)[sub].cpu().numpy(), s1, s2,
                           b1=b1.cpu().numpy())
     _compare_with_kernel_oracle(out_s[0].cpu().numpy(), osc_s.cpu().numpy(), ref)
