@@ -1101,8 +1101,10 @@ int mlp_core(const int8_t* x, const int8_t* W1, const int8_t* W2, int8_t* out, c
     // maxima of its row block (12-16 tiles on as many SMs) are exchanged through global
     // memory, and are quantised one tile later, when that exchange has long finished.
     {
+        // a_from_prev: x may come from the kernel launched just before this one (a quantiser that
+        // lets its successor start early), so the producer warp waits for it like everyone else
         EpiParams e1{scale_x, scale_W1, bias1, nullptr, nullptr, per_token, per_channel,
-                     w.hid_i8, w.hid_scale, w.parts1, 0, nullptr, kept ? 1 : 0, w.tensor_absmax,
+                     w.hid_i8, w.hid_scale, w.parts1, 1, nullptr, kept ? 1 : 0, w.tensor_absmax,
                      reinterpret_cast<uint4*>(w.parts2), p2_words};
         if (exact)
             rc = launch_gemm_bn<true, true, true, true>(x, W1, b_mn, e1, T, d_ff, d_model, w.status, st);
@@ -1160,7 +1162,7 @@ extern "C" int i8tk_linear_i8_f16(const int8_t* x, const int8_t* W, const float*
                  "workspace: 256 bytes, 256-byte aligned (the status block)");
     const bool b_mn = !(flags & I8TK_MLP_PREPACKED);
     EpiParams e{scale_x, scale_W, bias, static_cast<__half*>(out_f16), nullptr, (flags & I8TK_MLP_X_PER_TOKEN) ? 1 : 0,
-                (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0, nullptr, nullptr, nullptr, 0, nullptr, 1, nullptr, nullptr, 0};
+                (flags & I8TK_MLP_W_PER_CHANNEL) ? 1 : 0, nullptr, nullptr, nullptr, 1, nullptr, 1, nullptr, nullptr, 0};
     return launch_gemm_bn<false, false, false>(x, W, b_mn, e, T, N, K, static_cast<uint32_t*>(workspace),
                                                static_cast<cudaStream_t>(stream));
 }

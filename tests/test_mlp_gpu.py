@@ -409,3 +409,29 @@ def test_workspace_kept_flag_gives_identical_results():
             again = e.int8_mlp_forward_per_channel_bias(xs[0], w1, w2, sx, s1, s2, b1)
             assert torch.equal(again[0], first[0]) and torch.equal(again[1], first[1])
     e.check_status()
+
+
+def test_input_written_by_the_kernel_just_before():
+    """The activations usually come from the quantiser launched just before the MLP, and that kernel lets its
+    successor start while it is still running.  With the workspace kept there is no preset kernel in between,
+    so GEMM1's producer warp itself has to wait for the quantiser before it copies x: every forward of a run
+    on changing inputs must equal the same forward done after a full synchronisation."""
+    e = ext()
+    torch.manual_seed(11)
+    T, dm, dff = 8192, 256, 1024           # a long quantiser pass in front of a short GEMM
+    w1 = torch.randint(-127, 128, (dm, dff), dtype=torch.int8, device="cuda")
+    w2 = torch.randint(-127, 128, (dff, dm), dtype=torch.int8, device="cuda")
+    s1 = torch.rand(dff, device="cuda") * 1e-4 + 1e-4
+    s2 = torch.rand(dm, device="cuda") * 1e-4 + 1e-4
+    xs = [torch.randn(1, T, dm, device="cuda", dtype=torch.float16) * (i + 1) for i in range(6)]
+    wants = []
+    for x in xs:
+        codes, scales = e.quantize_per_token(x)
+        torch.cuda.synchronize()
+        out, osc = e.int8_mlp_forward(codes, w1, w2, scales.reshape(-1), s1, s2)
+        torch.cuda.synchronize()
+        wants.append((out.clone(), osc.clone()))
+    for x, (want, want_sc) in zip(xs, wants):
+        codes, scales = e.quantize_per_token(x)               # no synchronisation: back to back on the stream
+        out, osc = e.int8_mlp_forward(codes, w1, w2, scales.reshape(-1), s1, s2)
+        assert torch.equal(out, want) and torch.equal(osc, want_sc)
