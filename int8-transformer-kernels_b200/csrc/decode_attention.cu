@@ -441,7 +441,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         float m = -INFINITY, l = 0.f;
         f32x2 acc[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] = 0ull;
+        for (int k = 0; k < 8; ++k) acc[k] = pack2(0.f, 0.f);
 
         float sk_next = 0.f, sv_next = 0.f;         // scales when they do not ride the bulk copies
         if constexpr (!SCALES_BULK) {

@@ -15,6 +15,14 @@
 namespace i8tk {
 namespace {
 
+// packed fp32 pairs in their inline-PTX form here (see asm2 in common.cuh)
+using f32x2 = asm2::f32x2;
+using asm2::add2;
+using asm2::fma2;
+using asm2::mul2;
+using asm2::pack2;
+using asm2::unpack2;
+
 __device__ __forceinline__ int quant_exact(float x, float scale) {
     // true division + round-half-even + clamp, exactly as torch does on fp32
     const float r = rintf(__fdiv_rn(x, scale));
@@ -171,7 +179,7 @@ layernorm_quantize_warp_kernel(const __half* __restrict__ x, int8_t* __restrict_
     for (long long row = warp; row < rows; row += nwarps) {
         if constexpr (!kPrefetch) fetch(row);
         f32x2 v[NV][4];
-        f32x2 sum2 = 0ull;
+        f32x2 sum2 = pack2(0.f, 0.f);
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             const __half2* h = reinterpret_cast<const __half2*>(&t[j]);
@@ -186,7 +194,7 @@ layernorm_quantize_warp_kernel(const __half* __restrict__ x, int8_t* __restrict_
         const float2 s2 = unpack2(sum2);
         const float mean = warp_sum_f(s2.x + s2.y) * inv_d;
         const f32x2 nmean2 = pack2(-mean, -mean);
-        f32x2 ss2 = 0ull;
+        f32x2 ss2 = pack2(0.f, 0.f);
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             if (lane + j * 32 < nvec) {

@@ -289,7 +289,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         constexpr uint32_t kMagicI = 0x4B400000u;
         const f32x2 nmagic2 = pack2(-12582912.f, -12582912.f);
         float m_ref = -INFINITY;
-        f32x2 l2 = 0ull;
+        f32x2 l2 = pack2(0.f, 0.f);
         bool ok = true;
         // this warp's per-position scales, fetched ahead of the tile that uses them
         float pk0, pk1 = 0.f;
