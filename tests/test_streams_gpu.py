@@ -47,3 +47,35 @@ def test_decode_and_mlp_on_two_streams_match_serial_results():
             assert torch.equal(outs[rep][i], serial[i]), (rep, i)
     for o, sc in mlps:
         assert torch.equal(o, mlp_serial[0]) and torch.equal(sc, mlp_serial[1])
+
+
+def test_two_large_mlp_forwards_on_two_streams():
+    """Two forwards that each want nearly every SM, issued on two streams: the CTAs of the later kernels
+    become resident as those of the earlier ones leave, and the CTAs that share a row block wait (bounded)
+    for siblings that arrive a little later.  The results must be those of the serial calls and no wait may
+    have given up."""
+    e = ext()
+    g = torch.Generator(device="cuda").manual_seed(21)
+    shapes = [(4096, 1024, 4096), (4096, 768, 3072)]
+    jobs = []
+    for (M, dm, dff) in shapes:
+        xi, sx = e.quantize_per_token(torch.randn(1, M, dm, device="cuda", dtype=torch.float16, generator=g))
+        w1 = torch.randint(-127, 128, (dm, dff), dtype=torch.int8, device="cuda", generator=g)
+        w2 = torch.randint(-127, 128, (dff, dm), dtype=torch.int8, device="cuda", generator=g)
+        s1 = torch.rand(dff, device="cuda", generator=g) * 1e-4 + 1e-4
+        s2 = torch.rand(dm, device="cuda", generator=g) * 1e-4 + 1e-4
+        jobs.append((xi, w1, w2, sx.reshape(-1).contiguous(), s1, s2))
+    serial = [e.int8_mlp_forward(*j) for j in jobs]
+    torch.cuda.synchronize()
+    e.check_status()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    got = [[], []]
+    for rep in range(8):
+        for i, j in enumerate(jobs):
+            with torch.cuda.stream(streams[i]):
+                got[i].append(e.int8_mlp_forward(*j))
+    torch.cuda.synchronize()
+    e.check_status()                                     # raises if a bounded wait ran out
+    for i in range(2):
+        for o, sc in got[i]:
+            assert torch.equal(o, serial[i][0]) and torch.equal(sc, serial[i][1])
