@@ -248,6 +248,21 @@ def test_full_size_config_properties(M, dm, dff):
                                                        sx.reshape(-1)[last].contiguous(), s1_t, s2_t, b1)
     assert torch.equal(out_l[0], out[0, last]) and torch.equal(osc_l, osc[last])
     e.check_status()                                            # raises if any bounded wait ran out
+    # prepacked weights ([N][K], K-major operand descriptors) through the C ABI: the same bytes
+    c = cabi()
+    lib = c.load()
+    W1T, W2T = e.transpose_int8_weights(w1_t, w2_t)
+    flags = c.MLP_X_PER_TOKEN | c.MLP_W_PER_CHANNEL | c.MLP_PREPACKED
+    wb = lib.i8tk_mlp_workspace_bytes(M, dm, dff, flags)
+    ws = torch.empty(wb, dtype=torch.uint8, device="cuda")
+    out_p = torch.empty_like(out)
+    osc_p = torch.empty_like(osc)
+    c.check(lib.i8tk_mlp_forward(xi.data_ptr(), W1T.data_ptr(), W2T.data_ptr(), out_p.data_ptr(),
+                                 sx.reshape(-1).data_ptr(), s1_t.data_ptr(), s2_t.data_ptr(), b1.data_ptr(),
+                                 osc_p.data_ptr(), None, M, dm, dff, flags, ws.data_ptr(), wb,
+                                 torch.cuda.current_stream().cuda_stream))
+    assert lib.i8tk_check_status_word(ws.data_ptr(), torch.cuda.current_stream().cuda_stream) == c.OK
+    assert torch.equal(out_p, out) and torch.equal(osc_p, osc)
     ref = omlp.kernel_mlp(xi[0, sub].cpu().numpy(), w1i, w2i, sx.reshape(-1)[sub].cpu().numpy(), s1, s2,
                           b1=b1.cpu().numpy())
     _compare_with_kernel_oracle(out_s[0].cpu().numpy(), osc_s.cpu().numpy(), ref)
