@@ -218,7 +218,7 @@ int i8tk_decode_attention_forward_static(const int8_t* Q, const int8_t* K, const
  * max_seq_len is a host-side upper bound on seq_lens (it sizes the grid and the workspace:
  * i8tk_decode_workspace_bytes(batch*heads, max_seq_len, head_dim)); an entry of seq_lens outside
  * [0, max_seq_len] is read as the nearer end of that range, so a damaged length cannot send the
- * kernels past a page-table row.  Page ids are trusted.  The lengths themselves
+ * kernels past a page-table row.  Page ids are trusted here (see the _checked form below).  The lengths themselves
  * are read on the device only: a one-CTA kernel counts the 128-position tiles each request
  * really has and cuts their sequence into equal runs for the CTAs of the scan, so a batch of
  * mixed lengths takes the time of the bytes it reads, not of batch x the longest request.
@@ -230,6 +230,17 @@ int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool, const int
                                 int batch, int heads, int max_seq_len, int page_size,
                                 int max_pages_per_seq, int head_dim,
                                 void* workspace, size_t workspace_bytes, i8tk_stream_t stream);
+/* The same with the number of pages in the pools given: a page id outside [0, num_pages) met
+ * on the device is not followed -- page 0 is read in its place, so nothing outside the pools
+ * is touched -- and recorded in the status block: i8tk_check_status_word on the workspace then
+ * returns I8TK_ERR_INVALID_ARGUMENT (the output rows of the requests concerned are not valid). */
+int i8tk_decode_attention_paged_checked(const int8_t* Q, const int8_t* K_pool, const int8_t* V_pool,
+                                        void* out_f16, const float* sQ,
+                                        const float* sK_pool, const float* sV_pool,
+                                        const int32_t* page_table, const int32_t* seq_lens,
+                                        int batch, int heads, int max_seq_len, int page_size,
+                                        int max_pages_per_seq, int head_dim, int num_pages,
+                                        void* workspace, size_t workspace_bytes, i8tk_stream_t stream);
 
 /* Sequence-sharded form: the same scan over this caller's KV positions, but
  * the result is left as ONE unnormalised online-softmax partial per (b,h):

@@ -53,6 +53,7 @@ SIGNATURES = {
     "i8tk_decode_attention_forward_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "i8tk_decode_static_check_status": (_i, [_vp]),
     "i8tk_decode_attention_paged": (_i, [_vp] * 9 + [_i] * 6 + [_vp, _sz, _vp]),
+    "i8tk_decode_attention_paged_checked": (_i, [_vp] * 9 + [_i] * 7 + [_vp, _sz, _vp]),
     "i8tk_decode_attention_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "i8tk_decode_combine_partials": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "i8tk_decode_exchange_ctas": (_i, [_i]),

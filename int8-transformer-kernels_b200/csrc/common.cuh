@@ -43,6 +43,9 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 //   word 1  counts such give-ups and is never cleared by a kernel: a caller that zeroes it
 //           once can look at it as rarely as it likes and still learn that some call failed
 constexpr uint32_t kDeviceTimeoutMagic = 0xD1E7E0u;
+// Same two words, other cause: an index read on the device (a page id) lay outside the bound
+// the caller gave; the kernel used a valid one in its place so that nothing is read out of range.
+constexpr uint32_t kDeviceBadIndexMagic = 0xBAD1D0u;
 
 // ---- device helpers -----------------------------------------------------
 #ifdef __CUDACC__
@@ -50,6 +53,10 @@ constexpr uint32_t kDeviceTimeoutMagic = 0xD1E7E0u;
 // A bounded wait gave up: mark the call and bump the sticky count (see kDeviceTimeoutMagic).
 __device__ __forceinline__ void note_timeout(uint32_t* status) {
     atomicExch(status, kDeviceTimeoutMagic);
+    atomicAdd(status + 1, 1u);
+}
+__device__ __forceinline__ void note_bad_index(uint32_t* status) {
+    atomicExch(status, kDeviceBadIndexMagic);
     atomicAdd(status + 1, 1u);
 }
 // Run by one thread of the first kernel of a call, before anything of that call can give up.

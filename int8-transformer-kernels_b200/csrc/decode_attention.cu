@@ -88,12 +88,23 @@ struct PagedKV {
     int max_pages;           // row length of page_table
     int B;                   // requests
     int max_len;             // host-side bound on seq_lens: longer entries are read as this
+    int num_pages;           // pages in the pools, or 0 when the caller gave no bound: ids are then trusted
     const int* hdr;          // plan: [0] tiles per CTA, [1] tiles in all
     const int* prefix;       // plan: [B+1] tiles per head of the requests before b
     const int4* starts;      // plan: [nctas] {first (b,h) row, first tile in it, tiles of the run, 0}
 };
 
 __device__ __forceinline__ int tiles_of(int len) { return len > 0 ? (len + kTile - 1) / kTile : 0; }
+// A page id as the producer uses it: with a bound given, an id outside [0, num_pages) is
+// recorded in the status block and page 0 is read in its place.
+__device__ __forceinline__ int checked_page(const PagedKV& pg, const int* id_ptr, uint32_t* status) {
+    const int id = __ldg(id_ptr);
+    if (pg.num_pages > 0 && (unsigned)id >= (unsigned)pg.num_pages) {
+        note_bad_index(status);
+        return 0;
+    }
+    return id;
+}
 // A request's length as the kernels use it: inside [0, max_len], so that a damaged entry can
 // neither walk off its page-table row nor leave the workspace sized from max_len.
 __device__ __forceinline__ int request_len(const int* seq_lens, int b, int max_len) {
@@ -368,7 +379,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
                     if (lane == 0) mbar_expect_tx(bar, (uint32_t)npg * 2 * (kv_bytes + sc_bytes));
                     if (lane < npg) {
                         const int q = lane;
-                        const size_t first = ((size_t)__ldg(ids + q) * pg.H + h) * pg.page;   // first position of the page
+                        const size_t first = ((size_t)checked_page(pg, ids + q, status) * pg.H + h) * pg.page;   // first position of the page
                         bulk_g2s_hint(dst + 2 * T::TILE_BYTES + q * sc_bytes, sK + first, sc_bytes, bar, stream_once);
                         bulk_g2s_hint(dst + 2 * T::TILE_BYTES + T::SCALE_BYTES + q * sc_bytes, sV + first, sc_bytes, bar,
                                       stream_once);
@@ -381,7 +392,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
                     // 64-128 bytes of scales per page go as 16-byte asynchronous copies of the page's
                     // lane, which the stage's barrier is told to wait for before lane 0 arrives
                     if (lane < npg) {
-                        const size_t first = ((size_t)__ldg(ids + lane) * pg.H + h) * pg.page;
+                        const size_t first = ((size_t)checked_page(pg, ids + lane, status) * pg.H + h) * pg.page;
                         bulk_g2s_hint(dst + lane * kv_bytes, K + first * D, kv_bytes, bar, stream_once);
                         bulk_g2s_hint(dst + T::TILE_BYTES + lane * kv_bytes, V + first * D, kv_bytes, bar, stream_once);
                         const uint32_t dk = dst + 2 * T::TILE_BYTES + lane * sc_bytes;
@@ -1185,12 +1196,12 @@ extern "C" int i8tk_decode_attention_seq_sharded(const int8_t* Q, const int8_t* 
     return I8TK_OK;
 }
 
-extern "C" int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool, const int8_t* V_pool,
-                                           void* out_f16, const float* sQ, const float* sK_pool,
-                                           const float* sV_pool, const int32_t* page_table,
-                                           const int32_t* seq_lens, int batch, int heads, int max_seq_len,
-                                           int page_size, int max_pages_per_seq, int head_dim, void* workspace,
-                                           size_t workspace_bytes, i8tk_stream_t stream) {
+static int paged_forward(const int8_t* Q, const int8_t* K_pool, const int8_t* V_pool,
+                         void* out_f16, const float* sQ, const float* sK_pool,
+                         const float* sV_pool, const int32_t* page_table,
+                         const int32_t* seq_lens, int batch, int heads, int max_seq_len,
+                         int page_size, int max_pages_per_seq, int head_dim, int num_pages, void* workspace,
+                         size_t workspace_bytes, i8tk_stream_t stream) {
     I8TK_REQUIRE(Q && K_pool && V_pool && out_f16 && sQ && sK_pool && sV_pool && page_table && seq_lens,
                  I8TK_ERR_INVALID_ARGUMENT, "null pointer argument");
     I8TK_REQUIRE(batch > 0 && heads > 0 && max_seq_len > 0 && max_pages_per_seq > 0, I8TK_ERR_INVALID_ARGUMENT,
@@ -1218,7 +1229,7 @@ extern "C" int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool
     int* hdr = reinterpret_cast<int*>(ws + lay.hdr_off);
     int4* starts = reinterpret_cast<int4*>(ws + lay.starts_off);
     int* prefix = reinterpret_cast<int*>(ws + lay.prefix_off);
-    const PagedKV pg{page_table, seq_lens, heads, page_size, max_pages_per_seq, batch, max_seq_len, hdr, prefix, starts};
+    const PagedKV pg{page_table, seq_lens, heads, page_size, max_pages_per_seq, batch, max_seq_len, num_pages, hdr, prefix, starts};
     const int resident = sm_count() * (head_dim == 64 ? DecodeTraits<64>::CTAS_PER_SM : DecodeTraits<128>::CTAS_PER_SM);
     I8TK_CUDA(launch_after(decode_ragged_plan_kernel, dim3(1), dim3(1024), 0, st, seq_lens, batch, heads, max_seq_len,
                            p.nctas, resident < p.nctas ? resident : p.nctas, paged_target_tiles(kPagedTargetTiles), hdr,
@@ -1236,6 +1247,28 @@ extern "C" int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool
                                (const float*)rows, BH, 0, p, static_cast<__half*>(out_f16), (float*)nullptr, pg, QuantOut{}));
     }
     return I8TK_OK;
+}
+
+extern "C" int i8tk_decode_attention_paged(const int8_t* Q, const int8_t* K_pool, const int8_t* V_pool,
+                                           void* out_f16, const float* sQ, const float* sK_pool,
+                                           const float* sV_pool, const int32_t* page_table,
+                                           const int32_t* seq_lens, int batch, int heads, int max_seq_len,
+                                           int page_size, int max_pages_per_seq, int head_dim, void* workspace,
+                                           size_t workspace_bytes, i8tk_stream_t stream) {
+    return paged_forward(Q, K_pool, V_pool, out_f16, sQ, sK_pool, sV_pool, page_table, seq_lens, batch, heads,
+                         max_seq_len, page_size, max_pages_per_seq, head_dim, 0, workspace, workspace_bytes, stream);
+}
+
+extern "C" int i8tk_decode_attention_paged_checked(const int8_t* Q, const int8_t* K_pool, const int8_t* V_pool,
+                                                   void* out_f16, const float* sQ, const float* sK_pool,
+                                                   const float* sV_pool, const int32_t* page_table,
+                                                   const int32_t* seq_lens, int batch, int heads, int max_seq_len,
+                                                   int page_size, int max_pages_per_seq, int head_dim, int num_pages,
+                                                   void* workspace, size_t workspace_bytes, i8tk_stream_t stream) {
+    I8TK_REQUIRE(num_pages > 0, I8TK_ERR_INVALID_ARGUMENT, "num_pages must be positive (got %d)", num_pages);
+    return paged_forward(Q, K_pool, V_pool, out_f16, sQ, sK_pool, sV_pool, page_table, seq_lens, batch, heads,
+                         max_seq_len, page_size, max_pages_per_seq, head_dim, num_pages, workspace, workspace_bytes,
+                         stream);
 }
 
 extern "C" int i8tk_decode_attention_partial(const int8_t* Q, const int8_t* K, const int8_t* V,

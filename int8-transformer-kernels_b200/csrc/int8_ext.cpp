@@ -136,7 +136,8 @@ int64_t check_status_torch() {
         }
     }
     TORCH_CHECK(failures == 0, "int8_ext: ", failures,
-                " bounded device-side wait(s) gave up since the last check; the outputs of those calls are not valid");
+                " device-side check(s) failed since the last look (a bounded wait that gave up, or a page id outside "
+                "the pool); the outputs of those calls are not valid");
     return static_cast<int64_t>(blocks.size());
 }
 
@@ -252,13 +253,14 @@ torch::Tensor int8_decode_attention_paged_torch(torch::Tensor Q, torch::Tensor K
     const size_t wbytes = i8tk_decode_workspace_bytes(static_cast<int>(B * H), static_cast<int>(max_seq_len),
                                                       static_cast<int>(D));
     auto ws = make_workspace(wbytes, Q.device());
-    check_status(i8tk_decode_attention_paged(
+    // the pool size is known here, so page ids are checked on the device (check_status() reports a bad one)
+    check_status(i8tk_decode_attention_paged_checked(
                      Q.data_ptr<int8_t>(), K_pool.data_ptr<int8_t>(), V_pool.data_ptr<int8_t>(), out.data_ptr(),
                      sq.data_ptr<float>(), sK_pool.data_ptr<float>(), sV_pool.data_ptr<float>(),
                      page_table.data_ptr<int32_t>(), seq_lens.data_ptr<int32_t>(), static_cast<int>(B),
                      static_cast<int>(H), static_cast<int>(max_seq_len), static_cast<int>(page),
-                     static_cast<int>(page_table.size(1)), static_cast<int>(D), ws.data_ptr(), wbytes,
-                     current_stream()),
+                     static_cast<int>(page_table.size(1)), static_cast<int>(D), static_cast<int>(pages),
+                     ws.data_ptr(), wbytes, current_stream()),
                  "int8_decode_attention_paged");
     return out;
 }

@@ -44,5 +44,7 @@ extern "C" int i8tk_check_status_word(const void* status_word, i8tk_stream_t str
     I8TK_CUDA(cudaStreamSynchronize(st));
     I8TK_REQUIRE(host != kDeviceTimeoutMagic, I8TK_ERR_DEVICE_TIMEOUT,
                  "a kernel gave up a bounded wait (status word 0x%x)", host);
+    I8TK_REQUIRE(host != kDeviceBadIndexMagic, I8TK_ERR_INVALID_ARGUMENT,
+                 "a page id outside [0, num_pages) was met on the device (page 0 was read in its place)");
     return I8TK_OK;
 }

@@ -156,3 +156,28 @@ def test_paged_more_requests_than_the_plan_keeps_in_shared_memory():
         same = e.int8_decode_attention_forward(Qi[b:b + 1].contiguous(), Kc[None], Vc[None], sQ[b:b + 1].reshape(-1),
                                                sKc.reshape(-1), sVc.reshape(-1))
         assert (out[b:b + 1].float() - same.float()).abs().max().item() < 2e-3
+
+
+def test_page_id_outside_the_pool_is_not_followed():
+    """With the pool size known (the op always passes it) a damaged page id is never used as an address:
+    the kernel reads page 0 in its place, the other requests come out as before and check_status() reports
+    the bad id; the call after that is clean again."""
+    e = ext()
+    lens = [300, 90, 257]
+    Qi, sQ, Kp, Vp, sKp, sVp, table, seq, _ = _paged_case(3, 2, 64, lens, 16, seed=23)
+    good = e.int8_decode_attention_paged(Qi, Kp, Vp, sQ.reshape(-1), sKp, sVp, table, seq, 300)
+    torch.cuda.synchronize()
+    e.check_status()
+    bad = table.clone()
+    bad[1, 2] = Kp.size(0) + 1000          # far outside the pool
+    bad[1, 4] = -7
+    out = e.int8_decode_attention_paged(Qi, Kp, Vp, sQ.reshape(-1), sKp, sVp, bad, seq, 300)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert (out[[0, 2]].float() - good[[0, 2]].float()).abs().max().item() < 2e-3
+    with pytest.raises(RuntimeError, match="page id"):
+        e.check_status()
+    again = e.int8_decode_attention_paged(Qi, Kp, Vp, sQ.reshape(-1), sKp, sVp, table, seq, 300)
+    torch.cuda.synchronize()
+    e.check_status()
+    assert (again.float() - good.float()).abs().max().item() < 2e-3
