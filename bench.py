@@ -254,6 +254,7 @@ MIN_WINDOW_S = 0.05         # each window runs at least this long (and at least 
 # 128 bytes of K+V, plus what does not scale with positions.  Traffic grows in proportion to the
 # positions scanned, so the bench-size figure is this ratio times the K+V bytes.
 DRAM_BYTES_PER_KV_BYTE = 1.0627
+MLP_DRAM_BYTES_PER_FORWARD = {(4096, 1024, 4096): 8_510_000 + 21_040_000}   # GEMM1 + GEMM2, dram__bytes_read + write
 
 
 def parity_of_rows(torch, out, args, rows):
@@ -515,7 +516,10 @@ def mlp_headline(torch, ext, cabi):
                    "frac": tops / int8_peak if int8_peak else None,
                    "frac_of_4.5_POPS_nominal": tops / 4500.0,
                    "algorithmic_ops_per_forward": ops, "us_per_forward": t_med * 1e6,
-                   "us_per_forward_min_max": [t_min * 1e6, t_max * 1e6], "traffic": None})
+                   "us_per_forward_min_max": [t_min * 1e6, t_max * 1e6],
+                   # DRAM bytes of the two GEMM launches in a profiler capture of this shape (cold caches: the
+                   # operands, 30 MB, are L2-resident in the timed loop); not captured at the other width
+                   "traffic": MLP_DRAM_BYTES_PER_FORWARD.get((M, dm, dff))})
     out["roofline_mlp"] = rl
 
     # int8 codes against the stage-by-stage restatement of the reference kernel, M=512 768->3072

@@ -60,6 +60,14 @@ struct DecodeTraits {
     static constexpr int ROW_FLOATS = D + 4;           // m, l, 0, 0, acc[D]
 };
 
+// Whole-row runs (short contexts): two sets of kConsumers row slots in shared memory behind the
+// ring and its barriers, then the barrier the consumer warps meet on.
+template <int D>
+constexpr int kWholeSlotBytes = 2 * kConsumers * (D + 4) * 4;
+template <int D>
+constexpr int kWholeSmemBytes = DecodeTraits<D>::SMEM_BYTES + kWholeSlotBytes<D> + 16;
+constexpr int kWholeRowMaxTiles = 16;        // a row of at most this many tiles is never split across CTAs
+
 // How the flat tile sequence is divided.  CTA c scans flat tiles
 // [c*tpc, min(total, (c+1)*tpc)); flat tile f is tile f % tpb of (b,h) f / tpb.
 struct DecodePlan {
@@ -282,6 +290,57 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Log-sum-exp merge of `n` unnormalised rows {m, l, 0, 0, acc[D]} by one warp: lane holds D / 32
+// consecutive output dims.  Rows with l <= 0 (no positions) are skipped.
+template <int D, typename RowPtr>
+__device__ __forceinline__ void merge_rows(RowPtr row_ptr, int n, int lane, float& L, float (&a)[D / 32],
+                                           float* max_out = nullptr) {
+    constexpr int DPL = D / 32;
+    float gm = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+        const float2 ml = *reinterpret_cast<const float2*>(row_ptr(i));
+        if (ml.y > 0.f) gm = fmaxf(gm, ml.x);
+    }
+    gm = warp_max(gm);
+    L = 0.f;
+#pragma unroll
+    for (int k = 0; k < DPL; ++k) a[k] = 0.f;
+#pragma unroll 4
+    for (int i = 0; i < n; ++i) {
+        const float* r = row_ptr(i);
+        const float2 ml = *reinterpret_cast<const float2*>(r);
+        if (ml.y <= 0.f) continue;                 // empty part
+        const float wgt = ex2_approx(ml.x - gm);
+        L = fmaf(ml.y, wgt, L);
+        if constexpr (DPL == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(r + 4 + lane * 4);
+            a[0] = fmaf(v.x, wgt, a[0]); a[1] = fmaf(v.y, wgt, a[1]);
+            a[2] = fmaf(v.z, wgt, a[2]); a[3] = fmaf(v.w, wgt, a[3]);
+        } else {
+            const float2 v = *reinterpret_cast<const float2*>(r + 4 + lane * 2);
+            a[0] = fmaf(v.x, wgt, a[0]); a[1] = fmaf(v.y, wgt, a[1]);
+        }
+    }
+    if (max_out) *max_out = gm;
+}
+// The normalised fp16 output row (o points at its first element); a row without positions gives zeros.
+template <int D>
+__device__ __forceinline__ void store_out_row(__half* o, int lane, float L, const float (&a)[D / 32]) {
+    constexpr int DPL = D / 32;
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    o += lane * DPL;
+    if constexpr (DPL == 4) {
+        __half2 h0 = __floats2half2_rn(a[0] * inv, a[1] * inv);
+        __half2 h1 = __floats2half2_rn(a[2] * inv, a[3] * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&h0);
+        pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        *reinterpret_cast<uint2*>(o) = pk;
+    } else {
+        *reinterpret_cast<__half2*>(o) = __floats2half2_rn(a[0] * inv, a[1] * inv);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Pass 1: persistent CTAs over the flat tile sequence.  Warp kConsumers feeds
 // the ring (one lane issues the bulk copies); warps 0..kConsumers-1 each scan
@@ -293,15 +352,19 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---------------------------------------------------------------------------
 // PAGED: K, V, sK, sV are page pools addressed through `pg` and every request has its own
 // length (S is then the longest one: tiles past a request's end carry no bytes).
-template <int D, bool SCALES_BULK, bool PAGED>
+// WHOLE: every CTA's run is made of whole (b,h) rows (short contexts: a row is a few tiles), so
+// nothing has to be merged across CTAs: the four consumer warps fold their rows in shared memory
+// and warp 0 writes the fp16 output row -- no second kernel.
+template <int D, bool SCALES_BULK, bool PAGED, bool WHOLE = false>
 __global__ void __launch_bounds__(kThreads)
 decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K,
                       const int8_t* __restrict__ V, const float* __restrict__ sQ,
                       const float* __restrict__ sK, const float* __restrict__ sV,
                       float* __restrict__ rows,     // [nctas * maxseg * kConsumers, D+4]
                       int S, DecodePlan plan, float score_scale_log2,
-                      uint32_t* __restrict__ status, PagedKV pg) {
+                      uint32_t* __restrict__ status, PagedKV pg, __half* __restrict__ out) {
     static_assert(!PAGED || SCALES_BULK, "paged scales always ride the bulk copies");
+    static_assert(!WHOLE || !PAGED, "whole-row runs are planned on the host, for the contiguous cache");
     using T = DecodeTraits<D>;
     constexpr int LPR = T::LPR, RPP = T::RPP, STAGES = T::STAGES;
 
@@ -340,6 +403,7 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, kConsumers);
         }
+        if constexpr (WHOLE) mbar_init(ring_s + T::SMEM_BYTES + kWholeSlotBytes<D>, kConsumers);
         fence_mbar_init();
     }
     __syncthreads();
@@ -550,12 +614,36 @@ decode_partial_kernel(const int8_t* __restrict__ Q, const int8_t* __restrict__ K
         // paged: slot (row + CTA) is unique because the CTAs' runs are ordered by row
         float* row = PAGED ? rows + ((size_t)(c_bh + blockIdx.x) * kConsumers + warp) * T::ROW_FLOATS
                            : rows + (((size_t)blockIdx.x * plan.maxseg + seg) * kConsumers + warp) * T::ROW_FLOATS;
+        if constexpr (WHOLE) {
+            // this warp's row goes to shared memory instead (two sets of slots, by segment parity:
+            // warp 0 reaches the next segment's barrier only after it has merged this one)
+            row = reinterpret_cast<float*>(smem + T::SMEM_BYTES) + ((seg & 1) * kConsumers + warp) * T::ROW_FLOATS;
+        }
         if (lane == 0) *reinterpret_cast<float4*>(row) = make_float4(m, lsum, 0.f, 0.f);
         if (g == 0) {
             float4* dst = reinterpret_cast<float4*>(row + 4 + c * 16);
 #pragma unroll
             for (int k = 0; k < 4; ++k)
                 dst[k] = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
+        }
+        if constexpr (WHOLE) {
+            // the consumer warps meet on a barrier of their own, one phase per segment; the wait is
+            // bounded like every other, so a warp that gave up earlier cannot hold the rest
+            const uint32_t fin_bar = ring_s + T::SMEM_BYTES + kWholeSlotBytes<D>;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(fin_bar);
+            const bool met = mbar_wait_bounded(fin_bar, seg & 1);
+            if (!__all_sync(0xffffffffu, met)) {
+                if (lane == 0) note_timeout(status);
+                return;
+            }
+            if (warp == 0) {
+                const float* slots = reinterpret_cast<const float*>(smem + T::SMEM_BYTES) + (seg & 1) * kConsumers * T::ROW_FLOATS;
+                float L;
+                float o[D / 32];
+                merge_rows<D>([&](int r) { return slots + r * T::ROW_FLOATS; }, kConsumers, lane, L, o);
+                store_out_row<D>(out + (size_t)c_bh * D, lane, L, o);
+            }
         }
         c_tb += seg_tiles;
         if (c_tb == c_tpb) {
@@ -624,33 +712,9 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, Decode
         }
     };
 
-    float gm = -INFINITY;
-    for (int i = lane; i < n; i += 32) {
-        const float2 ml = *reinterpret_cast<const float2*>(row_ptr(i));
-        if (ml.y > 0.f) gm = fmaxf(gm, ml.x);
-    }
-    gm = warp_max(gm);
-
-    float L = 0.f;
+    float L, gm;
     float a[DPL];
-#pragma unroll
-    for (int k = 0; k < DPL; ++k) a[k] = 0.f;
-#pragma unroll 4
-    for (int i = 0; i < n; ++i) {
-        const float* r = row_ptr(i);
-        const float2 ml = *reinterpret_cast<const float2*>(r);
-        if (ml.y <= 0.f) continue;                 // empty part
-        const float wgt = ex2_approx(ml.x - gm);
-        L = fmaf(ml.y, wgt, L);
-        if constexpr (DPL == 4) {
-            const float4 v = *reinterpret_cast<const float4*>(r + 4 + lane * 4);
-            a[0] = fmaf(v.x, wgt, a[0]); a[1] = fmaf(v.y, wgt, a[1]);
-            a[2] = fmaf(v.z, wgt, a[2]); a[3] = fmaf(v.w, wgt, a[3]);
-        } else {
-            const float2 v = *reinterpret_cast<const float2*>(r + 4 + lane * 2);
-            a[0] = fmaf(v.x, wgt, a[0]); a[1] = fmaf(v.y, wgt, a[1]);
-        }
-    }
+    merge_rows<D>(row_ptr, n, lane, L, a, &gm);
 
     if constexpr (QUANT) {
         const float inv = L > 0.f ? 1.0f / L : 0.f;
@@ -685,18 +749,7 @@ decode_combine_kernel(const float* __restrict__ rows, int BH, int nparts, Decode
         return;
     }
     if (out != nullptr) {
-        const float inv = L > 0.f ? 1.0f / L : 0.f;     // no positions at all: zeros
-        __half* o = out + (size_t)bh * D + lane * DPL;
-        if constexpr (DPL == 4) {
-            __half2 h0 = __floats2half2_rn(a[0] * inv, a[1] * inv);
-            __half2 h1 = __floats2half2_rn(a[2] * inv, a[3] * inv);
-            uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&h0);
-            pk.y = *reinterpret_cast<uint32_t*>(&h1);
-            *reinterpret_cast<uint2*>(o) = pk;
-        } else {
-            *reinterpret_cast<__half2*>(o) = __floats2half2_rn(a[0] * inv, a[1] * inv);
-        }
+        store_out_row<D>(out + (size_t)bh * D, lane, L, a);
     } else {
         float* r = row_out + (size_t)bh * ROW;
         if (lane == 0) *reinterpret_cast<float4*>(r) = make_float4(L > 0.f ? gm : -INFINITY, L, 0.f, 0.f);
@@ -873,6 +926,7 @@ int env_int(const char* name, int dflt) {
 // Tuning overrides, read from the environment once per process.
 int forced_ctas() { static const int v = env_int("I8TK_DECODE_CTAS", 0); return v; }
 int scales_by_ldg() { static const int v = env_int("I8TK_DECODE_SCALES_LDG", 0); return v; }
+int whole_row_tiles(int dflt) { static const int v = env_int("I8TK_DECODE_WHOLE_TILES", -1); return v >= 0 ? v : dflt; }
 int paged_target_tiles(int dflt) { static const int v = env_int("I8TK_DECODE_TARGET_TILES", 0); return v > 0 ? v : dflt; }
 
 // CTAs are persistent over contiguous runs of the flat tile sequence.  The
@@ -907,6 +961,21 @@ DecodePlan make_plan(int BH, int S, int D, int sms) {
     return p;
 }
 
+// Runs of whole rows for contexts of at most kWholeRowMaxTiles tiles: as many CTAs as rows, up
+// to one resident wave; beyond that a CTA takes several rows, one after the other.
+DecodePlan make_whole_plan(int BH, int S, int D, int sms) {
+    const int ctas_per_sm = (D == 64) ? DecodeTraits<64>::CTAS_PER_SM : DecodeTraits<128>::CTAS_PER_SM;
+    DecodePlan p;
+    p.tpb = (S + kTile - 1) / kTile;
+    p.total = (long long)BH * p.tpb;
+    const long long cap = (long long)sms * ctas_per_sm;
+    const int rows_per_cta = (int)((BH + cap - 1) / cap);
+    p.tpc = rows_per_cta * p.tpb;
+    p.nctas = (BH + rows_per_cta - 1) / rows_per_cta;
+    p.maxseg = rows_per_cta;
+    return p;
+}
+
 size_t rows_bytes(const DecodePlan& p, int D) {
     return (size_t)p.nctas * p.maxseg * kConsumers * (D + 4) * sizeof(float);
 }
@@ -936,23 +1005,25 @@ size_t workspace_bytes(int BH, int S, int D) {
     return flat > ragged ? flat : ragged;
 }
 
-template <int D, bool SCALES_BULK, bool PAGED = false>
+// `whole_out`: the plan is one of whole rows (make_whole_plan) and the scan writes the fp16 output itself.
+template <int D, bool SCALES_BULK, bool PAGED = false, bool WHOLE = false>
 int launch_partial(const int8_t* Q, const int8_t* K, const int8_t* V, const float* sQ,
                    const float* sK, const float* sV, float* rows, int S, const DecodePlan& p,
-                   uint32_t* status, cudaStream_t stream, PagedKV pg = PagedKV{}) {
+                   uint32_t* status, cudaStream_t stream, PagedKV pg = PagedKV{}, __half* whole_out = nullptr) {
     using T = DecodeTraits<D>;
+    constexpr int kSmem = WHOLE ? kWholeSmemBytes<D> : T::SMEM_BYTES;
     static bool attr_done[64] = {false};   // per template instance
     int dev = 0;
     I8TK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        I8TK_CUDA(cudaFuncSetAttribute(decode_partial_kernel<D, SCALES_BULK, PAGED>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+        I8TK_CUDA(cudaFuncSetAttribute(decode_partial_kernel<D, SCALES_BULK, PAGED, WHOLE>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
         attr_done[dev] = true;
     }
     const float score_scale_log2 = kLog2e / sqrtf((float)D);
     if (g_probe_start) I8TK_CUDA(cudaEventRecord(g_probe_start, stream));
-    I8TK_CUDA(launch_after(decode_partial_kernel<D, SCALES_BULK, PAGED>, dim3(p.nctas), dim3(kThreads),
-                           T::SMEM_BYTES, stream, Q, K, V, sQ, sK, sV, rows, S, p, score_scale_log2, status, pg));
+    I8TK_CUDA(launch_after(decode_partial_kernel<D, SCALES_BULK, PAGED, WHOLE>, dim3(p.nctas), dim3(kThreads),
+                           kSmem, stream, Q, K, V, sQ, sK, sV, rows, S, p, score_scale_log2, status, pg, whole_out));
     if (g_probe_stop) I8TK_CUDA(cudaEventRecord(g_probe_stop, stream));
     return I8TK_OK;
 }
@@ -973,6 +1044,20 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
     const bool bulk_scales = (S % 4 == 0) && aligned_to(sK, 16) && aligned_to(sV, 16) &&
                              scales_by_ldg() == 0;
     int rc;
+    // Short contexts, fp16 output: runs of whole rows, merged inside the scan's CTAs -- one launch.
+    // Measured against the split plan + merge kernel: it wins (1.2-1.9 us of 6-20 us per step) while
+    // a row is at most 8 tiles, or at most 16 with enough rows to keep the SMs busy on whole rows
+    // (a single CTA streams a row at a few tens of GB/s), and while the rows fit two resident
+    // waves (beyond that equal runs of tiles balance better than whole rows).
+    const int wt = whole_row_tiles(kWholeRowMaxTiles);
+    const long long slots = (long long)sm_count() * T::CTAS_PER_SM;
+    const bool whole = p.tpb <= wt && (p.tpb <= wt / 2 || BH >= 24) && BH <= 2 * slots;
+    if (out != nullptr && part == nullptr && qo.codes == nullptr && whole && forced_ctas() == 0) {
+        const DecodePlan wp = make_whole_plan(BH, S, D, sm_count());
+        return bulk_scales
+                   ? launch_partial<D, true, false, true>(Q, K, V, sQ, sK, sV, rows, S, wp, status, stream, PagedKV{}, out)
+                   : launch_partial<D, false, false, true>(Q, K, V, sQ, sK, sV, rows, S, wp, status, stream, PagedKV{}, out);
+    }
     if (bulk_scales)
         rc = launch_partial<D, true>(Q, K, V, sQ, sK, sV, rows, S, p, status, stream);
     else

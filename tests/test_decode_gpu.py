@@ -79,6 +79,21 @@ def test_more_shapes_vs_oracle(B, H, D, S):
     _assert_close(out, ref, (B, H, D, S))
 
 
+@pytest.mark.parametrize("B,H,D,S", [(50, 12, 64, 300), (20, 30, 128, 261), (40, 12, 64, 1025), (3, 8, 64, 2048),
+                                     (1, 32, 128, 2040)])
+def test_short_contexts_merged_inside_the_scan(B, H, D, S):
+    """Rows of at most 16 tiles are scanned whole by one CTA, which merges its four warps' partial rows in
+    shared memory and writes the output itself (no merge kernel); with more rows than one resident wave a
+    CTA takes several rows in turn.  Shapes on both sides of that plan's limits, scales riding the bulk
+    copies (S % 4 == 0) and loaded by the lanes."""
+    args = _seeded_case(B, H, D, S, 7 + S)
+    out = _run(*args)
+    ref = odec.decode_attention(*args)
+    _assert_close(out, ref, (B, H, D, S))
+    again = _run(*args)
+    assert np.array_equal(out, again)
+
+
 def test_degenerate_inputs():
     # zeros: uniform softmax over zero values -> 0; constant: output == the V row
     for D in (64, 128):
