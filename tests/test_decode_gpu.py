@@ -80,12 +80,16 @@ def test_more_shapes_vs_oracle(B, H, D, S):
 
 
 @pytest.mark.parametrize("B,H,D,S", [(50, 12, 64, 300), (20, 30, 128, 261), (40, 12, 64, 1025), (3, 8, 64, 2048),
-                                     (1, 32, 128, 2040)])
+                                     (1, 32, 128, 2040),
+                                     # few rows: a cluster of CTAs per row, merged through distributed shared memory
+                                     (1, 12, 64, 4096), (1, 32, 128, 2048), (2, 5, 64, 1500), (1, 3, 128, 1027),
+                                     (6, 12, 64, 1024), (1, 1, 64, 1100)])
 def test_short_contexts_merged_inside_the_scan(B, H, D, S):
     """Rows of at most 16 tiles are scanned whole by one CTA, which merges its four warps' partial rows in
     shared memory and writes the output itself (no merge kernel); with more rows than one resident wave a
-    CTA takes several rows in turn.  Shapes on both sides of that plan's limits, scales riding the bulk
-    copies (S % 4 == 0) and loaded by the lanes."""
+    CTA takes several rows in turn.  With few rows of 8 tiles or more, a cluster of 2-8 CTAs shares a row
+    (some ranks may get no tile of it) and rank 0 merges the ranks' rows.  Shapes on both sides of those
+    plans' limits, scales riding the bulk copies (S % 4 == 0) and loaded by the lanes."""
     args = _seeded_case(B, H, D, S, 7 + S)
     out = _run(*args)
     ref = odec.decode_attention(*args)
