@@ -15,8 +15,8 @@
 //   kernel repeated the work S/128 times and took a fifth of its instructions.  Q and K
 //   tiles (int8) and V16 tiles (fp16) arrive by TMA; V16 lands directly in the MN-major
 //   128-byte-swizzled layout the PV instruction reads.
-// * Eight softmax warps, two per TMEM lane quarter, each thread owning 64 KV
-//   positions of one query row.  The scores are read from tensor memory once
+// * Eight softmax warps, two per TMEM lane quarter, each thread owning half of the KV
+//   positions of a tile (32 of 64) for one query row.  The scores are read from tensor memory once
 //   (tcgen05.ld), converted without the conversion unit (|q.k| < 2^22, so the
 //   integer is added to the bit pattern of 1.5*2^23 and 1.5*2^23 subtracted as a
 //   float), scaled by sK and kept in registers; the row maximum is combined across
@@ -26,8 +26,9 @@
 //   tcgen05.st) rare.  The exponentials of tile j (special-function unit) are
 //   interleaved, eight columns at a time, with the conversion of tile j+1's scores
 //   (integer and FMA pipes), which take over the registers just released; Q.K^T
-//   therefore runs two tiles ahead of P.V.  P goes as fp16 pairs into one of two
-//   64-column blocks of tensor memory (tcgen05.st), from where the P.V instruction reads
+//   therefore runs two tiles ahead of P.V (one tile at head_dim 128, which keeps a single
+//   score tile in tensor memory).  P goes as fp16 pairs into one of two blocks of tensor
+//   memory (tcgen05.st), from where the P.V instruction reads
 //   its A operand: no shared-memory round trip, no swizzle arithmetic, no proxy fence.
 //   Packed fp32x2 arithmetic throughout.
 // * K and V16 tiles move through rings of kRing stages, so a late tile does not hold up the
@@ -35,8 +36,12 @@
 // * Every mbarrier wait is bounded; on expiry a status word is set and all
 //   roles fall through to the common exit, which frees tensor memory.
 //
-// Supported: head_dim 64, 128 (KV tiles of 128 positions) and 256 (tiles of 64: the score, P and
-// 256-column output accumulators of a 128-position tile exceed tensor memory), any seq_len (a
+// * KV tiles are 64 positions.  At head_dim 64 and 128 a CTA then needs 96 registers per thread, 256
+//   columns of tensor memory and at most 88 KB of shared memory, so TWO CTAs share an SM and their
+//   sixteen softmax warps hide one another's waits; at head_dim 256 the 256-column output leaves
+//   room for one CTA.
+//
+// Supported: head_dim 64, 128 and 256, any seq_len (a
 // partial last tile is masked: the operand tiles then hold rows of the next head or TMA's zero
 // fill, whose scores are set to -inf).
 #include "tcgen05.cuh"
@@ -74,10 +79,19 @@ struct PrefillCfg {
     static constexpr int OFF_BARS = OFF_XCH + 2 * 2 * kQT * 4;
     static constexpr int NUM_BARS = 24;
     static constexpr int SMEM_BYTES = 1024 + OFF_BARS + NUM_BARS * 8 + 16;
-    static constexpr int TMEM_COLS = 512;                  // S0 | S1 | P0 | P1 | O
-    static constexpr int TM_S0 = 0, TM_S1 = KT;            // two score tiles of KT int32 columns
-    static constexpr int TM_P = 2 * KT;                    // two fp16 P tiles of KT / 2 columns (two values per column)
-    static constexpr int TM_O = (D == 256) ? 256 : 3 * KT; // fp32 output, D columns
+    // S0 | S1 | P0 | P1 | O; half of the tensor memory where that is enough, so that two CTAs fit an SM
+    static constexpr int TMEM_COLS = (((D == 256) ? 256 : ((D == 128 && KT == 64) ? 1 : 2) * KT + KT) + D <= 256) ? 256 : 512;
+    // head_dim 64 and 128 on 64-position tiles: 96 registers, 44 / 88 KB of shared memory and 256
+    // columns per CTA, i.e. two CTAs and sixteen softmax warps per SM to hide the waits of one another
+    // (B8 H8 S4096 D64: 582 -> 522 us; B4 H8 S4096 D128, where the 256 columns leave room for one score
+    // tile only, so Q.K^T runs one tile ahead instead of two: 311 -> 297 us; 32-position tiles with two
+    // score buffers at D=128: 552 us)
+    static constexpr int CTAS_PER_SM = ((D == 64 || D == 128) && KT == 64) ? 2 : 1;
+    // score tiles of KT int32 columns: two, or one where the other would cost the second CTA per SM
+    static constexpr int NSB = (D == 128 && KT == 64) ? 1 : 2;
+    static constexpr int TM_S0 = 0;
+    static constexpr int TM_P = NSB * KT;                  // two fp16 P tiles of KT / 2 columns (two values per column)
+    static constexpr int TM_O = (D == 256) ? 256 : TM_P + KT; // fp32 output, D columns
     static_assert(TM_P + KT <= TM_O && TM_O + D <= TMEM_COLS, "tensor-memory layout");
     static_assert(SMEM_BYTES <= 232448, "shared memory of an SM");
 };
@@ -127,7 +141,7 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 }
 
 template <int D, int KT>
-__global__ void __launch_bounds__(kPrefillThreads, 1)
+__global__ void __launch_bounds__(kPrefillThreads, PrefillCfg<D, KT>::CTAS_PER_SM)
 prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const float* __restrict__ sQ,
                          const float* __restrict__ sK,
@@ -245,10 +259,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             // while they exponentiate tile j, so S(j+1) has to be on its way before P(j-1) is complete.
             for (int j = 0; j < nt + 2 && ok; ++j) {
                 if (j < nt) {
-                    const int st = j & 1;                // score buffer
+                    const int st = j % Cfg::NSB;         // score buffer
                     const int kst = j % kRing;           // stage of the K ring
                     if (!mbar_wait_spin_bounded(bar(B_KFULL + kst), (j / kRing) & 1) ||
-                        !mbar_wait_spin_bounded(bar(B_SEMPTY + st), ((j >> 1) & 1) ^ 1)) {
+                        !mbar_wait_spin_bounded(bar(B_SEMPTY + st), ((j / Cfg::NSB) & 1) ^ 1)) {
                         ok = false;
                         break;
                     }
@@ -262,7 +276,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                         const uint32_t ka = ks + (k / 4) * Cfg::K_SLAB;
                         const uint64_t da = (D >= 128) ? smem_desc_sw128(qa) : smem_desc_sw64(qa);
                         const uint64_t db = (D >= 128) ? smem_desc_sw128(ka) : smem_desc_sw64(ka);
-                        mma_i8(tmem_base + (st ? Cfg::TM_S1 : Cfg::TM_S0), da + 2 * (k % 4), db + 2 * (k % 4), idesc_qk,
+                        mma_i8(tmem_base + Cfg::TM_S0 + st * kKT, da + 2 * (k % 4), db + 2 * (k % 4), idesc_qk,
                                k != 0);
                     }
                     tc_commit(bar(B_KEMPTY + kst));
@@ -423,11 +437,12 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             if (has_next) {
                 commit_scales(j + 1);
                 if (j + 2 < nt) prefetch(j + 2);
-                const bool got = mbar_wait_spin_bounded(bar(B_SFULL + (st ^ 1)), ((j + 1) >> 1) & 1);
+                const int sb1 = (j + 1) % Cfg::NSB;       // score buffer of the next tile
+                const bool got = mbar_wait_spin_bounded(bar(B_SFULL + sb1), ((j + 1) / Cfg::NSB) & 1);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
                 tc_fence_after();
                 const float* ksc = wsc + (st ^ 1) * HK;
-                const uint32_t s_addr = lane_addr + (st ? Cfg::TM_S0 : Cfg::TM_S1) + half * HK;
+                const uint32_t s_addr = lane_addr + Cfg::TM_S0 + sb1 * kKT + half * HK;
                 uint32_t sr[2][16];
                 tmem_ld16(s_addr, sr[0]);
 #pragma unroll
@@ -444,7 +459,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                 if (j + 2 == nt && tail_valid < kKT) mask_tail(y, mx);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_SEMPTY + (st ^ 1)));
+                if (lane == 0) mbar_arrive(bar(B_SEMPTY + sb1));
             } else {
 #pragma unroll
                 for (int c = 0; c < HK / 8; ++c) exp8(&y[c * 4], nm2, prow + c * 4);
@@ -568,8 +583,8 @@ extern "C" int i8tk_attention_forward(const int8_t* Q, const int8_t* K, const in
     __half* V16 = reinterpret_cast<__half*>(static_cast<unsigned char*>(workspace) + 256);
     const int BH = batch * heads;
     if (head_dim == 64)
-        return launch_prefill<64, 128>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
+        return launch_prefill<64, 64>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
     if (head_dim == 128)
-        return launch_prefill<128, 128>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
+        return launch_prefill<128, 64>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
     return launch_prefill<256, 64>(Q, K, V, static_cast<__half*>(out_f16), sQ, sK, sV, BH, seq_len, status, V16, st);
 }
