@@ -43,6 +43,8 @@ def make_inputs(torch, ext, b, h, s, d, outliers=False, seed=0):
 PROFILE_CASES = {
     "decode_d64": (8, 12, 64, 16384),      # 201 MB of int8 K+V
     "decode_d128": (8, 8, 128, 8192),      # 134 MB
+    "decode_d64_ctx4096": (32, 12, 64, 4096),   # the short end of the serving sweep: 201 MB, 28 tiles per CTA
+    "decode_d64_cfg0": (1, 12, 64, 1024),  # one request: a thread-block cluster per (b,h) row, no merge kernel
     "mlp_m512_768": (512, 768, 3072),      # the reference's own benchmark shape: latency, not throughput
     "mlp_m4096_768": (4096, 768, 3072),    # fused MLP forward (L2 resident by nature: 30 MB of operands)
     "mlp_m4096_1024": (4096, 1024, 4096),
@@ -52,6 +54,7 @@ PROFILE_CASES = {
     "prefill_d128": (2, 8, 4096, 128),
     "prefill_d256": (2, 8, 2048, 256),     # 64-position KV tiles
     "paged_d64_p64": (8, 12, 64, 16384, 64),   # B, H, D, longest request, page: lengths 2048..16384, shuffled table
+    "paged_d64_p16": (8, 12, 64, 16384, 16),   # the same on 16-position pages: 1 KB bulk copies
     "lnquant_f16_1024": (131072, 1024),    # rows, cols: 268 MB in, 134 MB of codes out
 }
 
