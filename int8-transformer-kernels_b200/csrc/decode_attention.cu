@@ -1159,6 +1159,41 @@ int launch_partial(const int8_t* Q, const int8_t* K, const int8_t* V, const floa
     return I8TK_OK;
 }
 
+// Whether the device can co-schedule clusters of `cluster` CTAs of the cluster form of the scan at
+// all (a partitioned or otherwise restricted device may not): asked once per size, otherwise the
+// other plans are used.
+template <int D>
+bool clusters_fit(int cluster, bool bulk) {
+    static int known[64][9] = {};            // 0 unknown, 1 yes, -1 no
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cluster < 2 || cluster > 8) return false;
+    int& k = known[dev][cluster];
+    if (k == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)cluster);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kClusterSmemBytes<D>;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)cluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        cudaError_t e = cudaFuncSetAttribute(decode_partial_kernel<D, true, false, 2>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kClusterSmemBytes<D>);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(decode_partial_kernel<D, false, false, 2>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kClusterSmemBytes<D>);
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, decode_partial_kernel<D, true, false, 2>, &cfg);
+        if (e != cudaSuccess) (void)cudaGetLastError();
+        k = (e == cudaSuccess && n > 0) ? 1 : -1;
+    }
+    (void)bulk;
+    return k > 0;
+}
+
 template <int D>
 int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out, float* part,
                   const float* sQ, const float* sK, const float* sV, int BH, int S,
@@ -1190,7 +1225,8 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
     if (out != nullptr && part == nullptr && qo.codes == nullptr && wt > 0 && forced_ctas() == 0 && p.tpb >= 8) {
         int cl = 8;
         while (cl > 2 && (cl > p.tpb || (long long)BH * cl > slots)) cl >>= 1;
-        if (cl <= p.tpb && (long long)BH * cl <= slots && (p.tpb + cl - 1) / cl <= 4) {
+        if (cl <= p.tpb && (long long)BH * cl <= slots && (p.tpb + cl - 1) / cl <= 4 &&
+            clusters_fit<D>(cl, bulk_scales)) {
             const DecodePlan cp = make_cluster_plan(BH, S, cl);
             return bulk_scales ? launch_partial<D, true, false, 2>(Q, K, V, sQ, sK, sV, rows, S, cp, status, stream,
                                                                    PagedKV{}, out, cl)
