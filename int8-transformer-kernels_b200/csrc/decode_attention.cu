@@ -1217,7 +1217,15 @@ int launch_decode(const int8_t* Q, const int8_t* K, const int8_t* V, __half* out
     // waves (beyond that equal runs of tiles balance better than whole rows).
     const int wt = whole_row_tiles(kWholeRowMaxTiles);
     const long long slots = (long long)sm_count() * T::CTAS_PER_SM;
-    const bool whole = p.tpb <= wt && (p.tpb <= wt / 2 || BH >= 24) && BH <= 2 * slots;
+    bool whole = p.tpb <= wt && (p.tpb <= wt / 2 || BH >= 24) && BH <= 2 * slots;
+    // Longer rows (up to 4 x that, 8192 positions) when the rows by themselves fill the machine: whole rows
+    // on at least three quarters of the resident slots read as fast as equal runs and save the merge kernel
+    // (B32 H12 ctx 4096 34.8 vs 36.9 us, ctx 8192 66.3 vs 70.5 us, B16 H32 D128 ctx 8192 163.8 vs 168.4 us;
+    // break-even at ctx 16384, 5 % slower at 32768, where fewer CTAs keep fewer bytes in flight).
+    if (!whole && p.tpb <= 4 * wt && BH <= 2 * slots) {
+        const long long per_cta = (BH + slots - 1) / slots;
+        whole = 4 * ((BH + per_cta - 1) / per_cta) >= 3 * slots;
+    }
     // Few rows (one request, a handful of heads): a cluster of up to eight CTAs per row, merged through
     // distributed shared memory, while a rank gets at most four tiles and all clusters are resident.
     // (Measured: B1 H12 ctx 1024 / 2048 / 4096 5.0 / 5.4 / 6.6 us per step replayed from a CUDA graph against
